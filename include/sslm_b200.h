@@ -1,0 +1,193 @@
+/* libsslm_b200 -- the C ABI of the B200 (sm_100a) implementation of SuperSLM's
+ * integer-only transformer forward pass.
+ *
+ * The first block re-declares, name for name and argument for argument, the verbs of the
+ * reference's public ABI that lie on the forward-pass path, so that a program written
+ * against the reference header links against this library unchanged. Each declaration
+ * cites the reference declaration it replaces (paths inside the reference project).
+ * Handles are opaque; statuses keep the reference's frozen ordinals
+ * (include/superslm/sslm_abi.h:96-163).
+ *
+ * Differences a caller can observe, all inside the reference's contract:
+ *  - model weights and KV live in GPU memory. The `buf` passed to sslm_kv_pool_create /
+ *    sslm_workspace_create is still validated (non-null, size, 64-byte alignment) but is
+ *    used only as the caller's reservation: device memory of the same capacity is
+ *    allocated by the call (SSLM_ALLOCATION_FAILED if the device cannot provide it).
+ *  - sslm_kv_block_size still returns layers*context_cap*kv_heads*head_dim*2 bytes; a
+ *    pool of N blocks holds N full-length sequences, stored as 16-token pages.
+ *  - q/k/v bias sections (BIA1) and the int16 KV precision are rejected at map time with
+ *    SSLM_ARTIFACT_REJECTED; the Option-G header flag is ignored, as the reference's CPU
+ *    ABI path ignores it.
+ * There is no CPU fallback: every compute verb fails with SSLM_ALLOCATION_FAILED if no
+ * CUDA device is usable.
+ */
+#ifndef SSLM_B200_H
+#define SSLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- types: include/superslm/sslm_abi.h:20-46, :96-224, :250 ---------------------- */
+typedef struct sslm_model_s* sslm_model;
+typedef struct sslm_seq_s* sslm_seq;
+typedef struct sslm_adapter_s* sslm_adapter;
+typedef struct sslm_kv_pool_s* sslm_kv_pool;
+typedef struct sslm_workspace_s* sslm_workspace;
+
+typedef struct sslm_config {
+	int32_t max_batch;        /* max sequences in one sslm_decode_step call, >= 1 */
+	int32_t max_chunk_budget; /* max tokens in one sslm_prefill call, >= 1 */
+	int32_t max_layer_budget; /* in [1, num_hidden_layers] */
+	uint32_t reserved;        /* must be 0 */
+} sslm_config;
+
+typedef enum sslm_status {
+	SSLM_OK = 0,
+	SSLM_INVALID_ARGUMENT = 1,
+	SSLM_BUFFER_TOO_SMALL = 2,
+	SSLM_MISALIGNED_BUFFER = 3,
+	SSLM_ARTIFACT_REJECTED = 4,
+	SSLM_ADAPTER_MODEL_MISMATCH = 5,
+	SSLM_RESTORE_MODEL_MISMATCH = 6,
+	SSLM_RESTORE_KV_MISMATCH = 7,
+	SSLM_MODEL_HAS_LIVE_SEQUENCES = 8,
+	SSLM_POOL_HAS_LIVE_HANDLES = 9,
+	SSLM_ADAPTER_HAS_LIVE_SEQUENCES = 10,
+	SSLM_ADAPTER_SWAP_MIDTOKEN_REJECTED = 11,
+	SSLM_SEQ_RESET_MIDTOKEN_REJECTED = 12,
+	SSLM_PREFIX_FROZEN_REJECTED = 13,
+	SSLM_KV_POOL_EXHAUSTED = 14,
+	SSLM_TOKEN_ID_OUT_OF_RANGE = 15,
+	SSLM_CONTEXT_CAP_EXCEEDED = 16,
+	SSLM_TOKEN_ID_UNMAPPED = 17,
+	SSLM_SCHEMA_NOT_FOUND = 18,
+	SSLM_SCHEMA_BIND_REJECTED = 19,
+	SSLM_SCHEMA_SPAN_UNBOUND = 20,
+	SSLM_PREFIX_SCHEMA_MISMATCH = 21,
+	SSLM_RESTORE_SCHEMA_MISMATCH = 22,
+	SSLM_SCHEMA_SPAN_UNREACHABLE = 23,
+	SSLM_SCHEMA_UNSATISFIABLE = 24,
+	SSLM_ALLOCATION_FAILED = 25,
+	SSLM_NUMERIC_STEP_REFUSED = 26,
+	SSLM_STATUS_NEXT_FREE
+} sslm_status;
+
+typedef enum sslm_span_kind { SSLM_SPAN_PROMPT = 0, SSLM_SPAN_SCHEMA_CONTENT = 1 } sslm_span_kind;
+
+/* sslm_decode_step reads layer_budget only (the v1.1 four-byte prefix); the remaining
+ * fields exist so that the struct has the reference's size and layout. */
+typedef struct sslm_decode_params {
+	int32_t layer_budget;
+	uint32_t struct_size;
+	int32_t mode;
+	int32_t alpha_q15;
+	int32_t anti_lm_max_order;
+	int32_t top_k;
+	int64_t q_ln2;
+	int64_t q_b;
+	int64_t q_c;
+} sslm_decode_params;
+
+#define SSLM_ABI_ALIGNMENT_BYTES 64u
+
+/* every entry point below has default visibility; the rest of the library is hidden */
+#if defined(__GNUC__)
+#define SSLM_API __attribute__((visibility("default")))
+#else
+#define SSLM_API
+#endif
+
+/* ---- model: include/superslm/sslm_abi_functions_g5_comparable.inc (sslm_model_map,
+ *      sslm_model_unmap); src/sslm_abi.cpp:1058-1140. The artifact bytes are copied to the
+ *      device during the call; the caller may free `data` afterwards. */
+SSLM_API sslm_status sslm_model_map(const void* data, size_t size, sslm_model* out);
+SSLM_API sslm_status sslm_model_unmap(sslm_model model);
+
+/* ---- sizing + pool + workspace: sslm_abi_functions.inc (sslm_kv_block_size,
+ *      sslm_kv_pool_overhead_size, sslm_kv_pool_create/destroy, sslm_workspace_size,
+ *      sslm_workspace_create/destroy); src/sslm_abi.cpp:852-1051 */
+SSLM_API size_t sslm_kv_block_size(sslm_model model);
+SSLM_API size_t sslm_kv_pool_overhead_size(sslm_model model, uint32_t block_count);
+SSLM_API sslm_status sslm_kv_pool_create(sslm_model model, void* buf, size_t buf_size, uint32_t block_count,
+                                sslm_kv_pool* out);
+SSLM_API sslm_status sslm_kv_pool_destroy(sslm_kv_pool pool);
+SSLM_API size_t sslm_workspace_size(sslm_model model, const sslm_config* config);
+SSLM_API sslm_status sslm_workspace_create(sslm_model model, const sslm_config* config, void* buf,
+                                  size_t buf_size, sslm_workspace* out);
+SSLM_API sslm_status sslm_workspace_destroy(sslm_workspace ws);
+
+/* ---- sequences: sslm_abi_functions_g5_comparable.inc (sslm_seq_create, sslm_seq_release,
+ *      sslm_prefill, sslm_decode_step); src/sslm_abi.cpp:1695-1760, :1950-1975, :1989-2449.
+ *      sslm_prefill consumes min(count, chunk_budget) tokens as ONE chunk-batched pass;
+ *      sslm_decode_step advances every sequence by params->layer_budget layers and writes
+ *      the greedy token, or -1 while the token is in flight, -3 for a released handle. `ws`
+ *      may be NULL (an internal workspace is used). */
+SSLM_API sslm_status sslm_seq_create(sslm_model model, sslm_kv_pool* pool, sslm_seq* out);
+SSLM_API sslm_status sslm_seq_release(sslm_seq seq);
+SSLM_API sslm_status sslm_prefill(sslm_model model, sslm_seq seq, const int32_t* tokens, int32_t count,
+                         int32_t chunk_budget, sslm_span_kind kind, sslm_workspace ws,
+                         int32_t* consumed);
+SSLM_API sslm_status sslm_decode_step(sslm_model model, sslm_seq* seqs, int32_t n,
+                             const sslm_decode_params* params, sslm_workspace ws, int32_t* out_tokens);
+
+/* ---- adapters: sslm_abi_functions.inc (sslm_adapter_map, sslm_adapter_release,
+ *      sslm_adapter_residency, sslm_seq_set_adapter); src/sslm_abi.cpp:2990-3118 */
+SSLM_API sslm_status sslm_adapter_map(const void* data, size_t size, sslm_model base, sslm_adapter* out);
+SSLM_API sslm_status sslm_adapter_release(sslm_adapter adapter);
+SSLM_API size_t sslm_adapter_residency(sslm_adapter adapter);
+SSLM_API sslm_status sslm_seq_set_adapter(sslm_seq seq, sslm_adapter adapter /* NULL = detach */);
+
+/* ---- state export: sslm_abi_functions.inc (sslm_seq_save); src/sslm_abi.cpp:2620-2716.
+ *      Writes the reference's SSB3 blob, KV block in canonical
+ *      [layer][K|V][kv_head][position][head_dim] order. */
+SSLM_API sslm_status sslm_seq_save(sslm_seq seq, void* buf, size_t* n);
+
+/* ======================================================================================
+ * Entry points below have no counterpart in the reference; they exist for device
+ * selection, for the standalone linear-layer workload and for measurement.
+ * ====================================================================================== */
+
+/* CUDA device ordinal used by subsequent sslm_model_map calls of this process (default 0,
+ * or the SSLM_B200_DEVICE environment variable). */
+SSLM_API sslm_status sslm_b200_set_device(int ordinal);
+
+/* One int8 linear layer with the reference's full epilogue, on host buffers:
+ *   acc = x[M,K] . w[N,K]^T ; folded = ApplyWeightScaleFold(acc, fold[N,3]) ;
+ *   per row: RequantChainChecked(folded, incoming = {in_scale[m]}, site constant).
+ * (GemmInt8Accumulate + FunnelProjectedRow, src/matmul.cpp:466-509,
+ * src/forward/forward_sites.cpp:1114-1146, :1182-1203.) Outputs that are NULL are skipped.
+ * in_scales: M pairs (m, e); out_scales: M pairs; row_status: M reference
+ * SslmForwardStatus ordinals (0 = Ok). use_tensor_cores: 0 forces the streaming GEMV
+ * kernel, 1 lets M > 8 take the tcgen05 kernel. */
+SSLM_API sslm_status sslm_b200_linear(const int8_t* x, const int8_t* w, const int32_t* fold, int32_t M,
+                             int32_t N, int32_t K, const int64_t* in_scales, int64_t site_m,
+                             int64_t site_e, int32_t use_tensor_cores, int32_t* out_folded,
+                             int8_t* out_codes, int64_t* out_scales, int32_t* row_status);
+
+/* The same layer with operands resident in HBM, launched `iters` times back to back on one
+ * stream; returns the average device time of one launch of the GEMM/GEMV kernel plus its
+ * funnel kernel in microseconds through *avg_us (CUDA events). For the benchmark. */
+SSLM_API sslm_status sslm_b200_linear_bench(int32_t M, int32_t N, int32_t K, int32_t use_tensor_cores,
+                                   int32_t iters, uint64_t seed, double* avg_us_gemm,
+                                   double* avg_us_total);
+
+/* Device time (ms, CUDA events on the workspace stream) of the most recent sslm_prefill or
+ * sslm_decode_step that ran on `ws`, and the number of kernels launched on it so far. */
+SSLM_API sslm_status sslm_b200_last_call_ms(sslm_workspace ws, float* ms, uint64_t* kernel_launches);
+
+/* Tests only: capture the full int32 logit row of every token produced by later
+ * sslm_decode_step calls on `ws` into host memory ([tokens in call order][vocab]);
+ * pass NULL to stop. */
+SSLM_API sslm_status sslm_b200_capture_logits(sslm_workspace ws, int32_t* host_rows);
+
+/* Bytes of HBM held by the model's weights, tables and constants. */
+SSLM_API size_t sslm_b200_model_device_bytes(sslm_model model);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SSLM_B200_H */

@@ -1,0 +1,115 @@
+// Host-side objects behind the sslm_* handles: a model resident in HBM, a paged KV pool,
+// a workspace (device scratch + stream + pinned staging), sequences and adapters.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/sslm_b200.h"
+#include "sslm_artifact.h"
+#include "sslm_kernels.h"
+
+struct DeviceArena {
+	uint8_t* base = nullptr;
+	size_t size = 0, used = 0;
+	void* take(size_t bytes) {
+		used = (used + 255) & ~(size_t)255;
+		void* p = base + used;
+		used += bytes;
+		return p;
+	}
+};
+
+struct sslm_workspace_s {
+	sslm_model_s* model = nullptr;
+	sslm_config config{};
+	int device = 0;
+	int row_cap = 0;            // rows the device scratch can hold
+	cudaStream_t stream = nullptr;
+	uint8_t* d_scratch = nullptr;
+	size_t scratch_bytes = 0;
+	// pinned host staging, row_cap entries each
+	sslm::RowDesc* h_rows = nullptr;
+	sslm::RowSource* h_src = nullptr;
+	sslm::RowSink* h_sink = nullptr;
+	int32_t* h_status = nullptr;
+	unsigned long long* h_sat = nullptr;
+	unsigned long long* h_best = nullptr;
+	// device mirrors
+	sslm::RowDesc* d_rows = nullptr;
+	sslm::RowSource* d_src = nullptr;
+	sslm::RowSink* d_sink = nullptr;
+	// carved row buffers (base pointers for row 0)
+	sslm::RowBatch base{};
+	size_t wide_ld = 0;
+	int32_t* logit_capture = nullptr;   // host buffer for full logit rows (tests), or nullptr
+	int32_t* d_logits = nullptr;
+	cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+	float last_ms = 0.f;
+	uint64_t launches = 0;
+};
+
+struct sslm_model_s {
+	int device = 0;
+	sslm::Dims dims{};
+	sslm::ConfigView cfg{};
+	uint8_t hash[32]{};
+	DeviceArena arena;
+	std::vector<sslm::LayerDev> h_layers;
+	sslm::LayerDev* d_layers = nullptr;
+	const int8_t* d_embed = nullptr;
+	const int8_t* d_head = nullptr;
+	const int8_t* d_final_gain = nullptr;
+	sslm::Scale c_embed{}, c_final{};
+	int32_t* d_cos = nullptr;
+	int32_t* d_sin = nullptr;
+	int32_t* d_silu = nullptr;
+	std::atomic<uint32_t> live_refs{0};
+	std::mutex default_ws_mutex;
+	sslm_workspace_s* default_ws = nullptr;
+	size_t weight_bytes = 0;
+};
+
+struct sslm_kv_pool_s {
+	sslm_model_s* model = nullptr;
+	uint32_t block_count = 0;
+	uint32_t blocks_free = 0;
+	int pages_per_block = 0;
+	sslm::KvPoolDev dev{};
+	std::mutex mutex;
+	std::vector<int32_t> free_pages;
+	std::atomic<uint32_t> live_refs{0};
+};
+
+struct sslm_adapter_s {
+	sslm_model_s* base = nullptr;
+	size_t artifact_bytes = 0;
+	DeviceArena arena;
+	sslm::LoraLayerDev* d_layers = nullptr;  // [layers]
+	uint32_t rank = 0;
+	std::atomic<uint32_t> live_refs{0};
+};
+
+struct sslm_seq_s {
+	sslm_model_s* model = nullptr;
+	sslm_kv_pool_s* pool = nullptr;
+	uint8_t* d_state = nullptr;     // two (hidden codes + carried scale) slots
+	size_t state_stride = 0, scale_off = 0;
+	int cur = 0;                    // slot holding the committed stream
+	std::vector<int32_t> pages;     // page ids in position order
+	int32_t* d_pages = nullptr;     // device page table, pages_per_block entries
+	int64_t context_length = 0;
+	uint32_t layer_index = 0;
+	int32_t current_token = -1;
+	bool ready_for_logits = false;
+	uint64_t kv_saturation_count = 0;
+	sslm_adapter_s* adapter = nullptr;
+	std::mutex lifecycle_mutex;
+
+	int8_t* hidden(int slot) const { return (int8_t*)(d_state + (size_t)slot * state_stride); }
+	sslm::Scale* scale(int slot) const { return (sslm::Scale*)(d_state + (size_t)slot * state_stride + scale_off); }
+};

@@ -1,0 +1,72 @@
+// Launch interface of the CUDA kernels (host side). Every launcher enqueues on the given
+// stream and returns immediately; errors surface through cudaGetLastError at the call
+// site. Nothing here allocates.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "sslm_types.cuh"
+
+namespace sslm {
+
+struct RowSource { const int8_t* hidden; const Scale* scale; };  // nullptr hidden: embed rows[r].token
+struct RowSink { int8_t* hidden; Scale* scale; };                // nullptr hidden: drop
+
+// ---- per-row sites (sslm_rows.cu)
+cudaError_t rows_configure(const Dims& d);
+void launch_begin(const RowBatch& b, const Dims& d, const int8_t* embed, Scale c_embed,
+                  const RowSource* src, const LayerDev* layer, cudaStream_t st);
+void launch_rmsnorm(const RowBatch& b, const Dims& d, const int8_t* gain, Scale site, cudaStream_t st);
+void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
+                     KvPoolDev pool, const int32_t* cos, const int32_t* sin, cudaStream_t st);
+void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st);
+void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st);
+void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev* next,
+                 cudaStream_t st);
+void launch_act(const RowBatch& b, const Dims& d, const LayerDev* layer, const int32_t* silu,
+                cudaStream_t st);
+void launch_scatter(const RowBatch& b, const Dims& d, const RowSink* sink, cudaStream_t st);
+
+// ---- int8 linear layers (sslm_gemv.cu, sslm_gemm_tc.cu)
+// out[m, n] = fold_n( sum_k x[m,k] * w[n,k] ) (+ LoRA delta), plus the per-row max |out|
+// of each column segment, reduced into rowmax[m][slot].
+struct LinearArgs {
+	const int8_t* x;      // [M, K] row-major activations
+	const int8_t* w;      // [N, K] row-major weights
+	const int32_t* fold;  // [N, 3] or nullptr (no fold: logits)
+	int M, N, K;
+	void* out;            // [M, out_ld] int32, or int64 when out64
+	int out_ld;
+	int out64;
+	unsigned long long* rowmax;  // [M][4] or nullptr
+	int nseg;             // column segments (fused projections)
+	int seg_end[3];       // exclusive end column of each segment
+	int seg_slot[3];      // rowmax slot per segment, -1: none
+	int seg_lora[3];      // LoraSlot per segment, -1: projection is never adapted
+	const RowDesc* rows;  // per-row adapter pointers (may be nullptr: no LoRA at all)
+	int layer;
+	const int8_t* lora_u; // [M][3][kMaxLoraRank]
+	// head mode: packed argmax keys instead of a stored row (out may be nullptr)
+	unsigned long long* best;
+	int32_t* logits;      // optional full dump [M, N]
+};
+// HBM-bound small-M path: vectorised weight streaming, dp4a, warp-shuffle reduction.
+void launch_linear_gemv(const LinearArgs& a, cudaStream_t st);
+// tensor-core path for M > 8 rows (tcgen05 kind::i8, TMA-fed). Returns false when the
+// shape is not supported by that kernel (caller then uses the GEMV path).
+bool launch_linear_tc(const LinearArgs& a, cudaStream_t st);
+
+// u = clamp127(amp_fold(A x)) for up to three projections sharing the input x
+// (AddAmplifyingLoraDelta's first half, src/forward/forward_sites.cpp:1062-1080)
+void launch_lora_u(const RowBatch& b, const int8_t* x, int k_in, int layer, int nproj,
+                   const int* lora_slots, cudaStream_t st);
+
+// ---- attention over the paged KV pool (sslm_attn.cu)
+cudaError_t attn_configure(const Dims& d);
+void launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
+                      KvPoolDev pool, int max_width, cudaStream_t st);
+// gather a sequence's pages into the reference's canonical block layout
+// [layer][K|V][kv_head][position][head_dim]; positions beyond `valid(layer)` are zero
+void launch_kv_export(const Dims& d, KvPoolDev pool, const int32_t* pages, int context_length,
+                      int layer_index, int8_t* out, cudaStream_t st);
+
+}  // namespace sslm

@@ -1,0 +1,464 @@
+// Per-row sites of the integer forward pass as fused CUDA kernels: one thread block
+// owns one row (one token of one sequence) and carries it through every step that
+// needs only that row -- the dynamic-scale requant "funnel", RMSNorm, q/k/v
+// post-processing (K/V landing, RoPE, page write, softmax constants), the residual
+// reconciliation and the SwiGLU activation. All of these are HBM/latency-bound integer
+// work; rows are independent, so the grid is simply the row count.
+#include <cuda_runtime.h>
+
+#include "sslm_kernels.h"
+
+namespace sslm {
+
+// ------------------------------------------------------------ block reductions
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+	for (int o = 16; o > 0; o >>= 1) {
+		unsigned long long t = __shfl_xor_sync(0xffffffffu, v, o);
+		v = t > v ? t : v;
+	}
+	return v;
+}
+__device__ __forceinline__ long long warp_sum_i64(long long v) {
+#pragma unroll
+	for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+	return v;
+}
+// red: shared scratch of at least 33 x 8 bytes. Every thread gets the result.
+__device__ unsigned long long block_max_u64(unsigned long long v, unsigned long long* red) {
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+	v = warp_max_u64(v);
+	__syncthreads();
+	if (lane == 0) red[warp] = v;
+	__syncthreads();
+	if (warp == 0) {
+		unsigned long long t = lane < nw ? red[lane] : 0ull;
+		t = warp_max_u64(t);
+		if (lane == 0) red[32] = t;
+	}
+	__syncthreads();
+	return red[32];
+}
+__device__ long long block_sum_i64(long long v, unsigned long long* red) {
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+	v = warp_sum_i64(v);
+	__syncthreads();
+	if (lane == 0) red[warp] = (unsigned long long)v;
+	__syncthreads();
+	if (warp == 0) {
+		long long t = lane < nw ? (long long)red[lane] : 0ll;
+		t = warp_sum_i64(t);
+		if (lane == 0) red[32] = (unsigned long long)t;
+	}
+	__syncthreads();
+	return (long long)red[32];
+}
+
+__device__ __forceinline__ unsigned long long abs_u64(int64_t v) {
+	return v < 0 ? (~(unsigned long long)v + 1ull) : (unsigned long long)v;
+}
+__device__ __forceinline__ int64_t load_wide(const RowBatch& b, int row, int col) {
+	const size_t i = (size_t)row * b.wide_ld + col;
+	return b.wide64 ? ((const int64_t*)b.wide)[i] : (int64_t)((const int32_t*)b.wide)[i];
+}
+// read a GEMM-reduced row maximum and leave the slot zero for its next producer
+__device__ __forceinline__ unsigned long long take_rowmax(const RowBatch& b, int row, int slot,
+                                                          unsigned long long* red) {
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		red[33] = b.rowmax[row * 4 + slot];
+		b.rowmax[row * 4 + slot] = 0ull;
+	}
+	__syncthreads();
+	return red[33];
+}
+
+// Funnel over a row staged in shared memory (RequantChainChecked,
+// src/forward/checked_chain_funnel.cpp:257-364). Codes go to out_g (global) and, when
+// non-null, out_s (shared). Every thread returns the same status; on failure nothing
+// is written.
+template <typename WT>
+__device__ int32_t block_funnel(const WT* w, int n, const Scale* incoming, int n_incoming, Scale site,
+                                int8_t* out_g, int8_t* out_s, Scale* out_scale,
+                                unsigned long long* red) {
+	unsigned long long mx = 0;
+	for (int i = threadIdx.x; i < n; i += blockDim.x) {
+		unsigned long long a = abs_u64((int64_t)w[i]);
+		mx = a > mx ? a : mx;
+	}
+	mx = block_max_u64(mx, red);
+	const FunnelParams fp = funnel_params(mx, incoming, n_incoming, site);
+	if (fp.status != kOk) return fp.status;
+	for (int i = threadIdx.x; i < n; i += blockDim.x) {
+		const int8_t c = requant_code((int64_t)w[i], fp.r, fp.s);
+		if (out_g) out_g[i] = c;
+		if (out_s) out_s[i] = c;
+	}
+	if (threadIdx.x == 0 && out_scale) *out_scale = fp.out;
+	return kOk;
+}
+
+// RmsNormSite (src/forward/forward_sites.cpp:410-459) on codes h[n] (global or shared):
+// root = max(isqrt(floor((sum h^2) << 32 / n)), 1); wide_i = floor((h_i << 32) / root) * g_i;
+// funnel with no incoming scale. wide: shared int64[n].
+__device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Scale site, int64_t* wide,
+                                 int8_t* out_g, Scale* out_scale, unsigned long long* red) {
+	long long ss = 0;
+	for (int i = threadIdx.x; i < n; i += blockDim.x) {
+		const int v = h[i];
+		ss += v * v;
+	}
+	ss = block_sum_i64(ss, red);
+	int64_t root = isqrt64(floor_div((int64_t)ss << 32, (int64_t)n));
+	if (root < 1) root = 1;
+	for (int i = threadIdx.x; i < n; i += blockDim.x) {
+		const int64_t num = (int64_t)h[i] * ((int64_t)1 << 32);
+		wide[i] = floor_div(num, root) * (int64_t)gain[i];
+	}
+	__syncthreads();
+	return block_funnel<int64_t>(wide, n, nullptr, 0, site, out_g, nullptr, out_scale, red);
+}
+
+__device__ __forceinline__ void set_status(const RowBatch& b, int row, int32_t st) {
+	if (threadIdx.x == 0 && st != kOk) atomicCAS(&b.status[row], 0, st);
+}
+
+// ------------------------------------------------------------------- kernels
+// Start of a call for each row: embed the token (EmbedEntry,
+// src/forward/forward_sites.cpp:763-787) or pick up the sequence's stored mid-token
+// stream, then the first layer's attention RMSNorm.
+__global__ void __launch_bounds__(kRowThreads)
+k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource* src,
+        const LayerDev* layer) {
+	extern __shared__ __align__(16) unsigned char smem[];
+	unsigned long long* red = (unsigned long long*)smem;
+	int64_t* wide = (int64_t*)(smem + 34 * 8);
+	const int r = blockIdx.x, n = d.hidden;
+	int8_t* x = b.x + (size_t)r * n;
+	if (threadIdx.x == 0) {
+		b.status[r] = 0;
+		b.sat[r] = 0ull;
+	}
+	int32_t st = kOk;
+	const RowSource s = src[r];
+	if (s.hidden != nullptr) {
+		for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = s.hidden[i];
+		if (threadIdx.x == 0) b.xs[r] = *s.scale;
+	} else {
+		const int8_t* e = embed + (size_t)b.rows[r].token * n;
+		for (int i = threadIdx.x; i < n; i += blockDim.x) wide[i] = e[i];
+		__syncthreads();
+		st = block_funnel<int64_t>(wide, n, nullptr, 0, c_embed, x, nullptr, &b.xs[r], red);
+	}
+	__syncthreads();
+	if (st == kOk && layer != nullptr) {
+		st = block_rmsnorm(x, layer->g_attn, n, layer->c_attn_norm, wide, b.nrm + (size_t)r * n,
+		                   &b.ns[r], red);
+	}
+	set_status(b, r, st);
+}
+
+// RMSNorm of the stream with the given gain (used for the final norm before the head).
+__global__ void __launch_bounds__(kRowThreads)
+k_rmsnorm(RowBatch b, Dims d, const int8_t* gain, Scale site) {
+	extern __shared__ __align__(16) unsigned char smem[];
+	unsigned long long* red = (unsigned long long*)smem;
+	int64_t* wide = (int64_t*)(smem + 34 * 8);
+	const int r = blockIdx.x, n = d.hidden;
+	if (b.status[r] != 0) return;
+	const int32_t st = block_rmsnorm(b.x + (size_t)r * n, gain, n, site, wide, b.nrm + (size_t)r * n,
+	                                 &b.ns[r], red);
+	set_status(b, r, st);
+}
+
+// After the fused q/k/v projection: q funnel (ProjectAndFunnel's tail,
+// forward_sites.cpp:1114-1146), K/V landing with the saturation counter (LandTokenKVRow
+// :1397-1415, LandingRescale :513-653), RoPE on q and on the landed K (:1748-1787,
+// RopeApplySite :663-761), the page write, and the per-kv-head softmax constants with
+// their domain gates (:1806-1856).
+__global__ void __launch_bounds__(kRowThreads)
+k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool,
+           const int32_t* rope_cos, const int32_t* rope_sin) {
+	extern __shared__ __align__(16) unsigned char smem[];
+	unsigned long long* red = (unsigned long long*)smem;      // 34 words
+	int32_t* st_kv = (int32_t*)(smem + 34 * 8);                // 16 ints
+	int8_t* sq = (int8_t*)(smem + 34 * 8 + 64);                // hidden
+	int8_t* sk = sq + d.hidden;                                // kv_hidden
+	const int r = blockIdx.x, H = d.hidden, hd = d.head_dim, half = hd / 2;
+	const unsigned long long mx = take_rowmax(b, r, 0, red);
+	if (b.status[r] != 0) return;
+	const LayerDev& lw = *layer;
+	const Scale ns = b.ns[r];
+	const int pos = b.rows[r].pos;
+
+	const FunnelParams fp = funnel_params(mx, &ns, 1, lw.c_q);
+	if (fp.status != kOk) {
+		set_status(b, r, fp.status);
+		return;
+	}
+	for (int i = threadIdx.x; i < H; i += blockDim.x) sq[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+
+	// K/V landing
+	const int page = b.rows[r].pages[pos / kPageTokens];
+	const int slot = pos % kPageTokens;
+	long long sat = 0;
+	for (int i = threadIdx.x; i < d.kv_hidden; i += blockDim.x) {
+		const int h = i / hd, dd = i - h * hd;
+		bool s1, s2;
+		const int64_t kraw = landing_rescale(load_wide(b, r, H + i), ns.m, lw.k_recip[3 * h + 2], ns.e,
+		                                     lw.k_recip[3 * h + 1], &s1, nullptr);
+		const int64_t vraw = landing_rescale(load_wide(b, r, H + d.kv_hidden + i), ns.m,
+		                                     lw.v_recip[3 * h + 2], ns.e, lw.v_recip[3 * h + 1], &s2, nullptr);
+		sat += (s1 ? 1 : 0) + (s2 ? 1 : 0);
+		sk[i] = (int8_t)clamp127(kraw);
+		int8_t* vdst = pool.base + kv_plane_offset(d, pool, layer_index, h, 1) +
+		               ((int64_t)page * kPageTokens + slot) * hd + dd;
+		*vdst = (int8_t)clamp127(vraw);
+	}
+	sat = block_sum_i64(sat, red);   // also orders the sq / sk writes before the reads below
+	if (threadIdx.x == 0) b.sat[r] += (unsigned long long)sat;
+
+	// RoPE: interleaved pairs (2i, 2i+1), table row = position
+	int8_t* qrot = b.qrot + (size_t)r * H;
+	for (int p = threadIdx.x; p < H / 2; p += blockDim.x) {
+		const int pi = p % half;
+		const int32_t c = rope_cos[(size_t)pos * half + pi], s = rope_sin[(size_t)pos * half + pi];
+		int8_t ox, oy;
+		rope_pair_clamped(sq[2 * p], sq[2 * p + 1], c, s, &ox, &oy);
+		qrot[2 * p] = ox;
+		qrot[2 * p + 1] = oy;
+	}
+	for (int p = threadIdx.x; p < d.kv_hidden / 2; p += blockDim.x) {
+		const int h = (2 * p) / hd, dd = 2 * p - h * hd, pi = dd / 2;
+		const int32_t c = rope_cos[(size_t)pos * half + pi], s = rope_sin[(size_t)pos * half + pi];
+		int8_t ox, oy;
+		rope_pair_clamped(sk[2 * p], sk[2 * p + 1], c, s, &ox, &oy);
+		int8_t* kdst = pool.base + kv_plane_offset(d, pool, layer_index, h, 0) +
+		               ((int64_t)page * kPageTokens + slot) * hd + dd;
+		kdst[0] = ox;
+		kdst[1] = oy;
+	}
+
+	// softmax constants per kv head: sm = Combine(S[q], softmax_khead) -> C30 constants -> width gate
+	if (threadIdx.x < d.kv_heads) {
+		const int h = threadIdx.x;
+		int32_t st = kOk;
+		const Scale kh = Scale{lw.sm_khead[2 * h], lw.sm_khead[2 * h + 1]};
+		SoftmaxConsts sc;
+		sc.c = IExpConsts{0, 0, 0};
+		sc.peak = 0;
+		if (!fits_i32(fp.out.m) || !fits_i32(kh.m)) {
+			st = kCarriedScaleMantissaOutOfDomain;
+		} else {
+			const Scale sm = combine(fp.out, kh);
+			if (!fits_i32(sm.m)) {
+				st = kCarriedScaleMantissaOutOfDomain;
+			} else if (iexp_scale_constants(sm.m, sm.e, &sc.c) != 0) {
+				st = kIExpScaleDerivationOutOfDomain;
+			} else if (!softmax_width_in_domain(sc.c.q_b, sc.c.q_c, (uint64_t)pos + 1, &sc.peak)) {
+				st = kSoftmaxRowWidthOutOfDomain;
+			} else if (sc.c.q_ln2 < 1 || sc.c.q_ln2 > sc.c.q_b) {
+				// q_ln2 == 0: every element's construction is refused by the reference
+				// (IExpConstruct's q_ln2 >= 1 check) -> SoftmaxKernelRefused
+				st = kSoftmaxKernelRefused;
+			}
+		}
+		st_kv[h] = st;
+		b.smc[(size_t)r * d.kv_heads + h] = sc;
+	}
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		if (b.xs != nullptr) { /* q scale is consumed only through smc */ }
+		for (int h = 0; h < d.kv_heads; ++h) {
+			if (st_kv[h] != kOk) {
+				atomicCAS(&b.status[r], 0, st_kv[h]);
+				break;
+			}
+		}
+	}
+}
+
+// Attention-context funnel (forward_sites.cpp:1898-1903): empty incoming, attn_ctx constant.
+__global__ void __launch_bounds__(kRowThreads)
+k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
+	extern __shared__ __align__(16) unsigned char smem[];
+	unsigned long long* red = (unsigned long long*)smem;
+	const int r = blockIdx.x, n = d.hidden;
+	const unsigned long long mx = take_rowmax(b, r, 3, red);
+	if (b.status[r] != 0) return;
+	const FunnelParams fp = funnel_params(mx, nullptr, 0, layer->c_ctx);
+	if (fp.status != kOk) {
+		set_status(b, r, fp.status);
+		return;
+	}
+	const int32_t* w = b.ctxw + (size_t)r * n;
+	int8_t* out = b.ctx + (size_t)r * n;
+	for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = requant_code((int64_t)w[i], fp.r, fp.s);
+	if (threadIdx.x == 0) b.cs[r] = fp.out;
+}
+
+// Residual reconciliation (ResidualReconcileSite, forward_sites.cpp:871-989) staged in
+// shared memory: wide_i = LandingRescale(branch_i, S[branch], Recip(S[stream].m), ...) + stream_i.
+__device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t* stream, Scale ss, int n,
+                                  Scale site, int64_t* wide, int8_t* out_g, int8_t* out_s,
+                                  Scale* out_scale, unsigned long long* red) {
+	if (!fits_i32(ss.m)) return kCarriedScaleMantissaOutOfDomain;
+	const int64_t r_h = dyn_recip(ss.m);
+	long long bad = 0;
+	for (int i = threadIdx.x; i < n; i += blockDim.x) {
+		bool ex;
+		const int64_t v = landing_rescale((int64_t)branch_s[i], bs.m, r_h, bs.e, ss.e, nullptr, &ex);
+		if (ex) {
+			bad = 1;
+			wide[i] = 0;
+		} else {
+			wide[i] = v + (int64_t)stream[i];
+		}
+	}
+	bad = block_sum_i64(bad, red);
+	if (bad != 0) return kResidualMagnitudeOutOfDomain;
+	return block_funnel<int64_t>(wide, n, &ss, 1, site, out_g, out_s, out_scale, red);
+}
+
+// o-projection funnel -> attention residual -> MLP RMSNorm (forward_sites.cpp:1906-1937)
+__global__ void __launch_bounds__(kRowThreads)
+k_res1(RowBatch b, Dims d, const LayerDev* layer) {
+	extern __shared__ __align__(16) unsigned char smem[];
+	unsigned long long* red = (unsigned long long*)smem;
+	int64_t* wide = (int64_t*)(smem + 34 * 8);
+	int8_t* so = (int8_t*)(wide + d.hidden);
+	int8_t* sa = so + d.hidden;
+	const int r = blockIdx.x, n = d.hidden;
+	const unsigned long long mx = take_rowmax(b, r, 0, red);
+	if (b.status[r] != 0) return;
+	const LayerDev& lw = *layer;
+	const Scale cs = b.cs[r];
+	const FunnelParams fp = funnel_params(mx, &cs, 1, lw.c_o);
+	int32_t st = fp.status;
+	if (st == kOk) {
+		for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+		__syncthreads();
+		st = block_residual(so, fp.out, b.x + (size_t)r * n, b.xs[r], n, lw.c_attn_res, wide,
+		                    b.a + (size_t)r * n, sa, &b.as[r], red);
+	}
+	if (st == kOk) {
+		__syncthreads();
+		st = block_rmsnorm(sa, lw.g_mlp, n, lw.c_mlp_norm, wide, b.nrm + (size_t)r * n, &b.ns[r], red);
+	}
+	set_status(b, r, st);
+}
+
+// down-projection funnel -> MLP residual -> (next layer's attention RMSNorm)
+// (forward_sites.cpp:1968-1987, :1694-1698)
+__global__ void __launch_bounds__(kRowThreads)
+k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
+	extern __shared__ __align__(16) unsigned char smem[];
+	unsigned long long* red = (unsigned long long*)smem;
+	int64_t* wide = (int64_t*)(smem + 34 * 8);
+	int8_t* sd = (int8_t*)(wide + d.hidden);
+	int8_t* sx = sd + d.hidden;
+	const int r = blockIdx.x, n = d.hidden;
+	const unsigned long long mx = take_rowmax(b, r, 0, red);
+	if (b.status[r] != 0) return;
+	const LayerDev& lw = *layer;
+	const Scale as = b.acts[r];
+	const FunnelParams fp = funnel_params(mx, &as, 1, lw.c_down);
+	int32_t st = fp.status;
+	if (st == kOk) {
+		for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+		__syncthreads();
+		st = block_residual(sd, fp.out, b.a + (size_t)r * n, b.as[r], n, lw.c_mlp_res, wide,
+		                    b.x + (size_t)r * n, sx, &b.xs[r], red);
+	}
+	if (st == kOk && next_layer != nullptr) {
+		__syncthreads();
+		st = block_rmsnorm(sx, next_layer->g_attn, n, next_layer->c_attn_norm, wide,
+		                   b.nrm + (size_t)r * n, &b.ns[r], red);
+	}
+	set_status(b, r, st);
+}
+
+// gate / up funnels -> SwiGLU activation site (MlpActSite, forward_sites.cpp:796-864)
+__global__ void __launch_bounds__(1024)
+k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
+	extern __shared__ __align__(16) unsigned char smem[];
+	unsigned long long* red = (unsigned long long*)smem;
+	int32_t* tab = (int32_t*)(smem + 34 * 8);          // 1025 entries, padded to 1028
+	int32_t* wide = tab + 1028;                         // inter
+	const int r = blockIdx.x, n = d.inter;
+	for (int i = threadIdx.x; i < 1025; i += blockDim.x) tab[i] = silu_table[i];
+	const unsigned long long mxg = take_rowmax(b, r, 1, red);
+	const unsigned long long mxu = take_rowmax(b, r, 2, red);
+	if (b.status[r] != 0) return;
+	const LayerDev& lw = *layer;
+	const Scale ns = b.ns[r];
+	const FunnelParams fg = funnel_params(mxg, &ns, 1, lw.c_gate);
+	const FunnelParams fu = funnel_params(mxu, &ns, 1, lw.c_up);
+	int32_t st = fg.status != kOk ? fg.status : fu.status;
+	if (st == kOk && !silu_scale_in_domain(fg.out)) st = kSiluScaleOutOfDomain;
+	if (st != kOk) {
+		set_status(b, r, st);
+		return;
+	}
+	const int ge = (int)fg.out.e;
+	for (int i = threadIdx.x; i < n; i += blockDim.x) {
+		const int g = requant_code(load_wide(b, r, i), fg.r, fg.s);
+		const int u = requant_code(load_wide(b, r, n + i), fu.r, fu.s);
+		const int32_t sig = silu_sigmoid_q15(tab, g, fg.out.m, ge);
+		wide[i] = g * sig * u;   // |.| <= 127 * 2^15 * 127 < 2^29
+	}
+	__syncthreads();
+	const Scale inc[2] = {fg.out, fu.out};
+	st = block_funnel<int32_t>(wide, n, inc, 2, lw.c_act, b.act + (size_t)r * n, nullptr, &b.acts[r], red);
+	set_status(b, r, st);
+}
+
+// End of a call: hand each row's stream back to its sequence (or nowhere).
+__global__ void __launch_bounds__(kRowThreads)
+k_scatter(RowBatch b, Dims d, const RowSink* sink) {
+	const int r = blockIdx.x, n = d.hidden;
+	const RowSink s = sink[r];
+	if (s.hidden == nullptr || b.status[r] != 0) return;
+	const int8_t* x = b.x + (size_t)r * n;
+	for (int i = threadIdx.x; i < n; i += blockDim.x) s.hidden[i] = x[i];
+	if (threadIdx.x == 0) *s.scale = b.xs[r];
+}
+
+// ------------------------------------------------------------------ launchers
+static size_t smem_wide(const Dims& d) { return 34 * 8 + (size_t)d.hidden * 8; }
+
+void launch_begin(const RowBatch& b, const Dims& d, const int8_t* embed, Scale c_embed,
+                  const RowSource* src, const LayerDev* layer, cudaStream_t st) {
+	k_begin<<<b.m, kRowThreads, smem_wide(d), st>>>(b, d, embed, c_embed, src, layer);
+}
+void launch_rmsnorm(const RowBatch& b, const Dims& d, const int8_t* gain, Scale site, cudaStream_t st) {
+	k_rmsnorm<<<b.m, kRowThreads, smem_wide(d), st>>>(b, d, gain, site);
+}
+void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
+                     KvPoolDev pool, const int32_t* cos, const int32_t* sin, cudaStream_t st) {
+	const size_t sm = 34 * 8 + 64 + d.hidden + d.kv_hidden;
+	k_qkv_post<<<b.m, kRowThreads, sm, st>>>(b, d, layer, layer_index, pool, cos, sin);
+}
+void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
+	k_ctx_funnel<<<b.m, kRowThreads, 34 * 8, st>>>(b, d, layer);
+}
+void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
+	k_res1<<<b.m, kRowThreads, smem_wide(d) + 2 * d.hidden, st>>>(b, d, layer);
+}
+void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev* next,
+                 cudaStream_t st) {
+	k_res2<<<b.m, kRowThreads, smem_wide(d) + 2 * d.hidden, st>>>(b, d, layer, next);
+}
+size_t act_smem_bytes(const Dims& d) { return 34 * 8 + 1028 * 4 + (size_t)d.inter * 4; }
+cudaError_t rows_configure(const Dims& d) {
+	return cudaFuncSetAttribute(k_act, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)act_smem_bytes(d));
+}
+void launch_act(const RowBatch& b, const Dims& d, const LayerDev* layer, const int32_t* silu,
+                cudaStream_t st) {
+	k_act<<<b.m, 1024, act_smem_bytes(d), st>>>(b, d, layer, silu);
+}
+void launch_scatter(const RowBatch& b, const Dims& d, const RowSink* sink, cudaStream_t st) {
+	k_scatter<<<b.m, kRowThreads, 0, st>>>(b, d, sink);
+}
+
+}  // namespace sslm
