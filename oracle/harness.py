@@ -97,6 +97,7 @@ def port():
             "osc_landing_rescale": (i64, [i64, i64, i64, i64, i64, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
             "osc_silu_sigmoid_q15": (i32, [p, C.c_int8, i64, C.c_int]),
             "osc_iexp_scale_constants": (C.c_int, [i64, i64, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64)]),
+            "osc_iexp": (C.c_int, [i64, i64, i64, i64, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64)]),
             "osc_softmax_width_domain": (C.c_int, [i64, i64, C.c_size_t]),
             "osc_softmax_row_q15": (C.c_int, [p, C.c_size_t, i64, i64, i64, p]),
             "osc_gemm": (None, [p, p, C.c_size_t, C.c_size_t, C.c_size_t, p]),

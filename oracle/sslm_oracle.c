@@ -268,6 +268,27 @@ static int iexp_element(int64_t q, int64_t q_ln2, int64_t q_b, int64_t q_c, int6
 	return 1;
 }
 
+/* 0 kOk, 1 kBadQ, 2 kBadQLn2, 3 kBadQB, 4 kNotRepresentable (IExpDomain,
+ * include/superslm/intmath.h:349); *value = IExpEvaluate of the construction */
+int osc_iexp(int64_t q, int64_t q_ln2, int64_t q_b, int64_t q_c, int64_t* z_out, int64_t* base_out,
+             int64_t* value) {
+	*value = 0;
+	if (q > 0) return 1;
+	if (q_ln2 < 1 || q_ln2 > INT64_MAX / 30) return 2;
+	int64_t clip_lo = -(int64_t)30 * q_ln2;
+	int64_t clipped = q < clip_lo ? clip_lo : q;
+	int64_t z = (-clipped) / q_ln2;
+	int64_t q_p = clipped + z * q_ln2;
+	if (q_b < INT64_MIN - q_p) return 3;
+	int64_t base = q_p + q_b;
+	if (z_out) *z_out = z;
+	if (base_out) *base_out = base;
+	s128 v = (s128)base * base + q_c;
+	*value = (int64_t)(v >> (int)z);
+	s128 limit = (s128)1 << (63 + (int)z);
+	return (v <= limit - 1 && v >= -limit) ? 0 : 4;
+}
+
 int osc_softmax_row_q15(const int64_t* scores, size_t width, int64_t q_ln2, int64_t q_b,
                         int64_t q_c, int64_t* out_probs) {
 	if (width == 0) return 1;

@@ -65,6 +65,9 @@ int64_t osc_landing_rescale(int64_t code, int64_t m_a, int64_t r_t, int64_t e_a,
 int32_t osc_silu_sigmoid_q15(const int32_t* table, int8_t code, int64_t m, int e); /* src/silu_lut.cpp:16-67 */
 /* returns 0 ok, 1 bad coefficient, 2 negative shift, 3 not representable (src/intmath.cpp:702-778) */
 int osc_iexp_scale_constants(int64_t m, int64_t e, int64_t* q_ln2, int64_t* q_b, int64_t* q_c);
+/* IExpConstruct + IExpEvaluate (src/intmath.cpp:540-668) */
+int osc_iexp(int64_t q, int64_t q_ln2, int64_t q_b, int64_t q_c, int64_t* z_out, int64_t* base_out,
+             int64_t* value);
 int osc_softmax_width_domain(int64_t q_b, int64_t q_c, size_t width); /* checked_chain_funnel.cpp:520-583 */
 int osc_softmax_row_q15(const int64_t* scores, size_t width, int64_t q_ln2, int64_t q_b,
                         int64_t q_c, int64_t* out_probs);   /* src/intmath.cpp:796-901 */

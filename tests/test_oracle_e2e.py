@@ -1,0 +1,143 @@
+"""End-to-end pins of the CPU oracle: the plain-C restatement must reproduce the records
+that the reference library produced through its own sslm_* ABI (tests/golden/e2e_golden.json),
+and, where the compiled reference is present, match it on fresh seeded runs and on seeded
+sweeps of every primitive and site."""
+import ctypes as C
+import hashlib
+import json
+import random
+
+import numpy as np
+import pytest
+
+from oracle import harness as H
+from oracle.harness import Scale
+from superslm_b200 import abi, artifact as A
+
+I64 = C.c_int64
+
+
+def port_record(case):
+    """Drive the restatement the way make_e2e_golden.py drives the reference."""
+    sh = A.SHAPES[case["shape"]]
+    art = A.build_synthetic_model(case["shape"], case["seed"], case["context_cap"], case["shift_lo"], case["shift_hi"])
+    prompt = A.stream_uniform(case["seed"] ^ 0xABCDEF, "prompt", case["prompt_len"], 0, sh.vocab - 1)
+    pm = H.PortModel(art)
+    s = H.PortSeq(pm)
+    la = lb = None
+    if case["adapters"]:
+        la = pm.lora(A.build_synthetic_adapter(art, case["adapters"][0]))
+        lb = pm.lora(A.build_synthetic_adapter(art, case["adapters"][1]))
+        s.lora = la
+    assert s.prefill(prompt) == 0
+    n = case["decode"]
+    toks = s.decode(n // 2, sh.layers)
+    if lb is not None:
+        s.lora = lb
+    toks += s.decode(n - n // 2, 1)   # a different layer budget: slicing must not matter
+    return {"tokens": toks, "context_length": s.s.context_length,
+            "hidden_scale": [s.s.hidden_scale.m, s.s.hidden_scale.e],
+            "kv_saturation_count": s.s.kv_saturation_count,
+            "kv_sha256": hashlib.sha256(s.kv.tobytes()).hexdigest()}
+
+
+@pytest.mark.parametrize("name", ["tiny", "small", "small_dense", "tiny_lora"])
+def test_port_reproduces_reference_records(e2e_golden, name):
+    case = e2e_golden[name]
+    got = port_record(case)
+    for k, v in got.items():
+        assert v == case[k], (name, k)
+
+
+def test_golden_records_are_not_degenerate(e2e_golden):
+    for name, c in e2e_golden.items():
+        assert len(set(c["tokens"])) > 1, name
+        assert c["kv_nonzero"] > 1000, name
+    # attaching an adapter changes the result
+    assert e2e_golden["tiny_lora"]["tokens"] != e2e_golden["tiny"]["tokens"]
+
+
+def test_reference_still_matches_its_records(e2e_golden, ref_lib):
+    import make_e2e_golden as G
+    for c in G.CASES:
+        assert json.loads(json.dumps(G.run_case(ref_lib, *c))) == e2e_golden[c[0]]
+
+
+def test_artifact_writer_round_trip():
+    art = A.build_synthetic_model("tiny", 5, 32)
+    v = A.parse_artifact(art)
+    assert v.config["hidden_size"] == 128 and v.config["context_cap"] == 32
+    w = v.tensors(A.SEC_WEIGHTS, np.int8)
+    assert w["layer1.down_proj"].shape == (128, 256)
+    assert int(np.abs(w["embed"]).max()) <= 127
+    assert hashlib.sha256(art[:32] + bytes(32) + art[64:]).digest() == art[32:64]
+    assert A.build_synthetic_model("tiny", 5, 32) == art      # deterministic
+    assert A.build_synthetic_model("tiny", 6, 32) != art
+
+
+def test_primitive_sweeps_against_reference(port, ref_shim):
+    rnd = random.Random(20260)
+    ri = lambda bits: rnd.randrange(-(1 << bits), 1 << bits)
+    for _ in range(20000):
+        x = rnd.choice([rnd.randrange(1 << 30, 1 << 31), ri(31), ri(45), rnd.randrange(1, 4096)])
+        assert port.osc_dyn_recip(x) == ref_shim.refshim_dyn_recip(x)
+        a, b = ri(31), ri(31)
+        assert port.osc_srdhm(a, b) == ref_shim.refshim_srdhm(a, b)
+        e = rnd.randrange(-31, 32)
+        assert port.osc_amp_fold(a, 0, b, e) == ref_shim.refshim_amp_fold(a, 0, b, e)
+        code, m = rnd.choice([ri(7), ri(33)]), rnd.choice([rnd.randrange(1 << 30, 1 << 31), ri(31)])
+        rt, ea, et = rnd.randrange((1 << 31) + 1, (1 << 32) + 1), rnd.randrange(-90, 45), rnd.randrange(-60, 20)
+        s1, s2, x1, x2 = C.c_uint64(0), C.c_uint64(0), C.c_int(), C.c_int()
+        assert port.osc_landing_rescale(code, m, rt, ea, et, C.byref(s1), C.byref(x1)) == \
+            ref_shim.refshim_landing_rescale(code, m, rt, ea, et, C.byref(s2), C.byref(x2))
+        assert (s1.value, x1.value) == (s2.value, x2.value)
+        cm, ce = rnd.randrange(1 << 30, 1 << 31), rnd.randrange(-60, -25)
+        A3, B3 = [I64() for _ in range(3)], [I64() for _ in range(3)]
+        sa = port.osc_iexp_scale_constants(cm, ce, *[C.byref(v) for v in A3])
+        sb = ref_shim.refshim_iexp_scale_constants(cm, ce, *[C.byref(v) for v in B3])
+        assert sa == sb and (sa != 0 or [v.value for v in A3] == [v.value for v in B3])
+
+
+def test_site_sweeps_against_reference(port, ref_shim):
+    rng = np.random.default_rng(7)
+    tab = C.cast(ref_shim.refshim_silu_canonical_table(), C.c_void_p)
+    mine = A.sigmoid_lut_table()
+    assert (np.ctypeslib.as_array(ref_shim.refshim_silu_canonical_table(), (1025,)) == mine).all()
+    for n in (1, 17, 128, 1536):
+        for _ in range(6):
+            h = rng.integers(-127, 128, n).astype(np.int8)
+            g = rng.integers(-127, 128, n).astype(np.int8)
+            g32 = g.astype(np.int32)
+            o1, o2 = np.zeros(n, np.int8), np.zeros(n, np.int8)
+            s1, m2, e2 = Scale(), I64(), I64()
+            cm, ce = int(rng.integers(1 << 30, 1 << 31)), int(rng.integers(-62, -40))
+            assert port.osc_rmsnorm_site(h.ctypes.data, g.ctypes.data, n, Scale(cm, ce), o1.ctypes.data, C.byref(s1)) == \
+                ref_shim.refshim_rmsnorm_site(h.ctypes.data, g32.ctypes.data, n, cm, ce, o2.ctypes.data, C.byref(m2), C.byref(e2))
+            assert (o1 == o2).all() and (s1.m, s1.e) == (m2.value, e2.value)
+            gm, ge = int(rng.integers(1 << 30, 1 << 31)), int(rng.integers(-45, -30))
+            um, ue = int(rng.integers(1 << 30, 1 << 31)), int(rng.integers(-45, -30))
+            st1 = port.osc_mlp_act_site(h.ctypes.data, Scale(gm, ge), g.ctypes.data, Scale(um, ue), n, tab,
+                                        Scale(cm, ce), o1.ctypes.data, C.byref(s1))
+            st2 = ref_shim.refshim_mlp_act_site(h.ctypes.data, gm, ge, g.ctypes.data, um, ue, n, tab, cm, ce,
+                                                o2.ctypes.data, C.byref(m2), C.byref(e2))
+            assert st1 == st2 == 0 and (o1 == o2).all() and (s1.m, s1.e) == (m2.value, e2.value)
+            be = ge + int(rng.integers(-6, 7))
+            st1 = port.osc_residual_site(h.ctypes.data, Scale(gm, be), g.ctypes.data, Scale(um, ge), n, Scale(cm, ce),
+                                         o1.ctypes.data, C.byref(s1))
+            st2 = ref_shim.refshim_residual_site(h.ctypes.data, gm, be, g.ctypes.data, um, ge, n, cm, ce,
+                                                 o2.ctypes.data, C.byref(m2), C.byref(e2))
+            assert st1 == st2 and (st1 != 0 or ((o1 == o2).all() and (s1.m, s1.e) == (m2.value, e2.value)))
+    # softmax rows
+    for _ in range(300):
+        m, e = int(rng.integers(1 << 30, 1 << 31)), int(rng.integers(-53, -30))
+        k = [I64() for _ in range(3)]
+        if ref_shim.refshim_iexp_scale_constants(m, e, *[C.byref(v) for v in k]) != 0:
+            continue
+        ln2, qb, qc = [v.value for v in k]
+        w = int(rng.integers(1, 400))
+        assert port.osc_softmax_width_domain(qb, qc, w) == ref_shim.refshim_softmax_width_domain(qb, qc, w)
+        sc = rng.integers(-(1 << 21), 1 << 21, w).astype(np.int64) // int(rng.choice([1, 100, 10000]))
+        p1, p2 = np.zeros(w, np.int64), np.zeros(w, np.int64)
+        assert port.osc_softmax_row_q15(sc.ctypes.data, w, ln2, qb, qc, p1.ctypes.data) == \
+            ref_shim.refshim_softmax_row_q15(sc.ctypes.data, w, ln2, qb, qc, p2.ctypes.data)
+        assert (p1 == p2).all()
