@@ -51,6 +51,19 @@ struct sslm_workspace_s {
 	cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 	float last_ms = 0.f;
 	uint64_t launches = 0;
+	// optional per-kernel-class timing (sslm_b200_profile): an event before every launch
+	bool profile = false;
+	std::vector<cudaEvent_t> prof_events;
+	std::vector<int> prof_class;
+	size_t prof_used = 0;
+	double prof_ms[16] = {0};
+	uint64_t prof_n[16] = {0};
+};
+
+// kernel classes reported by sslm_b200_profile_read
+enum ProfClass {
+	kProfBegin = 0, kProfLinQkv, kProfQkvPost, kProfAttention, kProfCtxFunnel, kProfLinO, kProfRes1,
+	kProfLinGateUp, kProfAct, kProfLinDown, kProfRes2, kProfHead, kProfLoraU, kProfOther, kProfClasses
 };
 
 struct sslm_model_s {

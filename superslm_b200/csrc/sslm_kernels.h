@@ -48,6 +48,7 @@ struct LinearArgs {
 	// head mode: packed argmax keys instead of a stored row (out may be nullptr)
 	unsigned long long* best;
 	int32_t* logits;      // optional full dump [M, N]
+	int32_t* status;      // [M] row statuses (a bounded device wait that ran out is reported here), or nullptr
 };
 // HBM-bound small-M path: vectorised weight streaming, dp4a, warp-shuffle reduction.
 void launch_linear_gemv(const LinearArgs& a, cudaStream_t st);
