@@ -179,6 +179,14 @@ SSLM_API sslm_status sslm_b200_linear_bench(int32_t M, int32_t N, int32_t K, int
  * sslm_decode_step that ran on `ws`, and the number of kernels launched on it so far. */
 SSLM_API sslm_status sslm_b200_last_call_ms(sslm_workspace ws, float* ms, uint64_t* kernel_launches);
 
+/* Per-kernel-class device timing of later calls on `ws` (CUDA events around every launch;
+ * slows the call slightly). Classes, in order: begin, linear q/k/v, q/k/v post, attention,
+ * context funnel, linear o, residual 1, linear gate/up, activation, linear down, residual 2,
+ * head, LoRA u, other. profile_read returns accumulated milliseconds and launch counts of the
+ * first n classes since profiling was enabled. */
+SSLM_API sslm_status sslm_b200_profile(sslm_workspace ws, int32_t enable);
+SSLM_API sslm_status sslm_b200_profile_read(sslm_workspace ws, double* ms, uint64_t* launches, int32_t n);
+
 /* Tests only: capture the full int32 logit row of every token produced by later
  * sslm_decode_step calls on `ws` into host memory ([tokens in call order][vocab]);
  * pass NULL to stop. */

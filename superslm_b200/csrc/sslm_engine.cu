@@ -410,6 +410,7 @@ static void destroy_workspace(sslm_workspace_s* w) {
 	cudaFreeHost(w->h_best);
 	if (w->ev0) cudaEventDestroy(w->ev0);
 	if (w->ev1) cudaEventDestroy(w->ev1);
+	for (cudaEvent_t e : w->prof_events) cudaEventDestroy(e);
 	if (w->stream) cudaStreamDestroy(w->stream);
 	delete w;
 }
@@ -455,6 +456,20 @@ extern "C" sslm_status sslm_b200_last_call_ms(sslm_workspace ws, float* ms, uint
 	if (!ws) return SSLM_INVALID_ARGUMENT;
 	if (ms) *ms = ws->last_ms;
 	if (launches) *launches = ws->launches;
+	return SSLM_OK;
+}
+
+extern "C" sslm_status sslm_b200_profile(sslm_workspace ws, int32_t enable) {
+	if (!ws) return SSLM_INVALID_ARGUMENT;
+	ws->profile = enable != 0;
+	ws->prof_used = 0;
+	for (int i = 0; i < 16; ++i) { ws->prof_ms[i] = 0; ws->prof_n[i] = 0; }
+	return SSLM_OK;
+}
+
+extern "C" sslm_status sslm_b200_profile_read(sslm_workspace ws, double* ms, uint64_t* launches, int32_t n) {
+	if (!ws || !ms || !launches || n < 0) return SSLM_INVALID_ARGUMENT;
+	for (int i = 0; i < n && i < kProfClasses; ++i) { ms[i] = ws->prof_ms[i]; launches[i] = ws->prof_n[i]; }
 	return SSLM_OK;
 }
 

@@ -176,6 +176,7 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 		const bool row_ok = acc_ok && row < a.M && s_timeout == 0;
 		const LoraLayerDev* lora = (row_ok && a.rows != nullptr && a.rows[row].lora != nullptr) ? a.rows[row].lora + a.layer : nullptr;
 		unsigned long long lmax[3] = {0ull, 0ull, 0ull};
+		unsigned long long lbest = 0ull;
 		for (int c0 = 0; c0 < BN; c0 += 32) {
 			uint32_t r[32];
 			tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);   // warp-collective: never skipped
@@ -205,6 +206,13 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 							v += (int64_t)amp_fold(dsum, p.df[3 * nl], p.df[3 * nl + 1], p.df[3 * nl + 2]);
 						}
 					}
+					if (a.best != nullptr) {   // head: greedy argmax key, lowest index wins ties
+						const unsigned long long key =
+						    ((unsigned long long)((uint32_t)v32 ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)n);
+						lbest = key > lbest ? key : lbest;
+						if (a.logits) a.logits[(size_t)row * a.N + n] = v32;
+						continue;
+					}
 					v4[jj] = v;
 					const unsigned long long ab = v < 0 ? (~(unsigned long long)v + 1ull) : (unsigned long long)v;
 					if (seg == 0) lmax[0] = ab > lmax[0] ? ab : lmax[0];
@@ -212,7 +220,7 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 					else lmax[2] = ab > lmax[2] ? ab : lmax[2];
 				}
 				const int nb = n0 + c0 + j4;
-				if (nb >= a.N) continue;
+				if (nb >= a.N || a.best != nullptr) continue;
 				if (vec_ok && nb + 3 < a.N) {
 					*(int4*)((int32_t*)a.out + (size_t)row * a.out_ld + nb) =
 					    make_int4((int)v4[0], (int)v4[1], (int)v4[2], (int)v4[3]);
@@ -226,6 +234,7 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 				}
 			}
 		}
+		if (row_ok && a.best != nullptr && lbest != 0ull) atomicMax(&a.best[row], lbest);
 		if (row_ok && a.rowmax != nullptr) {
 			for (int s = 0; s < a.nseg; ++s)
 				if (a.seg_slot[s] >= 0 && lmax[s] != 0ull) atomicMax(&a.rowmax[(size_t)row * 4 + a.seg_slot[s]], lmax[s]);
@@ -298,7 +307,7 @@ bool tensor_map(const void* ptr, int rows, int k, CUtensorMap* out) {
 }  // namespace
 
 bool launch_linear_tc(const LinearArgs& a, cudaStream_t st) {
-	if (a.best != nullptr || a.K % 16 != 0 || ((uintptr_t)a.x & 15) || ((uintptr_t)a.w & 15)) return false;
+	if (a.K % 16 != 0 || ((uintptr_t)a.x & 15) || ((uintptr_t)a.w & 15)) return false;
 	static bool configured = false;
 	if (!configured) {
 		if (cudaFuncSetAttribute(k_linear_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
