@@ -133,6 +133,7 @@ def bind_extras(lib):
     d.sslm_b200_profile_read.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.c_int32]
     d.sslm_b200_model_device_bytes.argtypes = [C.c_void_p]
     d.sslm_b200_model_device_bytes.restype = C.c_size_t
+    d.sslm_b200_tc_stats.argtypes = [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_int32)]
     return d
 
 
@@ -299,7 +300,7 @@ def run_ours(args):
     prompts_all = workload_prompts(args.shape, args.seqs, args.prompt_lo, args.prompt_hi, stream)
     prompts = [prompts_all[i] for i in ids]
     n = len(prompts)
-    eng = abi.Engine(lib, art, blocks=max(n, 1), max_batch=max(n, 1), max_chunk=args.chunk)
+    eng = abi.Engine(lib, art, blocks=n + 1, max_batch=max(n, 1), max_chunk=args.chunk)
     seqs = [eng.new_seq() for _ in range(n)]
 
     # ---- prefill (timed: wall clock through the ABI and device events)
@@ -347,7 +348,7 @@ def run_ours(args):
     produced_all = rsum(produced)
 
     # ---- per-kernel-class timing of a few more steps (rank 0), for the roofline object
-    roof, classes = None, {}
+    roof, classes, prefill_classes = None, {}, {}
     if rank == 0:
         d.sslm_b200_profile(eng.ws, 1)
         psteps = 4
@@ -371,6 +372,21 @@ def run_ours(args):
             if ab:
                 classes[name]["GBps"] = round(ab / (avg_us * 1e-6) / 1e9, 1)
                 classes[name]["frac_hbm"] = round(ab / (avg_us * 1e-6) / 1e9 / peak, 4)
+        # one more profiled pass: a 1024-token chunk-batched prefill of a fresh sequence
+        extra = eng.new_seq()
+        pp = A.stream_uniform(SEED ^ 0x77, "prefill_profile", min(1024, args.prompt_hi), 0, sh.vocab - 1).astype(np.int32)
+        d.sslm_b200_profile(eng.ws, 1)
+        extra.prefill(pp, args.chunk)
+        d.sslm_b200_profile_read(eng.ws, ms, cnt, 14)
+        d.sslm_b200_profile(eng.ws, 0)
+        ptotal = sum(ms[i] for i in range(14)) or 1.0
+        prefill_classes = {name: {"ms": round(ms[i], 3), "share": round(ms[i] / ptotal, 4)}
+                           for i, name in enumerate(PROF_CLASSES) if cnt[i]}
+        prefill_classes["_tokens"] = int(pp.size)
+        prefill_classes["_linear_TOPS"] = round(
+            2.0 * pp.size * sh.layers * (2 * sh.hidden ** 2 + 2 * sh.hidden * sh.kv_hidden + 3 * sh.hidden * sh.inter)
+            / (1e9 * (sum(ms[i] for i in (1, 5, 7, 9)) or 1.0)), 1)
+        extra.release()
         top = max((c for c in classes if "GBps" in classes[c]), key=lambda c: classes[c]["share"])
         roof = {"kernel": top, "bound": "hbm", "achieved": classes[top]["GBps"], "peak": peak, "unit": "GB/s",
                 "frac": classes[top]["frac_hbm"], "peak_source": "of " + peak_kind, "traffic": None,
@@ -391,6 +407,9 @@ def run_ours(args):
         cpu = {"value": round(r["decode_tok_s"], 3), "unit": "tok/s", "cores": r["cores"], "kind": r["kind"],
                "sample": r["sample"], "prefill_tok_s": round(r["prefill_tok_s"], 2)}
     model_bytes = d.sslm_b200_model_device_bytes(eng.model)
+    tcn, tcr, tcw = C.c_uint64(0), C.c_uint64(0), C.c_int32(0)
+    d.sslm_b200_tc_stats(C.byref(tcn), C.byref(tcr), C.byref(tcw))
+    tc_info = {"launches": tcn.value, "declined": tcr.value, "last_decline_reason": tcw.value}
     eng.close()
     if rank != 0:
         return
@@ -411,7 +430,7 @@ def run_ours(args):
         "gpu_launches": int(launches2 - launches1),
         "prefill": {"value": round(ptoks_all / prefill_dev, 1), "e2e": round(ptoks_all / prefill_wall, 1),
                     "unit": "tok/s", "tokens": int(ptoks_all), "gpu_launches": int(launches1 - launches0)},
-        "roofline": roof, "kernels": classes, "cpu_baseline": cpu, "parity": parity,
+        "tensor_core_kernel": tc_info, "roofline": roof, "kernels": classes, "kernels_prefill_1024": prefill_classes, "cpu_baseline": cpu, "parity": parity,
     }
     print(json.dumps(out))
 

@@ -179,6 +179,10 @@ SSLM_API sslm_status sslm_b200_linear_bench(int32_t M, int32_t N, int32_t K, int
  * sslm_decode_step that ran on `ws`, and the number of kernels launched on it so far. */
 SSLM_API sslm_status sslm_b200_last_call_ms(sslm_workspace ws, float* ms, uint64_t* kernel_launches);
 
+/* Process-wide counters of the tensor-core linear kernel: launches, times it declined a shape
+ * (the streaming kernel ran instead) and the reason code of the last refusal. */
+SSLM_API sslm_status sslm_b200_tc_stats(uint64_t* launches, uint64_t* refusals, int32_t* last_reason);
+
 /* Per-kernel-class device timing of later calls on `ws` (CUDA events around every launch;
  * slows the call slightly). Classes, in order: begin, linear q/k/v, q/k/v post, attention,
  * context funnel, linear o, residual 1, linear gate/up, activation, linear down, residual 2,

@@ -121,30 +121,42 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	}
 	__syncthreads();
 
-	// pass 4: ctx = P V. A warp step covers rows_per_step positions; each lane owns 4
-	// consecutive head-dim elements of one of them.
-	const int lanes_per_row = hd / 4, rows_per_step = 32 / lanes_per_row;
+	// pass 4: ctx = P V. A warp step covers rows_per_step positions; each lane owns 8
+	// consecutive head-dim elements of one of them. Four steps are issued back to back so
+	// that every lane keeps four independent 8-byte V loads in flight.
+	const int lanes_per_row = hd / 8, rows_per_step = 32 / lanes_per_row;
 	const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
 	const int sub = lane / lanes_per_row, dq = lane % lanes_per_row;
-	int cacc[8][4];
+	constexpr int kUnroll = 4;
+	int cacc[8][8];
 #pragma unroll
 	for (int g = 0; g < 8; ++g)
 #pragma unroll
-		for (int j = 0; j < 4; ++j) cacc[g][j] = 0;
-	for (int k0 = warp * rows_per_step; k0 < width; k0 += nw * rows_per_step) {
-		const int k = k0 + sub;
-		if (k < width) {
-			const int vv = __ldg((const int*)kv_row_ptr(vplane, pages, k, hd) + dq);
-			const int v0 = (int8_t)(vv & 0xff), v1 = (int8_t)((vv >> 8) & 0xff),
-			          v2 = (int8_t)((vv >> 16) & 0xff), v3 = (int8_t)((vv >> 24) & 0xff);
+		for (int j = 0; j < 8; ++j) cacc[g][j] = 0;
+	for (int k0 = warp * rows_per_step * kUnroll; k0 < width; k0 += nw * rows_per_step * kUnroll) {
+		int2 vv[kUnroll];
+#pragma unroll
+		for (int u = 0; u < kUnroll; ++u) {
+			const int k = k0 + u * rows_per_step + sub;
+			vv[u] = make_int2(0, 0);
+			if (k < width) vv[u] = __ldg((const int2*)kv_row_ptr(vplane, pages, k, hd) + dq);
+		}
+#pragma unroll
+		for (int u = 0; u < kUnroll; ++u) {
+			const int k = k0 + u * rows_per_step + sub;
+			if (k >= width) continue;
+			int v[8];
+#pragma unroll
+			for (int j = 0; j < 4; ++j) {
+				v[j] = (int8_t)((vv[u].x >> (8 * j)) & 0xff);
+				v[4 + j] = (int8_t)((vv[u].y >> (8 * j)) & 0xff);
+			}
 #pragma unroll
 			for (int g = 0; g < 8; ++g) {
 				if (g < group) {
 					const int p = sc[(size_t)g * width_pad + k];
-					cacc[g][0] += p * v0;
-					cacc[g][1] += p * v1;
-					cacc[g][2] += p * v2;
-					cacc[g][3] += p * v3;
+#pragma unroll
+					for (int j = 0; j < 8; ++j) cacc[g][j] += p * v[j];
 				}
 			}
 		}
@@ -153,7 +165,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 #pragma unroll
 	for (int g = 0; g < 8; ++g)
 #pragma unroll
-		for (int j = 0; j < 4; ++j) {
+		for (int j = 0; j < 8; ++j) {
 			int v = cacc[g][j];
 			for (int o = 16; o >= lanes_per_row; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
 			cacc[g][j] = v;
@@ -163,7 +175,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		for (int g = 0; g < 8; ++g)
 			if (g < group)
 #pragma unroll
-				for (int j = 0; j < 4; ++j) sred[((size_t)warp * group + g) * hd + dq * 4 + j] = cacc[g][j];
+				for (int j = 0; j < 8; ++j) sred[((size_t)warp * group + g) * hd + dq * 8 + j] = cacc[g][j];
 	}
 	__syncthreads();
 	unsigned long long lmax = 0;

@@ -459,6 +459,16 @@ extern "C" sslm_status sslm_b200_last_call_ms(sslm_workspace ws, float* ms, uint
 	return SSLM_OK;
 }
 
+extern "C" sslm_status sslm_b200_tc_stats(uint64_t* launches, uint64_t* refusals, int32_t* last_reason) {
+	unsigned long long l = 0, r = 0;
+	int why = 0;
+	tc_stats(&l, &r, &why);
+	if (launches) *launches = l;
+	if (refusals) *refusals = r;
+	if (last_reason) *last_reason = why;
+	return SSLM_OK;
+}
+
 extern "C" sslm_status sslm_b200_profile(sslm_workspace ws, int32_t enable) {
 	if (!ws) return SSLM_INVALID_ARGUMENT;
 	ws->profile = enable != 0;

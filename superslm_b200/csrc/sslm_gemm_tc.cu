@@ -3,22 +3,29 @@
 //   out[m,n] = fold_n( sum_k x[m,k] * w[n,k] ) (+ LoRA delta), per-row max |out| per segment
 //
 // A = activations [M,K] and B = weights [N,K] are both K-major, which is exactly the
-// operand form tcgen05.mma wants, so no repacking happens anywhere: TMA
-// (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) streams 128x128-byte tiles of
-// both into a shared-memory ring, one elected thread issues tcgen05.mma.kind::i8
-// (M=128, N=128, K=32 per instruction, s8 x s8 -> s32) into a TMEM accumulator, and four
-// epilogue warps read the accumulator back with tcgen05.ld, apply the per-channel
-// fixed-point fold (ApplyWeightScaleFold, src/forward/forward_sites.cpp:461-470), add the
-// runtime LoRA delta (:1082-1102), store the wide row and reduce the row maximum that the
-// requant funnel needs (an integer max: order-free, so deterministic).
+// operand form tcgen05.mma wants, so nothing is repacked: TMA (cp.async.bulk.tensor.2d,
+// 128-byte swizzle, no multicast) streams 128-byte-wide tiles of both into a shared-memory
+// ring, one thread issues tcgen05.mma.kind::i8 (s8 x s8 -> s32, M=128, N=BN, K=32 per
+// instruction) into TMEM accumulators, and four epilogue warps read the accumulators back
+// with tcgen05.ld, apply the per-channel fixed-point fold (ApplyWeightScaleFold,
+// src/forward/forward_sites.cpp:461-470), add the runtime LoRA delta (:1082-1102), store the
+// wide row and reduce the row maximum the requant funnel needs (integer max: order-free).
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31, one output row per thread).
-// Every wait on an mbarrier is bounded; a wait that runs out marks the tile's rows with an
-// internal status and the block tears down normally (TMEM is always freed).
+// The kernel is persistent: one block per SM walks a list of output tiles. A tile is BN
+// weight rows by MT*128 activation rows (MT = 2 shares every weight tile between two
+// accumulators, so a decode batch of up to 256 sequences reads each weight byte once).
+// Accumulators are double-buffered in TMEM, so the epilogue of tile i overlaps the main
+// loop of tile i+1.
+//
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31, one output row per thread,
+// two warps per lane quarter sharing the columns).
+// Every wait on an mbarrier is bounded; a wait that runs out marks the rows with an internal
+// status and the block tears down normally (TMEM is always freed).
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -26,13 +33,30 @@
 
 namespace sslm {
 
+// how often the tensor-core path ran / declined, and why it last declined
+// (1 alignment, 2 shared-memory opt-in, 3 no cuTensorMapEncodeTiled, 4 tensor-map encode failed)
+static std::atomic<unsigned long long> g_tc_launches{0}, g_tc_refusals{0};
+static std::atomic<int> g_tc_last_reason{0};
+
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 128, UMMA_K = 32, STAGES = 6;
-constexpr int kTcThreads = 192;
-constexpr uint32_t kStageBytes = (BM + BN) * BK;          // 32 KiB
-constexpr uint32_t kSmemBytes = STAGES * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int BM = 128, BK = 128, UMMA_K = 32;
+constexpr int kTcThreads = 320;   // producer warp, MMA warp, eight epilogue warps
+constexpr int kEpiThreads = 256;
 constexpr uint32_t kMaxPolls = 1u << 22;
+constexpr int kSmemBudget = 200 * 1024;
+
+template <int MT, int BN>
+struct TcCfg {
+	static constexpr uint32_t kStageBytes = (uint32_t)(MT * BM + BN) * BK;
+	static constexpr int kStages = (kSmemBudget / (int)kStageBytes) > 8 ? 8 : (kSmemBudget / (int)kStageBytes);
+	static constexpr uint32_t kTmemCols = 2u * MT * BN;                       // two accumulator stages
+	static constexpr uint32_t kFoldBytes = 2u * BN * 3 * 4;                   // double-buffered fold triples
+	static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kFoldBytes + 1024 /*align*/ + 256 /*barriers*/;
+	// s8 x s8 -> s32, A and B K-major, M = 128, N = BN
+	static constexpr uint32_t kInstrDesc =
+	    (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -40,6 +64,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 	asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 	uint32_t ok;
@@ -54,7 +81,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 	for (uint32_t i = 0; i < kMaxPolls; ++i) {
 		if (mbar_try_wait(bar, parity)) return true;
-		if (i > 1024) __nanosleep(64);
+		if (i > 2048) __nanosleep(64);
 	}
 	return false;
 }
@@ -73,15 +100,13 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 	d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
 	return d;
 }
-// s8 x s8 -> s32, A and B K-major, M = 128, N = BN
-constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
-__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
 	asm volatile(
 	    "{\n\t.reg .pred p;\n\t"
 	    "setp.ne.b32 p, %4, 0;\n\t"
 	    "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-	    ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate) : "memory");
+	    ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
 	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -98,36 +123,109 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// One 32-column chunk of one output row: fold, LoRA delta, store, row max / argmax key.
+// sfold: this tile's fold triples in shared memory (or nullptr: no fold), indexed by column
+// offset inside the tile.
+__device__ __forceinline__ void epilogue_chunk(const LinearArgs& a, const uint32_t (&r)[32], int row, int n_base,
+                                               int col_in_tile, const int32_t* sfold, const LoraLayerDev* lora,
+                                               bool vec_ok, unsigned long long (&lmax)[3], unsigned long long& lbest) {
+#pragma unroll
+	for (int j4 = 0; j4 < 32; j4 += 4) {
+		const int nb = n_base + j4;
+		if (nb >= a.N) break;
+		int64_t v4[4];
+#pragma unroll
+		for (int jj = 0; jj < 4; ++jj) {
+			const int n = nb + jj;
+			v4[jj] = 0;
+			if (n >= a.N) continue;
+			int32_t v32 = (int32_t)r[j4 + jj];
+			if (sfold != nullptr) {
+				const int32_t* f = sfold + 3 * (col_in_tile + j4 + jj);
+				v32 = fold(v32, f[0], f[1], f[2]);
+			}
+			if (a.best != nullptr) {   // head: greedy argmax key, lowest index wins ties
+				const unsigned long long key =
+				    ((unsigned long long)((uint32_t)v32 ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)n);
+				lbest = key > lbest ? key : lbest;
+				if (a.logits) a.logits[(size_t)row * a.N + n] = v32;
+				continue;
+			}
+			int seg = 0;
+			if (a.nseg > 1) {
+				while (seg + 1 < a.nseg && n >= a.seg_end[seg]) ++seg;
+			}
+			int64_t v = v32;
+			if (lora != nullptr && a.seg_lora[seg] >= 0) {
+				const LoraProjDev& p = lora->p[a.seg_lora[seg]];
+				if (p.a != nullptr) {
+					const int nl = n - (seg ? a.seg_end[seg - 1] : 0);
+					const int8_t* brow = p.b + (size_t)nl * lora->rank;
+					const int8_t* u = a.lora_u + ((size_t)row * 3 + seg) * kMaxLoraRank;
+					int dsum = 0;
+					for (uint32_t t = 0; t < lora->rank; ++t) dsum += (int)brow[t] * (int)u[t];
+					v += (int64_t)amp_fold(dsum, p.df[3 * nl], p.df[3 * nl + 1], p.df[3 * nl + 2]);
+				}
+			}
+			v4[jj] = v;
+			const unsigned long long ab = v < 0 ? (~(unsigned long long)v + 1ull) : (unsigned long long)v;
+			if (seg == 0) lmax[0] = ab > lmax[0] ? ab : lmax[0];
+			else if (seg == 1) lmax[1] = ab > lmax[1] ? ab : lmax[1];
+			else lmax[2] = ab > lmax[2] ? ab : lmax[2];
+		}
+		if (a.best != nullptr) continue;
+		if (vec_ok && nb + 3 < a.N) {
+			*(int4*)((int32_t*)a.out + (size_t)row * a.out_ld + nb) = make_int4((int)v4[0], (int)v4[1], (int)v4[2], (int)v4[3]);
+		} else {
+#pragma unroll
+			for (int jj = 0; jj < 4; ++jj) {
+				if (nb + jj >= a.N) break;
+				if (a.out64) ((int64_t*)a.out)[(size_t)row * a.out_ld + nb + jj] = v4[jj];
+				else ((int32_t*)a.out)[(size_t)row * a.out_ld + nb + jj] = (int32_t)v4[jj];
+			}
+		}
+	}
+}
+
+template <int MT, int BN>
 __global__ void __launch_bounds__(kTcThreads, 1)
-k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, LinearArgs a,
-            int32_t* row_status) {
+k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, LinearArgs a) {
+	using Cfg = TcCfg<MT, BN>;
+	constexpr int S = Cfg::kStages;
 	extern __shared__ unsigned char smem_raw[];
 	const uint32_t raw = smem_u32(smem_raw);
 	const uint32_t base = (raw + 1023u) & ~1023u;            // SW128 tiles want 1024-byte alignment
 	unsigned char* smem = smem_raw + (base - raw);
-	const uint32_t bars = base + STAGES * kStageBytes;       // full[S], empty[S], acc_full, tmem slot
+	int32_t* sfold = (int32_t*)(smem + S * Cfg::kStageBytes);                       // [2][BN*3]
+	const uint32_t bars = base + S * Cfg::kStageBytes + Cfg::kFoldBytes;            // 8-byte slots
 	auto full_bar = [&](int s) { return bars + 8u * s; };
-	auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-	const uint32_t acc_bar = bars + 8u * (2 * STAGES);
-	uint32_t* tmem_slot = (uint32_t*)(smem + STAGES * kStageBytes + 8 * (2 * STAGES + 1));
-	__shared__ int s_timeout;
+	auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+	auto accf_bar = [&](int s) { return bars + 8u * (2 * S + s); };
+	auto acce_bar = [&](int s) { return bars + 8u * (2 * S + 2 + s); };
+	uint32_t* tmem_slot = (uint32_t*)(smem + S * Cfg::kStageBytes + Cfg::kFoldBytes + 8 * (2 * S + 4));
+	__shared__ volatile int s_timeout;
+	__shared__ volatile int s_stop[2];
 
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-	const int tile_n = blockIdx.x, tile_m = blockIdx.y;
-	const int m0 = tile_m * BM, n0 = tile_n * BN;
 	const int kblocks = (a.K + BK - 1) / BK;
+	const int n_tiles = (a.N + BN - 1) / BN;
+	const int m_groups = (a.M + MT * BM - 1) / (MT * BM);
+	const int tiles = n_tiles * m_groups;
 
 	if (threadIdx.x == 0) {
-		for (int s = 0; s < STAGES; ++s) {
+		for (int s = 0; s < S; ++s) {
 			mbar_init(full_bar(s), 1);
 			mbar_init(empty_bar(s), 1);
 		}
-		mbar_init(acc_bar, 1);
+		for (int s = 0; s < 2; ++s) {
+			mbar_init(accf_bar(s), 1);
+			mbar_init(acce_bar(s), 8);       // one arrival per epilogue warp
+		}
 		s_timeout = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
 	if (warp == 1) {
-		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN));
+		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::kTmemCols));
 		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
 	}
 	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -137,116 +235,165 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
 	if (warp == 0) {
 		if (lane == 0) {
-			for (int kb = 0; kb < kblocks; ++kb) {
-				const int s = kb % STAGES;
-				const uint32_t phase = (uint32_t)(kb / STAGES) & 1u;
-				if (!mbar_wait(empty_bar(s), phase ^ 1u)) { s_timeout = 1; break; }
-				mbar_expect_tx(full_bar(s), kStageBytes);
-				const uint32_t sa = base + s * kStageBytes, sb = sa + BM * BK;
-				tma_load_2d(sa, &map_a, full_bar(s), kb * BK, m0);
-				tma_load_2d(sb, &map_b, full_bar(s), kb * BK, n0);
+			uint32_t it = 0;
+			for (int t = blockIdx.x; t < tiles && s_timeout == 0; t += gridDim.x) {
+				const int m0 = (t % m_groups) * MT * BM, n0 = (t / m_groups) * BN;
+				for (int kb = 0; kb < kblocks; ++kb, ++it) {
+					const int s = (int)(it % S);
+					const uint32_t phase = (it / S) & 1u;
+					if (!mbar_wait(empty_bar(s), phase ^ 1u)) { s_timeout = 1; break; }
+					mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
+					const uint32_t sa = base + s * Cfg::kStageBytes;
+#pragma unroll
+					for (int mt = 0; mt < MT; ++mt) tma_load_2d(sa + mt * BM * BK, &map_a, full_bar(s), kb * BK, m0 + mt * BM);
+					tma_load_2d(sa + MT * BM * BK, &map_b, full_bar(s), kb * BK, n0);
+				}
 			}
 		}
 	} else if (warp == 1) {
 		if (lane == 0) {
-			bool ok = true;
-			for (int kb = 0; kb < kblocks && ok; ++kb) {
-				const int s = kb % STAGES;
-				const uint32_t phase = (uint32_t)(kb / STAGES) & 1u;
-				if (!mbar_wait(full_bar(s), phase)) { s_timeout = 1; ok = false; break; }
+			uint32_t it = 0, tc = 0;
+			for (int t = blockIdx.x; t < tiles && s_timeout == 0; t += gridDim.x, ++tc) {
+				const uint32_t as = tc & 1u;
+				if (!mbar_wait(acce_bar(as), ((tc >> 1) & 1u) ^ 1u)) { s_timeout = 1; break; }
 				asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-				const uint32_t sa = base + s * kStageBytes, sb = sa + BM * BK;
-				const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
+				for (int kb = 0; kb < kblocks; ++kb, ++it) {
+					const int s = (int)(it % S);
+					const uint32_t phase = (it / S) & 1u;
+					if (!mbar_wait(full_bar(s), phase)) { s_timeout = 1; break; }
+					asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+					const uint32_t sa = base + s * Cfg::kStageBytes;
+					const uint64_t db = umma_desc_sw128(sa + MT * BM * BK);
 #pragma unroll
-				for (int k = 0; k < BK / UMMA_K; ++k) {
-					// advancing inside the 128-byte swizzle atom: +32 bytes = +2 in descriptor units
-					umma_i8(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), (kb | k) != 0 ? 1u : 0u);
-				}
-				umma_commit(empty_bar(s));     // frees the stage once these MMAs have read it
-			}
-			umma_commit(acc_bar);              // accumulator complete (arrives even after a timeout)
-		}
-	} else {
-		// epilogue: this thread owns output row m0 + 32*q + lane
-		const int q = warp & 3;
-		const int row = m0 + q * 32 + lane;
-		const bool acc_ok = mbar_wait(acc_bar, 0);
-		asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-		if (!acc_ok) s_timeout = 1;
-		const bool row_ok = acc_ok && row < a.M && s_timeout == 0;
-		const LoraLayerDev* lora = (row_ok && a.rows != nullptr && a.rows[row].lora != nullptr) ? a.rows[row].lora + a.layer : nullptr;
-		unsigned long long lmax[3] = {0ull, 0ull, 0ull};
-		unsigned long long lbest = 0ull;
-		for (int c0 = 0; c0 < BN; c0 += 32) {
-			uint32_t r[32];
-			tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);   // warp-collective: never skipped
-			if (!row_ok || n0 + c0 >= a.N) continue;
-			const bool vec_ok = !a.out64 && (a.out_ld & 3) == 0 && (((uintptr_t)a.out) & 15) == 0;
+					for (int mt = 0; mt < MT; ++mt) {
+						const uint64_t da = umma_desc_sw128(sa + mt * BM * BK);
+						const uint32_t dcol = tmem_base + (as * MT + mt) * BN;
 #pragma unroll
-			for (int j4 = 0; j4 < 32; j4 += 4) {
-				int64_t v4[4];
-#pragma unroll
-				for (int jj = 0; jj < 4; ++jj) {
-					const int n = n0 + c0 + j4 + jj;
-					v4[jj] = 0;
-					if (n >= a.N) continue;
-					int seg = 0;
-					while (seg + 1 < a.nseg && n >= a.seg_end[seg]) ++seg;
-					int32_t v32 = (int32_t)r[j4 + jj];
-					if (a.fold) v32 = fold(v32, a.fold[3 * n], a.fold[3 * n + 1], a.fold[3 * n + 2]);
-					int64_t v = v32;
-					if (lora != nullptr && a.seg_lora[seg] >= 0) {
-						const LoraProjDev& p = lora->p[a.seg_lora[seg]];
-						if (p.a != nullptr) {
-							const int nl = n - (seg ? a.seg_end[seg - 1] : 0);
-							const int8_t* brow = p.b + (size_t)nl * lora->rank;
-							const int8_t* u = a.lora_u + ((size_t)row * 3 + seg) * kMaxLoraRank;
-							int dsum = 0;
-							for (uint32_t t = 0; t < lora->rank; ++t) dsum += (int)brow[t] * (int)u[t];
-							v += (int64_t)amp_fold(dsum, p.df[3 * nl], p.df[3 * nl + 1], p.df[3 * nl + 2]);
+						for (int k = 0; k < BK / UMMA_K; ++k) {
+							// advancing inside the 128-byte swizzle atom: +32 bytes = +2 descriptor units
+							umma_i8(dcol, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), Cfg::kInstrDesc, (kb | k) != 0 ? 1u : 0u);
 						}
 					}
-					if (a.best != nullptr) {   // head: greedy argmax key, lowest index wins ties
-						const unsigned long long key =
-						    ((unsigned long long)((uint32_t)v32 ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)n);
-						lbest = key > lbest ? key : lbest;
-						if (a.logits) a.logits[(size_t)row * a.N + n] = v32;
-						continue;
-					}
-					v4[jj] = v;
-					const unsigned long long ab = v < 0 ? (~(unsigned long long)v + 1ull) : (unsigned long long)v;
-					if (seg == 0) lmax[0] = ab > lmax[0] ? ab : lmax[0];
-					else if (seg == 1) lmax[1] = ab > lmax[1] ? ab : lmax[1];
-					else lmax[2] = ab > lmax[2] ? ab : lmax[2];
+					umma_commit(empty_bar(s));     // frees the stage once these MMAs have read it
 				}
-				const int nb = n0 + c0 + j4;
-				if (nb >= a.N || a.best != nullptr) continue;
-				if (vec_ok && nb + 3 < a.N) {
-					*(int4*)((int32_t*)a.out + (size_t)row * a.out_ld + nb) =
-					    make_int4((int)v4[0], (int)v4[1], (int)v4[2], (int)v4[3]);
-				} else {
+				umma_commit(accf_bar(as));         // this tile's accumulators are complete
+			}
+		}
+	} else {
+		// epilogue: eight warps. Warp w reads TMEM lanes 32*(w%4)..+31, so this thread owns
+		// rows m0 + mt*128 + 32*q + lane of every tile; the two warps of a lane quarter split
+		// the tile's 32-column chunks between them (half = 0 / 1).
+		const int q = warp & 3;
+		const int half = (warp - 2) >> 2;
+		const int et = threadIdx.x - 64;           // 0..255 within the epilogue group
+		const bool vec_ok = !a.out64 && (a.out_ld & 3) == 0 && (((uintptr_t)a.out) & 15) == 0;
+		// straight-line path: int32 rows, fold present, no adapters, not the head
+		const bool fast_ok = vec_ok && a.fold != nullptr && a.rows == nullptr && a.best == nullptr;
+		uint32_t tc = 0;
+		for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tc) {
+			const uint32_t as = tc & 1u;
+			const int m0 = (t % m_groups) * MT * BM, n0 = (t / m_groups) * BN;
+			int32_t* sf = nullptr;
+			if (a.fold != nullptr) {
+				sf = sfold + as * BN * 3;
+				for (int i = et; i < BN * 3; i += kEpiThreads) {
+					const int n = n0 + i / 3;
+					sf[i] = n < a.N ? a.fold[(size_t)n0 * 3 + i] : 0;
+				}
+			}
+			if (et == 0) s_stop[as] = s_timeout;               // one thread decides, so all eight warps agree
+			asm volatile("bar.sync 1, 256;" ::: "memory");     // fold triples + stop flag visible to the epilogue warps
+			if (s_stop[as] != 0) {
+				if (a.status != nullptr) {
+					for (int mt = 0; mt < MT; ++mt) {
+						const int row = m0 + mt * BM + q * 32 + lane;
+						if (row < a.M) atomicCAS(&a.status[row], 0, (int32_t)kInternalWaitTimeout);
+					}
+				}
+				break;
+			}
+			const bool acc_ok = mbar_wait(accf_bar(as), (tc >> 1) & 1u);
+			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+			if (!acc_ok) s_timeout = 1;
 #pragma unroll
-					for (int jj = 0; jj < 4; ++jj) {
-						if (nb + jj >= a.N) break;
-						if (a.out64) ((int64_t*)a.out)[(size_t)row * a.out_ld + nb + jj] = v4[jj];
-						else ((int32_t*)a.out)[(size_t)row * a.out_ld + nb + jj] = (int32_t)v4[jj];
+			for (int mt = 0; mt < MT; ++mt) {
+				const int row = m0 + mt * BM + q * 32 + lane;
+				const bool row_ok = acc_ok && row < a.M;
+				const LoraLayerDev* lora =
+				    (row_ok && a.rows != nullptr && a.rows[row].lora != nullptr) ? a.rows[row].lora + a.layer : nullptr;
+				unsigned long long lmax[3] = {0ull, 0ull, 0ull};
+				unsigned long long lbest = 0ull;
+				int best_v = INT32_MIN, best_n = -1;
+				if (m0 + mt * BM < a.M) {            // warp-uniform: the whole sub-tile is outside M otherwise
+					for (int c0 = half * 32; c0 < BN; c0 += 64) {
+						uint32_t r[32];
+						tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (as * MT + mt) * BN + c0, r);   // warp-collective
+						const int nb = n0 + c0;
+						if (!row_ok || nb >= a.N) continue;
+						const bool full = nb + 32 <= a.N;
+						if (a.best != nullptr && a.fold == nullptr && a.logits == nullptr && full) {
+							// head: running (value, index) maximum; columns ascend, so a strict
+							// comparison keeps the lowest index among equals
+#pragma unroll
+							for (int j = 0; j < 32; ++j) {
+								const int v = (int)r[j];
+								const bool gt = v > best_v;
+								best_v = gt ? v : best_v;
+								best_n = gt ? nb + j : best_n;
+							}
+							continue;
+						}
+						int seg = 0;
+						while (seg + 1 < a.nseg && nb >= a.seg_end[seg]) ++seg;
+						if (fast_ok && full && nb + 32 <= a.seg_end[seg]) {
+							// one segment, whole chunk inside N: no branches, so the 32 elements interleave
+							uint32_t mx = 0;
+							int32_t* dst = (int32_t*)a.out + (size_t)row * a.out_ld + nb;
+#pragma unroll
+							for (int j4 = 0; j4 < 32; j4 += 4) {
+								int v[4];
+#pragma unroll
+								for (int jj = 0; jj < 4; ++jj) {
+									const int32_t* f = sf + 3 * (c0 + j4 + jj);
+									const int32_t acc = (int32_t)r[j4 + jj];
+									const int32_t fv = rdivpot32(srdhm(acc, f[1]), f[2]);
+									v[jj] = f[0] != 0 ? acc : fv;
+									const uint32_t ab = v[jj] < 0 ? 0u - (uint32_t)v[jj] : (uint32_t)v[jj];
+									mx = ab > mx ? ab : mx;
+								}
+								*(int4*)(dst + j4) = make_int4(v[0], v[1], v[2], v[3]);
+							}
+							if (seg == 0) lmax[0] = mx > lmax[0] ? mx : lmax[0];
+							else if (seg == 1) lmax[1] = mx > lmax[1] ? mx : lmax[1];
+							else lmax[2] = mx > lmax[2] ? mx : lmax[2];
+						} else {
+							epilogue_chunk(a, r, row, nb, c0, sf, lora, vec_ok, lmax, lbest);
+						}
+					}
+				}
+				if (row_ok) {
+					if (best_n >= 0) {
+						const unsigned long long key =
+						    ((unsigned long long)((uint32_t)best_v ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)best_n);
+						lbest = key > lbest ? key : lbest;
+					}
+					if (a.best != nullptr && lbest != 0ull) atomicMax(&a.best[row], lbest);
+					if (a.rowmax != nullptr && a.best == nullptr) {
+						for (int s = 0; s < a.nseg; ++s)
+							if (a.seg_slot[s] >= 0 && lmax[s] != 0ull) atomicMax(&a.rowmax[(size_t)row * 4 + a.seg_slot[s]], lmax[s]);
 					}
 				}
 			}
-		}
-		if (row_ok && a.best != nullptr && lbest != 0ull) atomicMax(&a.best[row], lbest);
-		if (row_ok && a.rowmax != nullptr) {
-			for (int s = 0; s < a.nseg; ++s)
-				if (a.seg_slot[s] >= 0 && lmax[s] != 0ull) atomicMax(&a.rowmax[(size_t)row * 4 + a.seg_slot[s]], lmax[s]);
+			asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+			__syncwarp();
+			if (lane == 0) mbar_arrive(acce_bar(as));          // accumulator stage may be overwritten
 		}
 	}
 	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 	__syncthreads();
-	if (s_timeout != 0 && row_status != nullptr && threadIdx.x < BM && m0 + (int)threadIdx.x < a.M)
-		atomicCAS(&row_status[m0 + threadIdx.x], 0, (int32_t)kInternalWaitTimeout);
 	if (warp == 1) {
 		asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN));
+		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols));
 	}
 }
 
@@ -267,20 +414,20 @@ EncodeFn encode_fn() {
 
 struct MapKey {
 	const void* p;
-	int rows, k;
-	bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && k == o.k; }
+	int rows, k, box_rows;
+	bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && k == o.k && box_rows == o.box_rows; }
 };
 struct MapKeyHash {
 	size_t operator()(const MapKey& k) const {
-		return std::hash<const void*>()(k.p) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.k << 40);
+		return std::hash<const void*>()(k.p) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.k << 40) ^ ((size_t)k.box_rows << 20);
 	}
 };
 
-// [rows, K] int8 row-major -> 2-D map, box 128 bytes x 128 rows, 128-byte swizzle, zero fill
-bool tensor_map(const void* ptr, int rows, int k, CUtensorMap* out) {
+// [rows, K] int8 row-major -> 2-D map, box = 128 bytes x box_rows rows, 128-byte swizzle, zero fill
+bool tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out) {
 	static std::mutex mu;
 	static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-	const MapKey key{ptr, rows, k};
+	const MapKey key{ptr, rows, k, box_rows};
 	std::lock_guard<std::mutex> lock(mu);
 	auto it = cache.find(key);
 	if (it != cache.end()) {
@@ -291,7 +438,7 @@ bool tensor_map(const void* ptr, int rows, int k, CUtensorMap* out) {
 	if (!fn) return false;
 	const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
 	const cuuint64_t strides[1] = {(cuuint64_t)k};
-	const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+	const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
 	const cuuint32_t estr[2] = {1, 1};
 	CUtensorMap m;
 	if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -304,20 +451,63 @@ bool tensor_map(const void* ptr, int rows, int k, CUtensorMap* out) {
 	return true;
 }
 
-}  // namespace
+int sm_count() {
+	static int n = [] {
+		int dev = 0, v = 148;
+		cudaGetDevice(&dev);
+		if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) v = 148;
+		return v;
+	}();
+	return n;
+}
 
-bool launch_linear_tc(const LinearArgs& a, cudaStream_t st) {
-	if (a.K % 16 != 0 || ((uintptr_t)a.x & 15) || ((uintptr_t)a.w & 15)) return false;
+template <int MT, int BN>
+bool launch_cfg(const LinearArgs& a, cudaStream_t st) {
+	using Cfg = TcCfg<MT, BN>;
 	static bool configured = false;
 	if (!configured) {
-		if (cudaFuncSetAttribute(k_linear_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
+		if (cudaFuncSetAttribute(k_linear_tc<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes) != cudaSuccess) {
+			g_tc_last_reason.store(2);
 			return false;
+		}
 		configured = true;
 	}
 	CUtensorMap ma, mb;
-	if (!tensor_map(a.x, a.M, a.K, &ma) || !tensor_map(a.w, a.N, a.K, &mb)) return false;
-	const dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
-	k_linear_tc<<<grid, kTcThreads, kSmemBytes, st>>>(ma, mb, a, a.status);
+	if (!tensor_map(a.x, a.M, a.K, BM, &ma) || !tensor_map(a.w, a.N, a.K, BN, &mb)) {
+		g_tc_last_reason.store(encode_fn() ? 4 : 3);
+		return false;
+	}
+	const int tiles = ((a.N + BN - 1) / BN) * ((a.M + MT * BM - 1) / (MT * BM));
+	const int grid = tiles < sm_count() ? tiles : sm_count();
+	k_linear_tc<MT, BN><<<grid, kTcThreads, Cfg::kSmemBytes, st>>>(ma, mb, a);
+	return true;
+}
+
+}  // namespace
+
+void tc_stats(unsigned long long* launches, unsigned long long* refusals, int* last_reason) {
+	*launches = g_tc_launches.load();
+	*refusals = g_tc_refusals.load();
+	*last_reason = g_tc_last_reason.load();
+}
+static bool tc_refuse(int reason) {
+	g_tc_refusals.fetch_add(1);
+	g_tc_last_reason.store(reason);
+	return false;
+}
+
+bool launch_linear_tc(const LinearArgs& a, cudaStream_t st) {
+	if (a.K % 16 != 0 || ((uintptr_t)a.x & 15) || ((uintptr_t)a.w & 15)) return tc_refuse(1);
+	// two accumulators per weight tile once there is more than one 128-row group; narrower
+	// weight tiles when there would otherwise be fewer tiles than SMs
+	const bool two = a.M > BM;
+	const int tiles128 = ((a.N + 127) / 128) * ((a.M + (two ? 255 : 127)) / (two ? 256 : 128));
+	const bool narrow = tiles128 < sm_count();
+	bool ok;
+	if (two) ok = narrow ? launch_cfg<2, 64>(a, st) : launch_cfg<2, 128>(a, st);
+	else ok = narrow ? launch_cfg<1, 64>(a, st) : launch_cfg<1, 128>(a, st);
+	if (!ok) return tc_refuse(g_tc_last_reason.load() ? g_tc_last_reason.load() : 9);
+	g_tc_launches.fetch_add(1);
 	return true;
 }
 

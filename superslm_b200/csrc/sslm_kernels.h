@@ -55,6 +55,8 @@ void launch_linear_gemv(const LinearArgs& a, cudaStream_t st);
 // tensor-core path for M > 8 rows (tcgen05 kind::i8, TMA-fed). Returns false when the
 // shape is not supported by that kernel (caller then uses the GEMV path).
 bool launch_linear_tc(const LinearArgs& a, cudaStream_t st);
+// process-wide counters of the tensor-core path: launches, refusals, reason of the last refusal
+void tc_stats(unsigned long long* launches, unsigned long long* refusals, int* last_reason);
 
 // u = clamp127(amp_fold(A x)) for up to three projections sharing the input x
 // (AddAmplifyingLoraDelta's first half, src/forward/forward_sites.cpp:1062-1080)

@@ -237,6 +237,15 @@ def gpu_linear(lib, x, w, fold, in_scales, site, use_tc):
     return folded, codes, scales, status
 
 
+def tc_launches(lib):
+    f = lib.dll.sslm_b200_tc_stats
+    f.argtypes = [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_int32)]
+    n, r, why = C.c_uint64(0), C.c_uint64(0), C.c_int32(0)
+    assert f(C.byref(n), C.byref(r), C.byref(why)) == 0
+    assert r.value == 0, "tensor-core path declined a launch, reason %d" % why.value
+    return n.value
+
+
 LINEAR_CASES = [  # (K, N, M): every M class, ragged N, the real 1.5B K/V and hidden shapes
     (1536, 256, 1), (1536, 256, 16), (1536, 256, 128), (1536, 1536, 1), (1536, 1536, 5), (1536, 1536, 130),
     (8960, 1536, 1), (8960, 1536, 16), (1536, 8960, 2), (1536, 8960, 64), (128, 77, 3), (16, 1, 1), (256, 333, 257),
@@ -257,7 +266,10 @@ def test_linear_layer_sweep(gpu_lib, K, N, M, use_tc):
     in_scales = np.stack([rng.integers(1 << 30, 1 << 31, M), np.full(M, -37)], axis=1).astype(np.int64)
     site = (1090717716, -44)
     want = oracle_linear(x, w, fold, in_scales, site)
+    before = tc_launches(gpu_lib)
     got = gpu_linear(gpu_lib, x, w, fold, in_scales, site, use_tc)
+    # no silent substitution: M > 8 with tensor cores requested must run the tcgen05 kernel
+    assert tc_launches(gpu_lib) - before == (1 if (use_tc and M > 8) else 0)
     assert (got[3] == want[3]).all()
     assert (got[0].astype(np.int64) == want[0]).all()
     assert (got[1] == want[1]).all()
