@@ -173,6 +173,19 @@ SSLM_HD int64_t dyn_recip(int64_t dn) {
 SSLM_HD int8_t requant_code(int64_t x, int64_t r, int s) {
 	int exponent = 62 - s;  // [32,63]
 	uint64_t ax = x < 0 ? (~(uint64_t)x + 1u) : (uint64_t)x;
+	// Everything the funnel hands over satisfies |x| <= 2^31, 2^31 < R <= 2^32; for an
+	// exponent E >= 33 the composite floor((|x|*R*127 + 2^(E-1)) / 2^E) then needs 64-bit
+	// words only: with P = |x|*R*127 = A*2^32 + b (0 <= b < 2^32) it equals
+	// floor((A + 2^(E-33)) / 2^(E-32)), because the dropped fraction b/2^32 < 1 cannot carry
+	// the sum over a multiple of the integer divisor.
+	if (exponent >= 33 && ax <= ((uint64_t)1 << 31) && (uint64_t)r <= ((uint64_t)1 << 32)) {
+		const uint64_t p = ax * (uint64_t)r;                                   // <= 2^63
+		const uint64_t a = (p >> 32) * 127u + (((p & 0xFFFFFFFFull) * 127u) >> 32);
+		uint64_t mag = (a + ((uint64_t)1 << (exponent - 33))) >> (exponent - 32);
+		if (mag > 127u) mag = 127u;
+		const int32_t qf = (int32_t)mag;
+		return (int8_t)(x < 0 ? -qf : qf);
+	}
 	U128 prod = umul128x64(umul64(ax, (uint64_t)r), 127u);
 	U128 num = uadd(U128{prod.lo << 1, (prod.hi << 1) | (prod.lo >> 63)}, U128{(uint64_t)1 << exponent, 0});
 	U128 sh = ushr(num, exponent + 1);
@@ -253,6 +266,19 @@ SSLM_HD int64_t floor_div(int64_t a, int64_t b) {
 	int64_t q = a / b, r = a % b;
 	return (r != 0 && r < 0) ? q - 1 : q;
 }
+// floor((h << 32) / root) for an activation code |h| <= 127 and root >= 1: the per-element
+// division of RmsNormSite. A double-precision estimate (numerator < 2^39, so the estimate is
+// within one of the quotient) corrected by exact integer arithmetic, then floored toward
+// minus infinity for negative h.
+SSLM_HD int64_t floor_div_h32(int h, int64_t root, double inv_root) {
+	const uint64_t num = (uint64_t)(h < 0 ? -h : h) << 32;
+	uint64_t q = (uint64_t)((double)num * inv_root);
+	int64_t r = (int64_t)(num - q * (uint64_t)root);
+	while (r < 0) { --q; r += root; }
+	while (r >= root) { ++q; r -= root; }
+	if (h >= 0) return (int64_t)q;
+	return -(int64_t)q - (r != 0 ? 1 : 0);
+}
 // num / den (truncating, both non-negative, den >= 1) when the quotient is known to
 // be below 2^20: a double-precision estimate corrected by exact integer arithmetic.
 SSLM_HD uint64_t udiv_small_quotient(uint64_t num, uint64_t den, double inv_den) {
@@ -292,6 +318,19 @@ SSLM_HD int64_t landing_rescale(int64_t code, int64_t m_a, int64_t r_t, int64_t 
 	int64_t k = sat_sub64(62, sat_sub64(e_a, e_t));
 	if (k > 4096) k = 4096;
 	if (k < -4096) k = -4096;
+	// The operands every in-domain call site produces (|code| <= 2^31, |m_a| < 2^31,
+	// 0 < r_t <= 2^32, 33 <= k <= 94) keep the composite inside 64-bit words: with
+	// P = |code|*|m_a|*r_t = A*2^32 + b the rounded quotient floor((P + 2^(k-1)) / 2^k) is
+	// floor((A + 2^(k-33)) / 2^(k-32)). Anything else takes the general 128-bit route.
+	if (k >= 33 && k <= 94 && ac <= ((uint64_t)1 << 31) && am < ((uint64_t)1 << 31) && r_t > 0 &&
+	    (uint64_t)r_t <= ((uint64_t)1 << 32)) {
+		const uint64_t p = am * (uint64_t)r_t;                                        // < 2^63
+		const uint64_t a = ac * (p >> 32) + ((ac * (p & 0xFFFFFFFFull)) >> 32);       // floor(P / 2^32)
+		const uint64_t qm = (a + ((uint64_t)1 << (k - 33))) >> (k - 32);
+		if (saturated) *saturated = qm > 127;
+		if (exceeded_int64) *exceeded_int64 = false;
+		return neg ? -(int64_t)qm : (int64_t)qm;
+	}
 	bool over_clamp, over_i64;
 	int64_t raw;
 	if (k >= 0) {

@@ -111,9 +111,9 @@ __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Sca
 	ss = block_sum_i64(ss, red);
 	int64_t root = isqrt64(floor_div((int64_t)ss << 32, (int64_t)n));
 	if (root < 1) root = 1;
+	const double inv_root = 1.0 / (double)root;
 	for (int i = threadIdx.x; i < n; i += blockDim.x) {
-		const int64_t num = (int64_t)h[i] * ((int64_t)1 << 32);
-		wide[i] = floor_div(num, root) * (int64_t)gain[i];
+		wide[i] = floor_div_h32((int)h[i], root, inv_root) * (int64_t)gain[i];
 	}
 	__syncthreads();
 	return block_funnel<int64_t>(wide, n, nullptr, 0, site, out_g, nullptr, out_scale, red);

@@ -25,6 +25,7 @@ int dev_funnel_params(uint64_t max_abs, const int64_t* inc, int n, int64_t cm, i
 	return fp.status;
 }
 int64_t dev_floor_div(int64_t a, int64_t b) { return floor_div(a, b); }
+int64_t dev_floor_div_h32(int h, int64_t root) { return floor_div_h32(h, root, 1.0 / (double)root); }
 uint64_t dev_udiv_small(uint64_t n, uint64_t d) { return udiv_small_quotient(n, d, 1.0 / (double)d); }
 int64_t dev_isqrt(int64_t n) { return isqrt64(n); }
 int64_t dev_landing_rescale(int64_t c, int64_t m, int64_t r, int64_t ea, int64_t et, int* sat, int* ex) {

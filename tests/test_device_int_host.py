@@ -1,0 +1,114 @@
+"""The device integer library (csrc/sslm_int.cuh), compiled for the host, against the CPU
+oracle on seeded sweeps: every function the kernels call, on operands that take the 64-bit
+fast paths and on operands that force the general 128-bit routes."""
+import ctypes as C
+import random
+
+from tests.support import devint
+
+I64 = C.c_int64
+
+
+def ri(rnd, bits):
+    return rnd.randrange(-(1 << bits), 1 << bits)
+
+
+def test_reciprocal_and_requant(port):
+    d = devint.lib()
+    rnd = random.Random(1)
+    for _ in range(40000):
+        x = rnd.choice([rnd.randrange(1 << 30, 1 << 31), ri(rnd, 31), ri(rnd, 40), ri(rnd, 62), rnd.randrange(1, 1000)])
+        assert d.dev_dyn_recip(x) == port.osc_dyn_recip(x)
+    for _ in range(60000):
+        s = rnd.randrange(-1, 31)
+        dn = rnd.randrange(1 << 30, 1 << 31)
+        r = port.osc_dyn_recip(dn) if rnd.random() < 0.9 else rnd.randrange(1, 1 << 40)
+        x = rnd.choice([ri(rnd, 31), ri(rnd, 33), ri(rnd, 10), 1 << 31, -(1 << 31), (1 << 31) + 1, 0, 1, -1])
+        assert d.dev_requant_code(x, r, s) == port.osc_requant_code_wide(x, r, s), (x, r, s)
+
+
+def test_landing_rescale_fast_and_general(port):
+    d = devint.lib()
+    rnd = random.Random(2)
+    for i in range(120000):
+        code = rnd.choice([ri(rnd, 7), ri(rnd, 31), ri(rnd, 33), ri(rnd, 62), 1 << 31, -(1 << 31)])
+        m = rnd.choice([rnd.randrange(1 << 30, 1 << 31), ri(rnd, 31), (1 << 31) - 1, -(1 << 31)])
+        rt = rnd.choice([rnd.randrange((1 << 31) + 1, (1 << 32) + 1), 1 << 32, ri(rnd, 40), ri(rnd, 63), 0])
+        ea, et = rnd.randrange(-90, 45), rnd.randrange(-70, 20)
+        if i % 50 == 0:
+            ea, et = ri(rnd, 63), ri(rnd, 63)
+        if i % 7 == 0:      # pin the composed exponent to the edges of the fast window
+            et = ea - 62 + rnd.choice([32, 33, 34, 93, 94, 95, 0, -1, 127, 128])
+        s1, x1 = C.c_int(), C.c_int()
+        sat, x2 = C.c_uint64(0), C.c_int()
+        a = d.dev_landing_rescale(code, m, rt, ea, et, C.byref(s1), C.byref(x1))
+        b = port.osc_landing_rescale(code, m, rt, ea, et, C.byref(sat), C.byref(x2))
+        assert (a, s1.value, x1.value) == (b, sat.value, x2.value), (code, m, rt, ea, et)
+
+
+def test_floor_div_and_isqrt(port):
+    d = devint.lib()
+    rnd = random.Random(3)
+    for _ in range(60000):
+        h = rnd.randrange(-127, 128)
+        root = rnd.choice([1, 2, 3, rnd.randrange(1, 1 << 24), rnd.randrange(1, 1 << 12), 127 << 16])
+        assert d.dev_floor_div_h32(h, root) == port.osc_floor_div(h * (1 << 32), root), (h, root)
+        a, b = ri(rnd, 50), rnd.randrange(1, 1 << 30)
+        assert d.dev_floor_div(a, b) == port.osc_floor_div(a, b)
+        n = rnd.choice([rnd.randrange(0, 1 << 62), rnd.randrange(0, 1 << 40), rnd.randrange(0, 100)])
+        assert d.dev_isqrt(n) == port.osc_isqrt(n)
+    for den in (1, 2, 3, 1 << 40, (1 << 62) - 1):
+        for q in (0, 1, 2, 32767, 32768, 65535):
+            for rem in (0, 1, den - 1):
+                num = min(q * den + min(rem, den - 1), (1 << 63) - 1)
+                assert d.dev_udiv_small(num, den) == num // den
+
+
+def test_folds_and_scale_algebra(port):
+    d = devint.lib()
+    rnd = random.Random(4)
+    from oracle.harness import Scale
+    for _ in range(60000):
+        acc = ri(rnd, 31)
+        mult = rnd.randrange(1 << 30, 1 << 31) if rnd.random() < 0.8 else ri(rnd, 31)
+        sh, ex, idn = rnd.randrange(0, 32), rnd.randrange(-31, 32), int(rnd.random() < 0.1)
+        assert d.dev_fold(acc, idn, mult, sh) == port.osc_fold(acc, idn, mult, sh)
+        assert d.dev_amp_fold(acc, idn, mult, ex) == port.osc_amp_fold(acc, idn, mult, ex)
+        am, bm = ri(rnd, 31), ri(rnd, 31)
+        ae, be = rnd.choice([rnd.randrange(-80, 8), ri(rnd, 63)]), rnd.choice([rnd.randrange(-80, 8), ri(rnd, 63)])
+        om, oe = I64(), I64()
+        d.dev_combine(am, ae, bm, be, C.byref(om), C.byref(oe))
+        c = port.osc_combine(Scale(am, ae), Scale(bm, be))
+        assert (om.value, oe.value) == (c.m, c.e)
+
+
+def test_iexp_constants_and_elements(port):
+    d = devint.lib()
+    rnd = random.Random(5)
+    for _ in range(40000):
+        m = rnd.choice([rnd.randrange(1 << 30, 1 << 31), ri(rnd, 31)])
+        e = rnd.choice([rnd.randrange(-60, -25), rnd.randrange(-200, 100), ri(rnd, 63)])
+        a3, b3 = [I64() for _ in range(3)], [I64() for _ in range(3)]
+        sa = d.dev_iexp_scale_constants(m, e, *[C.byref(v) for v in a3])
+        sb = port.osc_iexp_scale_constants(m, e, *[C.byref(v) for v in b3])
+        assert (sa == 0) == (sb == 0)
+        if sa == 0:
+            assert [v.value for v in a3] == [v.value for v in b3]
+    # elements: constants that pass the width gate, shifted scores over the whole clip range
+    for _ in range(4000):
+        m, e = rnd.randrange(1 << 30, 1 << 31), rnd.randrange(-53, -30)
+        k = [I64() for _ in range(3)]
+        if port.osc_iexp_scale_constants(m, e, *[C.byref(v) for v in k]) != 0:
+            continue
+        ln2, qb, qc = [v.value for v in k]
+        pk = I64()
+        if not d.dev_softmax_width(qb, qc, 1, C.byref(pk)) or ln2 < 1:
+            continue
+        assert port.osc_softmax_width_domain(qb, qc, 1) == 0
+        for q in (0, -1, -ln2, -ln2 - 1, -29 * ln2, -30 * ln2, -30 * ln2 - 5, -(1 << 21), -rnd.randrange(0, 1 << 22)):
+            v1, v2 = I64(), I64()
+            ok = d.dev_iexp_element(q, ln2, qb, qc, pk.value, C.byref(v1))
+            dom = port.osc_iexp(q, ln2, qb, qc, None, None, C.byref(v2))
+            assert dom in (0, 4)
+            assert v1.value == v2.value
+            assert bool(ok) == (0 <= v2.value <= pk.value)
