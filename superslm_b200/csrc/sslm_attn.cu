@@ -1,14 +1,17 @@
 // Integer i-exp softmax attention over the paged int8 KV pool, staged through shared
-// memory. One thread block owns one (row, kv head); inside it ONE WARP owns one q head of
-// the GQA group, so the heads of a group run side by side with no block-level barrier and
-// each K / V byte of the sequence is fetched from HBM once per kv head (the other warps of
-// the block hit it in L1/L2).
+// memory, with both contractions on the tensor cores (mma.sync m16n8k32, exact int32
+// accumulation). One block of four warps owns one (row, kv head) and serves every q head
+// of the GQA group from one pass over the K and V pages, so each K / V byte of the
+// sequence leaves HBM once per kv head.
 //
-// Per warp (q head):
-//   pass 1  scores[k] = q_rot . K[k]   coalesced 16-byte K loads, dp4a, 3 shuffles per row
-//   pass 2  max, then total = sum_k e_k (e_k: second-order integer exp, SoftmaxRowQ15)
-//   pass 3  p_k = (e_k << 15) / total  exact division, stored over the score
-//   pass 4  ctx[d] = sum_k p_k V[k][d]  coalesced V loads, then the per-head fold and row max
+//   stage 1  scores[g][k] = q_rot[g] . K[k]      A = the group's q rows (heads in the M
+//            dimension), B = 8 K rows per MMA straight from the page (16-byte loads; the
+//            head-dim order inside an MMA is permuted identically on both operands)
+//   stage 2  e_k = second-order integer exp of (score - max); total; p_k = (e_k << 15) /
+//            total (SoftmaxRowQ15); p_k is split into two u8 planes, p = 256 ph + pl
+//   stage 3  ctx[g][d] = sum_k p_k V[k][d]       A = pl / ph (u8), B = transposed V page
+//            words (4 positions of one channel per register), two MMAs per plane, then
+//            ctx = acc_l + 256 acc_h, the per-head fold and the row max for the funnel
 //
 // Every reduction is an integer max or add, so the result does not depend on the order in
 // which lanes, warps or blocks contribute. Restates the attention block of RunLayerLoopImpl
@@ -20,140 +23,275 @@
 
 namespace sslm {
 
-__device__ __forceinline__ const int8_t* kv_row_ptr(const int8_t* plane, const int32_t* pages, int pos,
-                                                    int hd) {
-	return plane + ((int64_t)pages[pos / kPageTokens] * kPageTokens + (pos % kPageTokens)) * hd;
+constexpr int kAttnThreads = 128;
+constexpr int kAttnWarps = kAttnThreads / 32;
+
+// D += A(16x32, row) * B(32x8, col); rows 8..15 of A are always zero here (a1 = a3 = 0)
+__device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+	asm volatile(
+	    "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+	    : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+	    : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+	asm volatile(
+	    "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+	    : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+	    : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ int dot16(const int4& a, const int4& b) {
-	int acc = __dp4a(a.x, b.x, 0);
-	acc = __dp4a(a.y, b.y, acc);
-	acc = __dp4a(a.z, b.z, acc);
-	return __dp4a(a.w, b.w, acc);
-}
-
-// HD = head_dim (32, 64 or 128)
+// The HD/16 words of a head-dim row that lane column c (= lane & 3) feeds to the HD/32
+// score MMAs: MMA j takes words 2j (k slots 4c..4c+3) and 2j+1 (k slots 16+4c..). Any
+// assignment of head-dim bytes to k slots is valid as long as q and K use the same one.
 template <int HD>
-__global__ void __launch_bounds__(256)
-k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int width_pad) {
+__device__ __forceinline__ void load_row_words(const int8_t* row, int c, uint32_t (&w)[HD / 16]) {
+	if constexpr (HD == 32) {
+		const int2 x = __ldg((const int2*)(row + c * 8));
+		w[0] = (uint32_t)x.x; w[1] = (uint32_t)x.y;
+	} else {
+		const int4 x = __ldg((const int4*)(row + c * 16));
+		w[0] = (uint32_t)x.x; w[1] = (uint32_t)x.y; w[2] = (uint32_t)x.z; w[3] = (uint32_t)x.w;
+		if constexpr (HD == 128) {
+			const int4 y = __ldg((const int4*)(row + 64 + c * 16));
+			w[4] = (uint32_t)y.x; w[5] = (uint32_t)y.y; w[6] = (uint32_t)y.z; w[7] = (uint32_t)y.w;
+		}
+	}
+}
+
+struct AttnSmem {
+	int64_t* pbase;       // [wp/16] byte offset of each page inside a plane
+	int32_t* sc;          // [G][wp] scores
+	uint8_t* pl;          // [G][wp] low byte of the Q15 probability
+	uint8_t* ph;          // [G][wp] high byte
+	unsigned long long* red;   // [8][4] partials
+};
+__host__ __device__ inline size_t attn_smem_bytes(int group, int wp) {
+	return (size_t)wp / 16 * 8 + (size_t)group * wp * 6 + 8 * kAttnWarps * 8;
+}
+__device__ __forceinline__ AttnSmem carve(unsigned char* smem, int group, int wp) {
+	AttnSmem s;
+	s.pbase = (int64_t*)smem;
+	s.sc = (int32_t*)(smem + (size_t)wp / 16 * 8);
+	s.pl = (uint8_t*)(s.sc + (size_t)group * wp);
+	s.ph = s.pl + (size_t)group * wp;
+	s.red = (unsigned long long*)(s.ph + (size_t)group * wp);
+	return s;
+}
+
+// HD = head_dim (32, 64 or 128); wp = padded width, a multiple of 64
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads)
+k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int wp) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	const int r = blockIdx.y, kvh = blockIdx.x;
 	if (b.status[r] != 0) return;
-	const int group = d.heads / d.kv_heads;
-	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-	const int head = kvh * group + warp;               // one warp per q head
+	const int G = d.heads / d.kv_heads;
+	const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+	const int g = lane >> 2, c = lane & 3;
 	const int width = b.rows[r].pos + 1;
-	int32_t* sc = (int32_t*)smem + (size_t)warp * width_pad;   // this warp's scores / probabilities
+	const int w64 = (width + 63) & ~63;
+	const AttnSmem s = carve(smem, G, wp);
 
-	const int32_t* pages = b.rows[r].pages;
 	const int8_t* kplane = pool.base + kv_plane_offset(d, pool, layer_index, kvh, 0);
 	const int8_t* vplane = pool.base + kv_plane_offset(d, pool, layer_index, kvh, 1);
-	const int8_t* q = b.qrot + (size_t)r * d.hidden + (size_t)head * HD;
+	{
+		const int32_t* pages = b.rows[r].pages;
+		const int npages = (width + kPageTokens - 1) / kPageTokens;
+		for (int j = t; j < npages; j += kAttnThreads) s.pbase[j] = (int64_t)pages[j] * (kPageTokens * HD);
+	}
+	__syncthreads();
 
-	// ---- pass 1: scores. SL lanes share one K row (16 bytes each), RPI rows per load.
-	constexpr int SL = HD / 16, RPI = 32 / SL;
-	const int sl = lane % SL, sub = lane / SL;
-	const int4 qv = *((const int4*)q + sl);
-	int mx = INT32_MIN;
-	constexpr int U1 = 4;
-	for (int k0 = 0; k0 < width; k0 += RPI * U1) {
-		int4 kvv[U1];
+	// ---- stage 1: scores, 8 positions per MMA group, groups dealt round-robin to the warps
+	{
+		constexpr int NW = HD / 16;
+		uint32_t qw[NW];
 #pragma unroll
-		for (int u = 0; u < U1; ++u) {
-			const int k = k0 + u * RPI + sub;
-			kvv[u] = make_int4(0, 0, 0, 0);
-			if (k < width) kvv[u] = __ldg((const int4*)kv_row_ptr(kplane, pages, k, HD) + sl);
+		for (int j = 0; j < NW; ++j) qw[j] = 0;
+		if (g < G) load_row_words<HD>(b.qrot + (size_t)r * d.hidden + (size_t)(kvh * G + g) * HD, c, qw);
+		const int nblk = (width + 7) >> 3;
+		constexpr int U = 4;
+		for (int blk0 = warp * U; blk0 < nblk; blk0 += kAttnWarps * U) {
+			uint32_t kw[U][NW];
+#pragma unroll
+			for (int u = 0; u < U; ++u) {
+				const int pos = (blk0 + u) * 8 + g;
+#pragma unroll
+				for (int j = 0; j < NW; ++j) kw[u][j] = 0;
+				if (pos < width)
+					load_row_words<HD>(kplane + s.pbase[pos >> 4] + (pos & 15) * HD, c, kw[u]);
+			}
+#pragma unroll
+			for (int u = 0; u < U; ++u) {
+				int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+				for (int j = 0; j < NW / 2; ++j) mma_s8s8(acc, qw[2 * j], qw[2 * j + 1], kw[u][2 * j], kw[u][2 * j + 1]);
+				const int k = (blk0 + u) * 8 + c * 2;
+				if (g < G && blk0 + u < nblk) *(int2*)&s.sc[(size_t)g * wp + k] = make_int2(acc[0], acc[1]);
+			}
 		}
+	}
+	__syncthreads();
+
+	// ---- stage 2: softmax. Each thread takes 4 consecutive positions of every head.
+	const SoftmaxConsts smc = b.smc[(size_t)r * d.kv_heads + kvh];
+	int mx[8];
 #pragma unroll
-		for (int u = 0; u < U1; ++u) {
-			int s = dot16(kvv[u], qv);
+	for (int h = 0; h < 8; ++h) mx[h] = INT32_MIN;
+	for (int k4 = t * 4; k4 < width; k4 += kAttnThreads * 4) {
 #pragma unroll
-			for (int o = SL / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-			const int k = k0 + u * RPI + sub;
-			if (k < width) {
-				if (sl == 0) sc[k] = s;
-				mx = max(mx, s);
+		for (int h = 0; h < 8; ++h) {
+			if (h < G) {
+				const int4 v = *(const int4*)&s.sc[(size_t)h * wp + k4];
+				int m = v.x;
+				if (k4 + 1 < width) m = max(m, v.y);
+				if (k4 + 2 < width) m = max(m, v.z);
+				if (k4 + 3 < width) m = max(m, v.w);
+				mx[h] = max(mx[h], m);
+			}
+		}
+	}
+	int* redi = (int*)s.red;
+#pragma unroll
+	for (int h = 0; h < 8; ++h) {
+#pragma unroll
+		for (int o = 16; o > 0; o >>= 1) mx[h] = max(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
+		if (lane == 0) redi[h * kAttnWarps + warp] = mx[h];
+	}
+	__syncthreads();
+#pragma unroll
+	for (int h = 0; h < 8; ++h) {
+		int m = redi[h * kAttnWarps];
+#pragma unroll
+		for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[h * kAttnWarps + w]);
+		mx[h] = m;
+	}
+	__syncthreads();
+
+	unsigned long long tot[8];
+#pragma unroll
+	for (int h = 0; h < 8; ++h) tot[h] = 0;
+	bool bad = false;
+	for (int k4 = t * 4; k4 < width; k4 += kAttnThreads * 4) {
+#pragma unroll
+		for (int h = 0; h < 8; ++h) {
+			if (h < G) {
+				const int4 v = *(const int4*)&s.sc[(size_t)h * wp + k4];
+				const int sv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+				for (int j = 0; j < 4; ++j) {
+					int64_t e;
+					const bool ok = iexp_element((int64_t)sv[j] - mx[h], smc.c, smc.peak, &e);
+					if (k4 + j < width) {
+						tot[h] += ok ? (unsigned long long)e : 0ull;
+						bad |= !ok;
+					}
+				}
 			}
 		}
 	}
 #pragma unroll
-	for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-	__syncwarp();
-
-	// ---- pass 2: total of the integer exponentials
-	const SoftmaxConsts smc = b.smc[(size_t)r * d.kv_heads + kvh];
-	unsigned long long tot = 0;
-	bool bad = false;
-	for (int k = lane; k < width; k += 32) {
-		int64_t e;
-		if (iexp_element((int64_t)sc[k] - mx, smc.c, smc.peak, &e)) tot += (unsigned long long)e;
-		else bad = true;
-	}
+	for (int h = 0; h < 8; ++h) {
 #pragma unroll
-	for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-	if (__any_sync(0xffffffffu, bad)) {
+		for (int o = 16; o > 0; o >>= 1) tot[h] += __shfl_xor_sync(0xffffffffu, tot[h], o);
+		if (lane == 0) s.red[h * kAttnWarps + warp] = tot[h];
+	}
+	if (__syncthreads_or(bad ? 1 : 0)) {
 		// the reference refuses the row (SoftmaxKernelRefusedAfterGateAccepted)
-		if (lane == 0) atomicCAS(&b.status[r], 0, kSoftmaxKernelRefused);
+		if (t == 0) atomicCAS(&b.status[r], 0, kSoftmaxKernelRefused);
 		return;
 	}
-	// ---- pass 3: Q15 probabilities in place of the scores
-	const unsigned long long den = tot > 1ull ? tot : 1ull;
-	const double inv = 1.0 / (double)den;
-	for (int k = lane; k < width; k += 32) {
-		int64_t e;
-		iexp_element((int64_t)sc[k] - mx, smc.c, smc.peak, &e);
-		sc[k] = (int32_t)udiv_small_quotient((uint64_t)e << 15, den, inv);
-	}
-	__syncwarp();
-
-	// ---- pass 4: ctx = P V. DL lanes share one V row (4 head-dim elements each).
-	constexpr int DL = HD / 4, RPV = 32 / DL;
-	const int dl = lane % DL, vsub = lane / DL;
-	int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-	constexpr int U4 = 8;
-	for (int k0 = 0; k0 < width; k0 += RPV * U4) {
-		int vv[U4], pp[U4];
+	double inv[8];
 #pragma unroll
-		for (int u = 0; u < U4; ++u) {
-			const int k = k0 + u * RPV + vsub;
-			vv[u] = 0;
-			pp[u] = 0;
-			if (k < width) {
-				vv[u] = __ldg((const int*)kv_row_ptr(vplane, pages, k, HD) + dl);
-				pp[u] = sc[k];
+	for (int h = 0; h < 8; ++h) {
+		unsigned long long x = 0;
+#pragma unroll
+		for (int w = 0; w < kAttnWarps; ++w) x += s.red[h * kAttnWarps + w];
+		tot[h] = x > 1ull ? x : 1ull;
+		inv[h] = 1.0 / (double)tot[h];
+	}
+	// probabilities, zero beyond the width up to the next multiple of 64 (stage 3 reads whole pages)
+	for (int k4 = t * 4; k4 < w64; k4 += kAttnThreads * 4) {
+#pragma unroll
+		for (int h = 0; h < 8; ++h) {
+			if (h < G) {
+				const int4 v = *(const int4*)&s.sc[(size_t)h * wp + k4];
+				const int sv[4] = {v.x, v.y, v.z, v.w};
+				uint32_t lo = 0, hi = 0;
+#pragma unroll
+				for (int j = 0; j < 4; ++j) {
+					if (k4 + j < width) {
+						int64_t e;
+						iexp_element((int64_t)sv[j] - mx[h], smc.c, smc.peak, &e);
+						const uint32_t p = (uint32_t)udiv_small_quotient((uint64_t)e << 15, tot[h], inv[h]);
+						lo |= (p & 0xffu) << (8 * j);
+						hi |= (p >> 8) << (8 * j);
+					}
+				}
+				*(uint32_t*)&s.pl[(size_t)h * wp + k4] = lo;
+				*(uint32_t*)&s.ph[(size_t)h * wp + k4] = hi;
+			}
+		}
+	}
+	__syncthreads();
+
+	// ---- stage 3: ctx = P V. Lane column c owns page 4*grp + c of each 64-position group;
+	// its 16-byte row of the transposed page feeds two MMAs (positions 0..7 and 8..15).
+	constexpr int NDB = HD / 32;      // 8-channel blocks per warp
+	int accl[NDB][4], acch[NDB][4];
+#pragma unroll
+	for (int i = 0; i < NDB; ++i)
+#pragma unroll
+		for (int j = 0; j < 4; ++j) accl[i][j] = acch[i][j] = 0;
+	const int ngrp = w64 >> 6;
+	constexpr int UG = 2;
+	for (int grp0 = 0; grp0 < ngrp; grp0 += UG) {
+		int4 vv[UG][NDB];
+		int4 al[UG], ah[UG];
+#pragma unroll
+		for (int u = 0; u < UG; ++u) {
+			const int page = (grp0 + u) * 4 + c;
+			const bool live = page * kPageTokens < width;
+			al[u] = ah[u] = make_int4(0, 0, 0, 0);
+			if (g < G && live) {
+				al[u] = *(const int4*)&s.pl[(size_t)g * wp + page * kPageTokens];
+				ah[u] = *(const int4*)&s.ph[(size_t)g * wp + page * kPageTokens];
+			}
+#pragma unroll
+			for (int i = 0; i < NDB; ++i) {
+				vv[u][i] = make_int4(0, 0, 0, 0);
+				if (live) {
+					const int ch = (warp * NDB + i) * 8 + g;
+					vv[u][i] = __ldg((const int4*)(vplane + s.pbase[page] + ch * kPageTokens));
+				}
 			}
 		}
 #pragma unroll
-		for (int u = 0; u < U4; ++u) {
-			const int x = vv[u], p = pp[u];
-			c0 += p * (int)(int8_t)(x & 0xff);
-			c1 += p * (int)(int8_t)((x >> 8) & 0xff);
-			c2 += p * (int)(int8_t)((x >> 16) & 0xff);
-			c3 += p * (x >> 24);
+		for (int u = 0; u < UG; ++u) {
+#pragma unroll
+			for (int i = 0; i < NDB; ++i) {
+				const int4 v = vv[u][i];
+				mma_u8s8(accl[i], (uint32_t)al[u].x, (uint32_t)al[u].y, (uint32_t)v.x, (uint32_t)v.y);
+				mma_u8s8(accl[i], (uint32_t)al[u].z, (uint32_t)al[u].w, (uint32_t)v.z, (uint32_t)v.w);
+				mma_u8s8(acch[i], (uint32_t)ah[u].x, (uint32_t)ah[u].y, (uint32_t)v.x, (uint32_t)v.y);
+				mma_u8s8(acch[i], (uint32_t)ah[u].z, (uint32_t)ah[u].w, (uint32_t)v.z, (uint32_t)v.w);
+			}
 		}
 	}
-#pragma unroll
-	for (int o = 16; o >= DL; o >>= 1) {
-		c0 += __shfl_xor_sync(0xffffffffu, c0, o);
-		c1 += __shfl_xor_sync(0xffffffffu, c1, o);
-		c2 += __shfl_xor_sync(0xffffffffu, c2, o);
-		c3 += __shfl_xor_sync(0xffffffffu, c3, o);
-	}
 	// per-head context fold (forward_sites.cpp:1889-1896), store, row max for the funnel
-	const int32_t fi = layer->f_ctx[3 * head], fm = layer->f_ctx[3 * head + 1], fs = layer->f_ctx[3 * head + 2];
 	uint32_t lmax = 0;
-	if (vsub == 0) {
-		int4 o4;
-		o4.x = fold(c0, fi, fm, fs);
-		o4.y = fold(c1, fi, fm, fs);
-		o4.z = fold(c2, fi, fm, fs);
-		o4.w = fold(c3, fi, fm, fs);
-		*((int4*)(b.ctxw + (size_t)r * d.hidden + (size_t)head * HD) + dl) = o4;
-		const int vals[4] = {o4.x, o4.y, o4.z, o4.w};
+	if (g < G) {
+		const int head = kvh * G + g;
+		const int32_t fi = layer->f_ctx[3 * head], fm = layer->f_ctx[3 * head + 1], fs = layer->f_ctx[3 * head + 2];
 #pragma unroll
-		for (int j = 0; j < 4; ++j) {
-			const uint32_t ab = vals[j] < 0 ? 0u - (uint32_t)vals[j] : (uint32_t)vals[j];
-			lmax = ab > lmax ? ab : lmax;
+		for (int i = 0; i < NDB; ++i) {
+			int2 o;
+			o.x = fold(accl[i][0] + 256 * acch[i][0], fi, fm, fs);
+			o.y = fold(accl[i][1] + 256 * acch[i][1], fi, fm, fs);
+			const int ch = (warp * NDB + i) * 8 + c * 2;
+			*(int2*)(b.ctxw + (size_t)r * d.hidden + (size_t)head * HD + ch) = o;
+			const uint32_t ax = o.x < 0 ? 0u - (uint32_t)o.x : (uint32_t)o.x;
+			const uint32_t ay = o.y < 0 ? 0u - (uint32_t)o.y : (uint32_t)o.y;
+			lmax = max(lmax, max(ax, ay));
 		}
 	}
 #pragma unroll
@@ -161,14 +299,13 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	if (lane == 0 && lmax) atomicMax(&b.rowmax[(size_t)r * 4 + 3], (unsigned long long)lmax);
 }
 
-static int pad_width(int w) { return (w + 31) / 32 * 32 + 4; }
-static size_t attn_smem(const Dims& d, int width_pad) {
-	return (size_t)(d.heads / d.kv_heads) * width_pad * 4;
-}
+static int pad_width(int w) { return (w + 63) / 64 * 64; }
 
 cudaError_t attn_configure(const Dims& d) {
-	const size_t need = attn_smem(d, pad_width(d.context_cap));
-	if (need > 227 * 1024 || d.heads / d.kv_heads > 8) return cudaErrorInvalidConfiguration;
+	const int group = d.heads / d.kv_heads;
+	if (group < 1 || group > 8 || d.heads % d.kv_heads != 0) return cudaErrorInvalidConfiguration;
+	const size_t need = attn_smem_bytes(group, pad_width(d.context_cap));
+	if (need > 227 * 1024) return cudaErrorInvalidConfiguration;
 	const int n = (int)need;
 	if (d.head_dim == 128) return cudaFuncSetAttribute(k_attention<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, n);
 	if (d.head_dim == 64) return cudaFuncSetAttribute(k_attention<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, n);
@@ -180,14 +317,16 @@ void launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, i
                       KvPoolDev pool, int max_width, cudaStream_t st) {
 	const int wp = pad_width(max_width);
 	const dim3 grid(d.kv_heads, b.m);
-	const int threads = 32 * (d.heads / d.kv_heads);
-	const size_t sm = attn_smem(d, wp);
-	if (d.head_dim == 128) k_attention<128><<<grid, threads, sm, st>>>(b, d, layer, layer_index, pool, wp);
-	else if (d.head_dim == 64) k_attention<64><<<grid, threads, sm, st>>>(b, d, layer, layer_index, pool, wp);
-	else k_attention<32><<<grid, threads, sm, st>>>(b, d, layer, layer_index, pool, wp);
+	const size_t sm = attn_smem_bytes(d.heads / d.kv_heads, wp);
+	if (d.head_dim == 128) k_attention<128><<<grid, kAttnThreads, sm, st>>>(b, d, layer, layer_index, pool, wp);
+	else if (d.head_dim == 64) k_attention<64><<<grid, kAttnThreads, sm, st>>>(b, d, layer, layer_index, pool, wp);
+	else k_attention<32><<<grid, kAttnThreads, sm, st>>>(b, d, layer, layer_index, pool, wp);
 }
 
 // ------------------------------------------------------------ canonical KV export
+// Writes the sequence's K and V in the reference's save layout, [layer][K|V][kv head]
+// [context_cap][head_dim] with zeros past the valid positions, undoing the paging and the
+// V-page transposition.
 __global__ void k_kv_export(Dims d, KvPoolDev pool, const int32_t* pages, int context_length,
                             int layer_index, int8_t* out) {
 	const int hd = d.head_dim, vec = hd / 16;
@@ -204,8 +343,17 @@ __global__ void k_kv_export(Dims d, KvPoolDev pool, const int32_t* pages, int co
 		const int valid = context_length + (layer < layer_index ? 1 : 0);
 		int4 val = make_int4(0, 0, 0, 0);
 		if (pos < valid) {
-			const int8_t* src = pool.base + kv_plane_offset(d, pool, layer, kvh, is_v);
-			val = *((const int4*)kv_row_ptr(src, pages, pos, hd) + v);
+			const int8_t* src = pool.base + kv_plane_offset(d, pool, layer, kvh, is_v) +
+			                    (int64_t)pages[pos / kPageTokens] * (kPageTokens * hd);
+			const int slot = pos % kPageTokens;
+			if (!is_v) {
+				val = *((const int4*)(src + slot * hd) + v);
+			} else {
+				uint32_t w[4] = {0, 0, 0, 0};
+				for (int j = 0; j < 16; ++j)
+					w[j >> 2] |= (uint32_t)(uint8_t)src[(v * 16 + j) * kPageTokens + slot] << (8 * (j & 3));
+				val = make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]);
+			}
 		}
 		((int4*)out)[i] = val;
 	}

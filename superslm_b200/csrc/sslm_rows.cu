@@ -211,8 +211,10 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		                                     lw.v_recip[3 * h + 2], ns.e, lw.v_recip[3 * h + 1], &s2, nullptr);
 		sat += (s1 ? 1 : 0) + (s2 ? 1 : 0);
 		sk[i] = (int8_t)clamp127(kraw);
+		// V pages are stored transposed ([head_dim][16 positions]) so that the attention
+		// kernel can feed them to the tensor cores as the K-major operand of P.V
 		int8_t* vdst = pool.base + kv_plane_offset(d, pool, layer_index, h, 1) +
-		               ((int64_t)page * kPageTokens + slot) * hd + dd;
+		               ((int64_t)page * hd + dd) * kPageTokens + slot;
 		*vdst = (int8_t)clamp127(vraw);
 	}
 	sat = block_sum_i64(sat, red);   // also orders the sq / sk writes before the reads below
@@ -379,16 +381,22 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 }
 
 // gate / up funnels -> SwiGLU activation site (MlpActSite, forward_sites.cpp:796-864)
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(kRowThreads, 4)
 k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
-	int32_t* tab = (int32_t*)(smem + 34 * 8);          // 1025 entries, padded to 1028
+	int32_t* tab = (int32_t*)(smem + 36 * 8);          // 1025 entries, padded to 1028
 	int32_t* wide = tab + 1028;                         // inter
 	const int r = blockIdx.x, n = d.inter;
 	for (int i = threadIdx.x; i < 1025; i += blockDim.x) tab[i] = silu_table[i];
-	const unsigned long long mxg = take_rowmax(b, r, 1, red);
-	const unsigned long long mxu = take_rowmax(b, r, 2, red);
+	if (threadIdx.x == 0) {
+		red[33] = b.rowmax[r * 4 + 1];
+		red[34] = b.rowmax[r * 4 + 2];
+		b.rowmax[r * 4 + 1] = 0ull;
+		b.rowmax[r * 4 + 2] = 0ull;
+	}
+	__syncthreads();
+	const unsigned long long mxg = red[33], mxu = red[34];
 	if (b.status[r] != 0) return;
 	const LayerDev& lw = *layer;
 	const Scale ns = b.ns[r];
@@ -401,16 +409,59 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 		return;
 	}
 	const int ge = (int)fg.out.e;
-	for (int i = threadIdx.x; i < n; i += blockDim.x) {
-		const int g = requant_code(load_wide(b, r, i), fg.r, fg.s);
-		const int u = requant_code(load_wide(b, r, n + i), fu.r, fu.s);
-		const int32_t sig = silu_sigmoid_q15(tab, g, fg.out.m, ge);
-		wide[i] = g * sig * u;   // |.| <= 127 * 2^15 * 127 < 2^29
+	// products g * sigmoid(g) * u, |.| <= 127 * 2^15 * 127 < 2^29, staged in shared memory
+	// with their running maximum so that the funnel below needs no second pass for it
+	uint32_t lmax = 0;
+	const bool vec = !b.wide64 && (n & 3) == 0 && (b.wide_ld & 3) == 0;
+	if (vec) {
+		const int4* gp = (const int4*)((const int32_t*)b.wide + (size_t)r * b.wide_ld);
+		const int4* up = gp + (n >> 2);
+#pragma unroll 2
+		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+			const int4 gv = gp[i], uv = up[i];
+			const int gs[4] = {gv.x, gv.y, gv.z, gv.w}, us[4] = {uv.x, uv.y, uv.z, uv.w};
+			int pr[4];
+#pragma unroll
+			for (int j = 0; j < 4; ++j) {
+				const int g = requant_code((int64_t)gs[j], fg.r, fg.s);
+				const int u = requant_code((int64_t)us[j], fu.r, fu.s);
+				pr[j] = g * silu_sigmoid_q15(tab, g, fg.out.m, ge) * u;
+				const uint32_t a = pr[j] < 0 ? 0u - (uint32_t)pr[j] : (uint32_t)pr[j];
+				lmax = a > lmax ? a : lmax;
+			}
+			((int4*)wide)[i] = make_int4(pr[0], pr[1], pr[2], pr[3]);
+		}
+	} else {
+		for (int i = threadIdx.x; i < n; i += blockDim.x) {
+			const int g = requant_code(load_wide(b, r, i), fg.r, fg.s);
+			const int u = requant_code(load_wide(b, r, n + i), fu.r, fu.s);
+			const int p = g * silu_sigmoid_q15(tab, g, fg.out.m, ge) * u;
+			wide[i] = p;
+			const uint32_t a = p < 0 ? 0u - (uint32_t)p : (uint32_t)p;
+			lmax = a > lmax ? a : lmax;
+		}
 	}
-	__syncthreads();
+	const unsigned long long mx = block_max_u64((unsigned long long)lmax, red);
 	const Scale inc[2] = {fg.out, fu.out};
-	st = block_funnel<int32_t>(wide, n, inc, 2, lw.c_act, b.act + (size_t)r * n, nullptr, &b.acts[r], red);
-	set_status(b, r, st);
+	const FunnelParams fp = funnel_params(mx, inc, 2, lw.c_act);
+	if (fp.status != kOk) {
+		set_status(b, r, fp.status);
+		return;
+	}
+	int8_t* out = b.act + (size_t)r * n;
+	if ((n & 3) == 0) {
+		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+			const int4 p = ((const int4*)wide)[i];
+			const uint32_t c0 = (uint8_t)requant_code((int64_t)p.x, fp.r, fp.s);
+			const uint32_t c1 = (uint8_t)requant_code((int64_t)p.y, fp.r, fp.s);
+			const uint32_t c2 = (uint8_t)requant_code((int64_t)p.z, fp.r, fp.s);
+			const uint32_t c3 = (uint8_t)requant_code((int64_t)p.w, fp.r, fp.s);
+			((uint32_t*)out)[i] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+		}
+	} else {
+		for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = requant_code((int64_t)wide[i], fp.r, fp.s);
+	}
+	if (threadIdx.x == 0) b.acts[r] = fp.out;
 }
 
 // End of a call: hand each row's stream back to its sequence (or nowhere).
@@ -449,13 +500,13 @@ void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const 
                  cudaStream_t st) {
 	k_res2<<<b.m, kRowThreads, smem_wide(d) + 2 * d.hidden, st>>>(b, d, layer, next);
 }
-size_t act_smem_bytes(const Dims& d) { return 34 * 8 + 1028 * 4 + (size_t)d.inter * 4; }
+size_t act_smem_bytes(const Dims& d) { return 36 * 8 + 1028 * 4 + (size_t)d.inter * 4; }
 cudaError_t rows_configure(const Dims& d) {
 	return cudaFuncSetAttribute(k_act, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)act_smem_bytes(d));
 }
 void launch_act(const RowBatch& b, const Dims& d, const LayerDev* layer, const int32_t* silu,
                 cudaStream_t st) {
-	k_act<<<b.m, 1024, act_smem_bytes(d), st>>>(b, d, layer, silu);
+	k_act<<<b.m, kRowThreads, act_smem_bytes(d), st>>>(b, d, layer, silu);
 }
 void launch_scatter(const RowBatch& b, const Dims& d, const RowSink* sink, cudaStream_t st) {
 	k_scatter<<<b.m, kRowThreads, 0, st>>>(b, d, sink);

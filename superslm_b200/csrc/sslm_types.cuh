@@ -52,8 +52,11 @@ struct Dims {
 	int qkv_rows;    // hidden + 2*kv_hidden
 };
 
-// Paged KV pool: [layer][kv_head][K|V][page][16][head_dim] int8. A page id names the
-// same slot in every (layer, kv head, K|V) plane, so one page table serves all layers.
+// Paged KV pool: [layer][kv_head][K|V][page] int8 pages of 16 positions. A K page is
+// [16][head_dim] (one row per position); a V page is stored transposed, [head_dim][16],
+// so that 4 consecutive positions of one channel are one 32-bit word: the K-major operand
+// the tensor cores want for P.V. A page id names the same slot in every (layer, kv head,
+// K|V) plane, so one page table serves all layers.
 struct KvPoolDev {
 	int8_t* base;
 	int64_t num_pages;

@@ -57,6 +57,15 @@ def test_floor_div_and_isqrt(port):
         assert d.dev_floor_div(a, b) == port.osc_floor_div(a, b)
         n = rnd.choice([rnd.randrange(0, 1 << 62), rnd.randrange(0, 1 << 40), rnd.randrange(0, 100)])
         assert d.dev_isqrt(n) == port.osc_isqrt(n)
+    for _ in range(20000):      # perfect squares and their neighbours, up to the int64 ceiling
+        k = rnd.choice([rnd.randrange(0, 3037000500), rnd.randrange(3037000000, 3037000500), rnd.randrange(0, 1 << 16)])
+        for n in (k * k - 1, k * k, k * k + 1, k * k + k, k * k + 2 * k):
+            if 0 <= n < (1 << 63):
+                assert d.dev_isqrt(n) == port.osc_isqrt(n), n
+    for n in ((1 << 63) - 1, (1 << 62), (1 << 62) - 1, 0, 1, 2, 3, -1, -(1 << 40)):
+        assert d.dev_isqrt(n) == port.osc_isqrt(n), n
+    for dn in ((1 << 30), (1 << 30) + 1, (1 << 31) - 1, (1 << 31), (1 << 30) - 1, 3 << 29, (3 << 29) + 1):
+        assert d.dev_dyn_recip(dn) == port.osc_dyn_recip(dn), dn
     for den in (1, 2, 3, 1 << 40, (1 << 62) - 1):
         for q in (0, 1, 2, 32767, 32768, 65535):
             for rem in (0, 1, den - 1):
