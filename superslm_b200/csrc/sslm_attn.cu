@@ -1,6 +1,6 @@
 // Integer i-exp softmax attention over the paged int8 KV pool, staged through shared
 // memory, with both contractions on the tensor cores (mma.sync m16n8k32, exact int32
-// accumulation). One block of four warps owns one (row, kv head) and serves every q head
+// accumulation). One block of head_dim/16 warps owns one (row, kv head) and serves every q head
 // of the GQA group from one pass over the K and V pages, so each K / V byte of the
 // sequence leaves HBM once per kv head.
 //
@@ -23,8 +23,49 @@
 
 namespace sslm {
 
-constexpr int kAttnThreads = 128;
-constexpr int kAttnWarps = kAttnThreads / 32;
+// threads per block = 2 * head_dim: one warp per pair of 8-channel blocks of P.V
+constexpr int kAttnMaxWarps = 8;
+
+// One softmax element for constants that passed the gates of k_qkv_post (1 <= q_ln2 <= q_b
+// < 2^24, q_c >= 0): the value iexp_element() computes, on 32-bit words. dq = max - score
+// (0 <= dq < 2^32). z = floor(x / q_ln2) comes from a float estimate repaired with the
+// exact remainder.
+struct IExpFast {
+	uint32_t ln2, clip;     // q_ln2, 30 * q_ln2
+	int32_t qb;
+	int64_t qc, peak;
+	float inv_ln2;
+};
+__device__ __forceinline__ IExpFast iexp_fast_prepare(const SoftmaxConsts& k) {
+	IExpFast f;
+	f.ln2 = (uint32_t)k.c.q_ln2;
+	f.clip = 30u * f.ln2;
+	f.qb = (int32_t)k.c.q_b;
+	f.qc = k.c.q_c;
+	f.peak = k.peak;
+	f.inv_ln2 = 1.0f / (float)f.ln2;
+	return f;
+}
+__device__ __forceinline__ bool iexp_fast(uint32_t dq, const IExpFast& f, int64_t* value) {
+	const uint32_t x = dq < f.clip ? dq : f.clip;
+	int32_t z = (int32_t)((float)x * f.inv_ln2);
+	int32_t rem = (int32_t)(x - (uint32_t)z * f.ln2);
+	if (rem < 0) { --z; rem += (int32_t)f.ln2; }
+	if (rem >= (int32_t)f.ln2) { ++z; rem -= (int32_t)f.ln2; }
+	const int32_t base = f.qb - rem;
+	const int64_t v = ((int64_t)base * (int64_t)base + f.qc) >> z;
+	*value = v;
+	return f.peak >= 1 && v >= 0 && v <= f.peak;
+}
+// floor((e << 15) / tot) for 0 <= e <= tot, tot >= 1: float estimate (within 1), exact repair
+__device__ __forceinline__ uint32_t prob_q15(int64_t e, unsigned long long tot, float rinv) {
+	const unsigned long long num = (unsigned long long)e << 15;
+	unsigned long long p = (unsigned long long)((float)e * rinv);
+	if (p > 32768ull) p = 32768ull;
+	while (p * tot > num) --p;
+	while (num - p * tot >= tot) ++p;
+	return (uint32_t)p;
+}
 
 // D += A(16x32, row) * B(32x8, col); rows 8..15 of A are always zero here (a1 = a3 = 0)
 __device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
@@ -63,10 +104,10 @@ struct AttnSmem {
 	int32_t* sc;          // [G][wp] scores
 	uint8_t* pl;          // [G][wp] low byte of the Q15 probability
 	uint8_t* ph;          // [G][wp] high byte
-	unsigned long long* red;   // [8][4] partials
+	unsigned long long* red;   // [8 heads][warps] partials
 };
 __host__ __device__ inline size_t attn_smem_bytes(int group, int wp) {
-	return (size_t)wp / 16 * 8 + (size_t)group * wp * 6 + 8 * kAttnWarps * 8;
+	return (size_t)wp / 16 * 8 + (size_t)group * wp * 6 + 8 * kAttnMaxWarps * 8;
 }
 __device__ __forceinline__ AttnSmem carve(unsigned char* smem, int group, int wp) {
 	AttnSmem s;
@@ -80,11 +121,12 @@ __device__ __forceinline__ AttnSmem carve(unsigned char* smem, int group, int wp
 
 // HD = head_dim (32, 64 or 128); wp = padded width, a multiple of 64
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(2 * HD, HD == 128 ? 4 : 8)
 k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int wp) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	const int r = blockIdx.y, kvh = blockIdx.x;
 	if (b.status[r] != 0) return;
+	constexpr int kAttnThreads = 2 * HD, kAttnWarps = kAttnThreads / 32;
 	const int G = d.heads / d.kv_heads;
 	const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
 	const int g = lane >> 2, c = lane & 3;
@@ -133,7 +175,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	__syncthreads();
 
 	// ---- stage 2: softmax. Each thread takes 4 consecutive positions of every head.
-	const SoftmaxConsts smc = b.smc[(size_t)r * d.kv_heads + kvh];
+	const IExpFast fx = iexp_fast_prepare(b.smc[(size_t)r * d.kv_heads + kvh]);
 	int mx[8];
 #pragma unroll
 	for (int h = 0; h < 8; ++h) mx[h] = INT32_MIN;
@@ -180,7 +222,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 #pragma unroll
 				for (int j = 0; j < 4; ++j) {
 					int64_t e;
-					const bool ok = iexp_element((int64_t)sv[j] - mx[h], smc.c, smc.peak, &e);
+					const bool ok = iexp_fast((uint32_t)mx[h] - (uint32_t)sv[j], fx, &e);
 					if (k4 + j < width) {
 						tot[h] += ok ? (unsigned long long)e : 0ull;
 						bad |= !ok;
@@ -200,14 +242,14 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		if (t == 0) atomicCAS(&b.status[r], 0, kSoftmaxKernelRefused);
 		return;
 	}
-	double inv[8];
+	float inv[8];
 #pragma unroll
 	for (int h = 0; h < 8; ++h) {
 		unsigned long long x = 0;
 #pragma unroll
 		for (int w = 0; w < kAttnWarps; ++w) x += s.red[h * kAttnWarps + w];
 		tot[h] = x > 1ull ? x : 1ull;
-		inv[h] = 1.0 / (double)tot[h];
+		inv[h] = 32768.0f / (float)tot[h];
 	}
 	// probabilities, zero beyond the width up to the next multiple of 64 (stage 3 reads whole pages)
 	for (int k4 = t * 4; k4 < w64; k4 += kAttnThreads * 4) {
@@ -221,8 +263,8 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 				for (int j = 0; j < 4; ++j) {
 					if (k4 + j < width) {
 						int64_t e;
-						iexp_element((int64_t)sv[j] - mx[h], smc.c, smc.peak, &e);
-						const uint32_t p = (uint32_t)udiv_small_quotient((uint64_t)e << 15, tot[h], inv[h]);
+						iexp_fast((uint32_t)mx[h] - (uint32_t)sv[j], fx, &e);
+						const uint32_t p = prob_q15(e, tot[h], inv[h]);
 						lo |= (p & 0xffu) << (8 * j);
 						hi |= (p >> 8) << (8 * j);
 					}
@@ -236,7 +278,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 
 	// ---- stage 3: ctx = P V. Lane column c owns page 4*grp + c of each 64-position group;
 	// its 16-byte row of the transposed page feeds two MMAs (positions 0..7 and 8..15).
-	constexpr int NDB = HD / 32;      // 8-channel blocks per warp
+	constexpr int NDB = 2;            // 8-channel blocks per warp
 	int accl[NDB][4], acch[NDB][4];
 #pragma unroll
 	for (int i = 0; i < NDB; ++i)
@@ -300,6 +342,11 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 }
 
 static int pad_width(int w) { return (w + 63) / 64 * 64; }
+template <int HD>
+static void launch_attn(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index, KvPoolDev pool,
+                        int wp, size_t sm, cudaStream_t st) {
+	k_attention<HD><<<dim3(d.kv_heads, b.m), 2 * HD, sm, st>>>(b, d, layer, layer_index, pool, wp);
+}
 
 cudaError_t attn_configure(const Dims& d) {
 	const int group = d.heads / d.kv_heads;
@@ -307,20 +354,24 @@ cudaError_t attn_configure(const Dims& d) {
 	const size_t need = attn_smem_bytes(group, pad_width(d.context_cap));
 	if (need > 227 * 1024) return cudaErrorInvalidConfiguration;
 	const int n = (int)need;
-	if (d.head_dim == 128) return cudaFuncSetAttribute(k_attention<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, n);
-	if (d.head_dim == 64) return cudaFuncSetAttribute(k_attention<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, n);
-	if (d.head_dim == 32) return cudaFuncSetAttribute(k_attention<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, n);
-	return cudaErrorInvalidConfiguration;
+	const void* f = nullptr;
+	if (d.head_dim == 128) f = (const void*)k_attention<128>;
+	else if (d.head_dim == 64) f = (const void*)k_attention<64>;
+	else if (d.head_dim == 32) f = (const void*)k_attention<32>;
+	else return cudaErrorInvalidConfiguration;
+	cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, n);
+	if (e != cudaSuccess) return e;
+	// same carve-out as the kernels around it (see rows_configure)
+	return cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
 void launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
                       KvPoolDev pool, int max_width, cudaStream_t st) {
 	const int wp = pad_width(max_width);
-	const dim3 grid(d.kv_heads, b.m);
 	const size_t sm = attn_smem_bytes(d.heads / d.kv_heads, wp);
-	if (d.head_dim == 128) k_attention<128><<<grid, kAttnThreads, sm, st>>>(b, d, layer, layer_index, pool, wp);
-	else if (d.head_dim == 64) k_attention<64><<<grid, kAttnThreads, sm, st>>>(b, d, layer, layer_index, pool, wp);
-	else k_attention<32><<<grid, kAttnThreads, sm, st>>>(b, d, layer, layer_index, pool, wp);
+	if (d.head_dim == 128) launch_attn<128>(b, d, layer, layer_index, pool, wp, sm, st);
+	else if (d.head_dim == 64) launch_attn<64>(b, d, layer, layer_index, pool, wp, sm, st);
+	else launch_attn<32>(b, d, layer, layer_index, pool, wp, sm, st);
 }
 
 // ------------------------------------------------------------ canonical KV export

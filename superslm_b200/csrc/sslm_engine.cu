@@ -383,6 +383,14 @@ sslm_workspace_s* create_workspace(sslm_model_s* model, const sslm_config& cfg, 
 	ok = ok && cuda_ok(cudaMalloc((void**)&w->d_src, rows * sizeof(RowSource)));
 	ok = ok && cuda_ok(cudaMalloc((void**)&w->d_sink, rows * sizeof(RowSink)));
 	ok = ok && cuda_ok(cudaEventCreate(&w->ev0)) && cuda_ok(cudaEventCreate(&w->ev1));
+	if (ok && rows > 8) {
+		// K slices times tiles never exceeds the SM count, and a tile is at most 256 x 64
+		// accumulators, so 16 MiB holds every case the tensor-core path picks
+		w->tc_partial_bytes = (size_t)16 << 20;
+		ok = cuda_ok(cudaMalloc((void**)&w->d_tc_partial, w->tc_partial_bytes));
+		ok = ok && cuda_ok(cudaMalloc((void**)&w->d_tc_counters, kTcTileCounters * sizeof(unsigned int)));
+		ok = ok && cuda_ok(cudaMemset(w->d_tc_counters, 0, kTcTileCounters * sizeof(unsigned int)));
+	}
 	if (!ok) {
 		destroy_workspace(w);
 		return nullptr;
@@ -399,6 +407,8 @@ static void destroy_workspace(sslm_workspace_s* w) {
 	cudaSetDevice(w->device);
 	if (w->stream) cudaStreamSynchronize(w->stream);
 	cudaFree(w->d_scratch);
+	cudaFree(w->d_tc_partial);
+	cudaFree(w->d_tc_counters);
 	cudaFree(w->d_rows);
 	cudaFree(w->d_src);
 	cudaFree(w->d_sink);

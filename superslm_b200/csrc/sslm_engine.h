@@ -24,6 +24,8 @@ struct DeviceArena {
 	}
 };
 
+constexpr int kTcTileCounters = 1024;
+
 struct sslm_workspace_s {
 	sslm_model_s* model = nullptr;
 	sslm_config config{};
@@ -46,6 +48,11 @@ struct sslm_workspace_s {
 	// carved row buffers (base pointers for row 0)
 	sslm::RowBatch base{};
 	size_t wide_ld = 0;
+	// split-K scratch of the tensor-core linear kernel: parked partial accumulators and one
+	// arrival counter per output tile (zero between launches)
+	int32_t* d_tc_partial = nullptr;
+	size_t tc_partial_bytes = 0;
+	unsigned int* d_tc_counters = nullptr;
 	int32_t* logit_capture = nullptr;   // host buffer for full logit rows (tests), or nullptr
 	int32_t* d_logits = nullptr;
 	cudaEvent_t ev0 = nullptr, ev1 = nullptr;

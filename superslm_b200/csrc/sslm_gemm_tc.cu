@@ -26,6 +26,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -205,12 +206,17 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 	uint32_t* tmem_slot = (uint32_t*)(smem + S * Cfg::kStageBytes + Cfg::kFoldBytes + 8 * (2 * S + 4));
 	__shared__ volatile int s_timeout;
 	__shared__ volatile int s_stop[2];
+	__shared__ volatile int s_last[2];
 
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int kblocks = (a.K + BK - 1) / BK;
 	const int n_tiles = (a.N + BN - 1) / BN;
 	const int m_groups = (a.M + MT * BM - 1) / (MT * BM);
 	const int tiles = n_tiles * m_groups;
+	// split-K: work item w = (tile w % tiles, K slice w / tiles); slice s covers k-blocks
+	// [s*kblocks/splits, (s+1)*kblocks/splits). The slices of a tile meet in global scratch.
+	const int splits = a.splits > 1 ? a.splits : 1;
+	const int items = tiles * splits;
 
 	if (threadIdx.x == 0) {
 		for (int s = 0; s < S; ++s) {
@@ -236,9 +242,11 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 	if (warp == 0) {
 		if (lane == 0) {
 			uint32_t it = 0;
-			for (int t = blockIdx.x; t < tiles && s_timeout == 0; t += gridDim.x) {
+			for (int w = blockIdx.x; w < items && s_timeout == 0; w += gridDim.x) {
+				const int t = w % tiles, ks = w / tiles;
 				const int m0 = (t % m_groups) * MT * BM, n0 = (t / m_groups) * BN;
-				for (int kb = 0; kb < kblocks; ++kb, ++it) {
+				const int kb0 = (int)((long long)ks * kblocks / splits), kb1 = (int)((long long)(ks + 1) * kblocks / splits);
+				for (int kb = kb0; kb < kb1; ++kb, ++it) {
 					const int s = (int)(it % S);
 					const uint32_t phase = (it / S) & 1u;
 					if (!mbar_wait(empty_bar(s), phase ^ 1u)) { s_timeout = 1; break; }
@@ -253,11 +261,13 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 	} else if (warp == 1) {
 		if (lane == 0) {
 			uint32_t it = 0, tc = 0;
-			for (int t = blockIdx.x; t < tiles && s_timeout == 0; t += gridDim.x, ++tc) {
+			for (int w = blockIdx.x; w < items && s_timeout == 0; w += gridDim.x, ++tc) {
 				const uint32_t as = tc & 1u;
+				const int ks = w / tiles;
+				const int kb0 = (int)((long long)ks * kblocks / splits), kb1 = (int)((long long)(ks + 1) * kblocks / splits);
 				if (!mbar_wait(acce_bar(as), ((tc >> 1) & 1u) ^ 1u)) { s_timeout = 1; break; }
 				asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-				for (int kb = 0; kb < kblocks; ++kb, ++it) {
+				for (int kb = kb0; kb < kb1; ++kb, ++it) {
 					const int s = (int)(it % S);
 					const uint32_t phase = (it / S) & 1u;
 					if (!mbar_wait(full_bar(s), phase)) { s_timeout = 1; break; }
@@ -271,7 +281,7 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
 						for (int k = 0; k < BK / UMMA_K; ++k) {
 							// advancing inside the 128-byte swizzle atom: +32 bytes = +2 descriptor units
-							umma_i8(dcol, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), Cfg::kInstrDesc, (kb | k) != 0 ? 1u : 0u);
+							umma_i8(dcol, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), Cfg::kInstrDesc, (kb > kb0 || k != 0) ? 1u : 0u);
 						}
 					}
 					umma_commit(empty_bar(s));     // frees the stage once these MMAs have read it
@@ -290,8 +300,9 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 		// straight-line path: int32 rows, fold present, no adapters, not the head
 		const bool fast_ok = vec_ok && a.fold != nullptr && a.rows == nullptr && a.best == nullptr;
 		uint32_t tc = 0;
-		for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tc) {
+		for (int w = blockIdx.x; w < items; w += gridDim.x, ++tc) {
 			const uint32_t as = tc & 1u;
+			const int t = w % tiles, ks = w / tiles;
 			const int m0 = (t % m_groups) * MT * BM, n0 = (t / m_groups) * BN;
 			int32_t* sf = nullptr;
 			if (a.fold != nullptr) {
@@ -314,9 +325,52 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 			}
 			const bool acc_ok = mbar_wait(accf_bar(as), (tc >> 1) & 1u);
 			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-			if (!acc_ok) s_timeout = 1;
+			if (!acc_ok) {
+				s_timeout = 1;
+				if (a.status != nullptr) {
+					for (int mt = 0; mt < MT; ++mt) {
+						const int row = m0 + mt * BM + q * 32 + lane;
+						if (row < a.M) atomicCAS(&a.status[row], 0, (int32_t)kInternalWaitTimeout);
+					}
+				}
+			}
+			bool finish = true;                        // this block runs the tile's epilogue
+			if (splits > 1) {
+				// every K slice parks its raw accumulators in global scratch and then counts
+				// itself in; the slice that arrives last adds the others to its own and runs
+				// the epilogue. Nobody waits: the order of arrival decides the roles.
+#pragma unroll
+				for (int mt = 0; mt < MT; ++mt) {
+					const int row = m0 + mt * BM + q * 32 + lane;
+					if (m0 + mt * BM < a.M) {
+						for (int c0 = half * 32; c0 < BN; c0 += 64) {
+							uint32_t r[32];
+							tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (as * MT + mt) * BN + c0, r);
+								// scratch layout [slice][tile][mt][column quad][128 rows]: the 32 lanes of a
+							// warp touch 512 contiguous bytes per access
+							int4* dst = (int4*)a.partial +
+							            ((((size_t)ks * tiles + t) * MT + mt) * (BN / 4) + (c0 >> 2)) * BM + q * 32 + lane;
+#pragma unroll
+							for (int j4 = 0; j4 < 32; j4 += 4)
+								__stcg(dst + (size_t)(j4 >> 2) * BM, make_int4((int)r[j4], (int)r[j4 + 1], (int)r[j4 + 2], (int)r[j4 + 3]));
+						}
+					}
+				}
+				__threadfence();
+				asm volatile("bar.sync 1, 256;" ::: "memory");
+				if (et == 0) {
+					const unsigned int old = atomicAdd(&a.tile_counters[t], 1u);
+					const int last = old == (unsigned int)(splits - 1) ? 1 : 0;
+					if (last) a.tile_counters[t] = 0u;          // all slices are in: zero for the next launch
+					__threadfence();
+					s_last[as] = last;
+				}
+				asm volatile("bar.sync 1, 256;" ::: "memory");
+				finish = s_last[as] != 0;
+			}
 #pragma unroll
 			for (int mt = 0; mt < MT; ++mt) {
+				if (!finish) break;
 				const int row = m0 + mt * BM + q * 32 + lane;
 				const bool row_ok = acc_ok && row < a.M;
 				const LoraLayerDev* lora =
@@ -330,6 +384,33 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 						tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (as * MT + mt) * BN + c0, r);   // warp-collective
 						const int nb = n0 + c0;
 						if (!row_ok || nb >= a.N) continue;
+						if (splits > 1) {
+							// the other slices' accumulators, three slices' loads in flight at a time
+							constexpr int U = 3;
+							const size_t slice_stride = (size_t)tiles * MT * (BN / 4) * BM;
+							const int4* src0 = (const int4*)a.partial + (((size_t)t * MT + mt) * (BN / 4) + (c0 >> 2)) * BM + q * 32 + lane;
+							for (int s0 = 0; s0 < splits; s0 += U) {
+								int4 p[U][8];
+#pragma unroll
+								for (int u = 0; u < U; ++u) {
+									const int s2 = s0 + u;
+									const bool live = s2 < splits && s2 != ks;
+#pragma unroll
+									for (int j = 0; j < 8; ++j)
+										p[u][j] = live ? __ldcg(src0 + (size_t)s2 * slice_stride + (size_t)j * BM) : make_int4(0, 0, 0, 0);
+								}
+#pragma unroll
+								for (int u = 0; u < U; ++u) {
+#pragma unroll
+									for (int j = 0; j < 8; ++j) {
+										r[4 * j] += (uint32_t)p[u][j].x;
+										r[4 * j + 1] += (uint32_t)p[u][j].y;
+										r[4 * j + 2] += (uint32_t)p[u][j].z;
+										r[4 * j + 3] += (uint32_t)p[u][j].w;
+									}
+								}
+							}
+						}
 						const bool full = nb + 32 <= a.N;
 						if (a.best != nullptr && a.fold == nullptr && a.logits == nullptr && full) {
 							// head: running (value, index) maximum; columns ascend, so a strict
@@ -461,9 +542,31 @@ int sm_count() {
 	return n;
 }
 
+// K slices per output tile: only when the tiles alone would leave SMs idle, never fewer than
+// eight 128-wide k-blocks per slice (a shorter main loop is cheaper than the exchange), and
+// only as many as the scratch can hold.
 template <int MT, int BN>
-bool launch_cfg(const LinearArgs& a, cudaStream_t st) {
+int pick_splits(const LinearArgs& a, int tiles) {
+	if (a.partial == nullptr || a.tile_counters == nullptr || tiles > a.n_tile_counters) return 1;
+	const int kblocks = (a.K + BK - 1) / BK;
+	int s = sm_count() / tiles;
+	if (s > kblocks / 8) s = kblocks / 8;
+	if (s > 8) s = 8;
+	// tuning override: SSLM_B200_TC_SPLITS=n caps the slices (1 turns splitting off)
+	static const int cap = [] {
+		const char* e = getenv("SSLM_B200_TC_SPLITS");
+		return e ? atoi(e) : 0;
+	}();
+	if (cap > 0 && s > cap) s = cap;
+	const size_t per_slice = (size_t)tiles * MT * BM * BN * 4;
+	while (s > 1 && (size_t)s * per_slice > a.partial_bytes) --s;
+	return s < 2 ? 1 : s;
+}
+
+template <int MT, int BN>
+bool launch_cfg(const LinearArgs& a_in, cudaStream_t st) {
 	using Cfg = TcCfg<MT, BN>;
+	LinearArgs a = a_in;
 	static bool configured = false;
 	if (!configured) {
 		if (cudaFuncSetAttribute(k_linear_tc<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes) != cudaSuccess) {
@@ -478,7 +581,9 @@ bool launch_cfg(const LinearArgs& a, cudaStream_t st) {
 		return false;
 	}
 	const int tiles = ((a.N + BN - 1) / BN) * ((a.M + MT * BM - 1) / (MT * BM));
-	const int grid = tiles < sm_count() ? tiles : sm_count();
+	a.splits = pick_splits<MT, BN>(a, tiles);
+	const int items = tiles * a.splits;
+	const int grid = items < sm_count() ? items : sm_count();
 	k_linear_tc<MT, BN><<<grid, kTcThreads, Cfg::kSmemBytes, st>>>(ma, mb, a);
 	return true;
 }

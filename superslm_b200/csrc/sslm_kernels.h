@@ -49,6 +49,13 @@ struct LinearArgs {
 	unsigned long long* best;
 	int32_t* logits;      // optional full dump [M, N]
 	int32_t* status;      // [M] row statuses (a bounded device wait that ran out is reported here), or nullptr
+	// split-K scratch of the tensor-core path (optional): partial accumulators and one
+	// arrival counter per output tile. Counters are zero between launches.
+	int32_t* partial;
+	size_t partial_bytes;
+	unsigned int* tile_counters;
+	int n_tile_counters;
+	int splits;           // filled in by launch_linear_tc
 };
 // HBM-bound small-M path: vectorised weight streaming, dp4a, warp-shuffle reduction.
 void launch_linear_gemv(const LinearArgs& a, cudaStream_t st);

@@ -61,6 +61,22 @@ __device__ __forceinline__ int64_t load_wide(const RowBatch& b, int row, int col
 	const size_t i = (size_t)row * b.wide_ld + col;
 	return b.wide64 ? ((const int64_t*)b.wide)[i] : (int64_t)((const int32_t*)b.wide)[i];
 }
+// Cooperative 16-byte copy, global -> shared (both 16-byte aligned, bytes a multiple of 16).
+// The kernels below issue all of a row's input copies back to back at their start, so the
+// row pays one memory round trip instead of one per dependent phase.
+__device__ __forceinline__ void stage16(void* dst, const void* src, int bytes) {
+	const int4* s = (const int4*)src;
+	int4* d = (int4*)dst;
+#pragma unroll 4
+	for (int i = threadIdx.x; i < (bytes >> 4); i += blockDim.x) d[i] = s[i];
+}
+// the row of folded int32 accumulators can be staged with 16-byte copies
+__device__ __forceinline__ bool wide_stageable(const RowBatch& b, int cols) {
+	return !b.wide64 && (b.wide_ld & 3) == 0 && (cols & 3) == 0;
+}
+__device__ __forceinline__ const int32_t* wide_row32(const RowBatch& b, int row) {
+	return (const int32_t*)b.wide + (size_t)row * b.wide_ld;
+}
 // read a GEMM-reduced row maximum and leave the slot zero for its next producer
 __device__ __forceinline__ unsigned long long take_rowmax(const RowBatch& b, int row, int slot,
                                                           unsigned long long* red) {
@@ -185,18 +201,31 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	int8_t* sq = (int8_t*)(smem + 34 * 8 + 64);                // hidden
 	int8_t* sk = sq + d.hidden;                                // kv_hidden
 	const int r = blockIdx.x, H = d.hidden, hd = d.head_dim, half = hd / 2;
-	const unsigned long long mx = take_rowmax(b, r, 0, red);
-	if (b.status[r] != 0) return;
+	int32_t* sw = (int32_t*)(smem + 34 * 8 + 64 + ((H + d.kv_hidden + 15) & ~15));   // staged q|k|v row
+	int32_t* s_cos = sw + d.qkv_rows;                                                 // staged RoPE row
+	int32_t* s_sin = s_cos + half;
+	const bool vec = wide_stageable(b, d.qkv_rows) && (half & 3) == 0;
+	if (vec) stage16(sw, wide_row32(b, r), d.qkv_rows * 4);
 	const LayerDev& lw = *layer;
 	const Scale ns = b.ns[r];
+	const Scale c_q = lw.c_q;
 	const int pos = b.rows[r].pos;
+	if (vec) {
+		stage16(s_cos, rope_cos + (size_t)pos * half, half * 4);
+		stage16(s_sin, rope_sin + (size_t)pos * half, half * 4);
+	}
+	const int32_t* cos_row = vec ? s_cos : rope_cos + (size_t)pos * half;   // table row = position
+	const int32_t* sin_row = vec ? s_sin : rope_sin + (size_t)pos * half;
+	const unsigned long long mx = take_rowmax(b, r, 0, red);
+	if (b.status[r] != 0) return;
 
-	const FunnelParams fp = funnel_params(mx, &ns, 1, lw.c_q);
+	const FunnelParams fp = funnel_params(mx, &ns, 1, c_q);
 	if (fp.status != kOk) {
 		set_status(b, r, fp.status);
 		return;
 	}
-	for (int i = threadIdx.x; i < H; i += blockDim.x) sq[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+	auto wv = [&](int i) -> int64_t { return vec ? (int64_t)sw[i] : load_wide(b, r, i); };
+	for (int i = threadIdx.x; i < H; i += blockDim.x) sq[i] = requant_code(wv(i), fp.r, fp.s);
 
 	// K/V landing
 	const int page = b.rows[r].pages[pos / kPageTokens];
@@ -205,9 +234,9 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	for (int i = threadIdx.x; i < d.kv_hidden; i += blockDim.x) {
 		const int h = i / hd, dd = i - h * hd;
 		bool s1, s2;
-		const int64_t kraw = landing_rescale(load_wide(b, r, H + i), ns.m, lw.k_recip[3 * h + 2], ns.e,
+		const int64_t kraw = landing_rescale(wv(H + i), ns.m, lw.k_recip[3 * h + 2], ns.e,
 		                                     lw.k_recip[3 * h + 1], &s1, nullptr);
-		const int64_t vraw = landing_rescale(load_wide(b, r, H + d.kv_hidden + i), ns.m,
+		const int64_t vraw = landing_rescale(wv(H + d.kv_hidden + i), ns.m,
 		                                     lw.v_recip[3 * h + 2], ns.e, lw.v_recip[3 * h + 1], &s2, nullptr);
 		sat += (s1 ? 1 : 0) + (s2 ? 1 : 0);
 		sk[i] = (int8_t)clamp127(kraw);
@@ -224,7 +253,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	int8_t* qrot = b.qrot + (size_t)r * H;
 	for (int p = threadIdx.x; p < H / 2; p += blockDim.x) {
 		const int pi = p % half;
-		const int32_t c = rope_cos[(size_t)pos * half + pi], s = rope_sin[(size_t)pos * half + pi];
+		const int32_t c = cos_row[pi], s = sin_row[pi];
 		int8_t ox, oy;
 		rope_pair_clamped(sq[2 * p], sq[2 * p + 1], c, s, &ox, &oy);
 		qrot[2 * p] = ox;
@@ -232,7 +261,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	}
 	for (int p = threadIdx.x; p < d.kv_hidden / 2; p += blockDim.x) {
 		const int h = (2 * p) / hd, dd = 2 * p - h * hd, pi = dd / 2;
-		const int32_t c = rope_cos[(size_t)pos * half + pi], s = rope_sin[(size_t)pos * half + pi];
+		const int32_t c = cos_row[pi], s = sin_row[pi];
 		int8_t ox, oy;
 		rope_pair_clamped(sk[2 * p], sk[2 * p + 1], c, s, &ox, &oy);
 		int8_t* kdst = pool.base + kv_plane_offset(d, pool, layer_index, h, 0) +
@@ -285,17 +314,32 @@ __global__ void __launch_bounds__(kRowThreads)
 k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
+	int32_t* sw = (int32_t*)(smem + 34 * 8);
 	const int r = blockIdx.x, n = d.hidden;
+	const bool vec = (n & 3) == 0;
+	if (vec) stage16(sw, b.ctxw + (size_t)r * n, n * 4);
+	const Scale c_ctx = layer->c_ctx;
 	const unsigned long long mx = take_rowmax(b, r, 3, red);
 	if (b.status[r] != 0) return;
-	const FunnelParams fp = funnel_params(mx, nullptr, 0, layer->c_ctx);
+	const FunnelParams fp = funnel_params(mx, nullptr, 0, c_ctx);
 	if (fp.status != kOk) {
 		set_status(b, r, fp.status);
 		return;
 	}
-	const int32_t* w = b.ctxw + (size_t)r * n;
 	int8_t* out = b.ctx + (size_t)r * n;
-	for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = requant_code((int64_t)w[i], fp.r, fp.s);
+	if (vec) {
+		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+			const int4 p = ((const int4*)sw)[i];
+			const uint32_t c0 = (uint8_t)requant_code((int64_t)p.x, fp.r, fp.s);
+			const uint32_t c1 = (uint8_t)requant_code((int64_t)p.y, fp.r, fp.s);
+			const uint32_t c2 = (uint8_t)requant_code((int64_t)p.z, fp.r, fp.s);
+			const uint32_t c3 = (uint8_t)requant_code((int64_t)p.w, fp.r, fp.s);
+			((uint32_t*)out)[i] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+		}
+	} else {
+		const int32_t* w = b.ctxw + (size_t)r * n;
+		for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = requant_code((int64_t)w[i], fp.r, fp.s);
+	}
 	if (threadIdx.x == 0) b.cs[r] = fp.out;
 }
 
@@ -330,22 +374,36 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	int64_t* wide = (int64_t*)(smem + 34 * 8);
 	int8_t* so = (int8_t*)(wide + d.hidden);
 	int8_t* sa = so + d.hidden;
+	int8_t* sx = sa + d.hidden;                  // staged stream row
+	int8_t* sg = sx + d.hidden;                  // staged gain
+	int32_t* wraw = (int32_t*)(sg + d.hidden);   // staged projection row
 	const int r = blockIdx.x, n = d.hidden;
+	const LayerDev& lw = *layer;
+	const bool vec = wide_stageable(b, n) && (n & 15) == 0;
+	if (vec) {
+		stage16(wraw, wide_row32(b, r), n * 4);
+		stage16(sx, b.x + (size_t)r * n, n);
+		stage16(sg, lw.g_mlp, n);
+	}
+	const Scale cs = b.cs[r], xs = b.xs[r];
+	const Scale c_o = lw.c_o, c_res = lw.c_attn_res, c_norm = lw.c_mlp_norm;
 	const unsigned long long mx = take_rowmax(b, r, 0, red);
 	if (b.status[r] != 0) return;
-	const LayerDev& lw = *layer;
-	const Scale cs = b.cs[r];
-	const FunnelParams fp = funnel_params(mx, &cs, 1, lw.c_o);
+	const FunnelParams fp = funnel_params(mx, &cs, 1, c_o);
 	int32_t st = fp.status;
 	if (st == kOk) {
-		for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+		if (vec) {
+			for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = requant_code((int64_t)wraw[i], fp.r, fp.s);
+		} else {
+			for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+		}
 		__syncthreads();
-		st = block_residual(so, fp.out, b.x + (size_t)r * n, b.xs[r], n, lw.c_attn_res, wide,
+		st = block_residual(so, fp.out, vec ? sx : b.x + (size_t)r * n, xs, n, c_res, wide,
 		                    b.a + (size_t)r * n, sa, &b.as[r], red);
 	}
 	if (st == kOk) {
 		__syncthreads();
-		st = block_rmsnorm(sa, lw.g_mlp, n, lw.c_mlp_norm, wide, b.nrm + (size_t)r * n, &b.ns[r], red);
+		st = block_rmsnorm(sa, vec ? sg : lw.g_mlp, n, c_norm, wide, b.nrm + (size_t)r * n, &b.ns[r], red);
 	}
 	set_status(b, r, st);
 }
@@ -359,29 +417,45 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	int64_t* wide = (int64_t*)(smem + 34 * 8);
 	int8_t* sd = (int8_t*)(wide + d.hidden);
 	int8_t* sx = sd + d.hidden;
+	int8_t* sa = sx + d.hidden;                  // staged stream row (after the attention residual)
+	int8_t* sg = sa + d.hidden;                  // staged gain of the next layer
+	int32_t* wraw = (int32_t*)(sg + d.hidden);   // staged projection row
 	const int r = blockIdx.x, n = d.hidden;
+	const LayerDev& lw = *layer;
+	const bool vec = wide_stageable(b, n) && (n & 15) == 0;
+	if (vec) {
+		stage16(wraw, wide_row32(b, r), n * 4);
+		stage16(sa, b.a + (size_t)r * n, n);
+		if (next_layer != nullptr) stage16(sg, next_layer->g_attn, n);
+	}
+	const Scale as = b.acts[r], rs = b.as[r];
+	const Scale c_down = lw.c_down, c_res = lw.c_mlp_res;
+	Scale c_norm = Scale{0, 0};
+	if (next_layer != nullptr) c_norm = next_layer->c_attn_norm;
 	const unsigned long long mx = take_rowmax(b, r, 0, red);
 	if (b.status[r] != 0) return;
-	const LayerDev& lw = *layer;
-	const Scale as = b.acts[r];
-	const FunnelParams fp = funnel_params(mx, &as, 1, lw.c_down);
+	const FunnelParams fp = funnel_params(mx, &as, 1, c_down);
 	int32_t st = fp.status;
 	if (st == kOk) {
-		for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+		if (vec) {
+			for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = requant_code((int64_t)wraw[i], fp.r, fp.s);
+		} else {
+			for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+		}
 		__syncthreads();
-		st = block_residual(sd, fp.out, b.a + (size_t)r * n, b.as[r], n, lw.c_mlp_res, wide,
+		st = block_residual(sd, fp.out, vec ? sa : b.a + (size_t)r * n, rs, n, c_res, wide,
 		                    b.x + (size_t)r * n, sx, &b.xs[r], red);
 	}
 	if (st == kOk && next_layer != nullptr) {
 		__syncthreads();
-		st = block_rmsnorm(sx, next_layer->g_attn, n, next_layer->c_attn_norm, wide,
+		st = block_rmsnorm(sx, vec ? sg : next_layer->g_attn, n, c_norm, wide,
 		                   b.nrm + (size_t)r * n, &b.ns[r], red);
 	}
 	set_status(b, r, st);
 }
 
 // gate / up funnels -> SwiGLU activation site (MlpActSite, forward_sites.cpp:796-864)
-__global__ void __launch_bounds__(kRowThreads, 4)
+__global__ void __launch_bounds__(kRowThreads, 1024 / kRowThreads)
 k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
@@ -477,6 +551,8 @@ k_scatter(RowBatch b, Dims d, const RowSink* sink) {
 
 // ------------------------------------------------------------------ launchers
 static size_t smem_wide(const Dims& d) { return 34 * 8 + (size_t)d.hidden * 8; }
+// reductions, the int64 staging row, four code rows and the staged int32 projection row
+static size_t res_smem_bytes(const Dims& d) { return 34 * 8 + (size_t)d.hidden * 16; }
 
 void launch_begin(const RowBatch& b, const Dims& d, const int8_t* embed, Scale c_embed,
                   const RowSource* src, const LayerDev* layer, cudaStream_t st) {
@@ -487,22 +563,38 @@ void launch_rmsnorm(const RowBatch& b, const Dims& d, const int8_t* gain, Scale 
 }
 void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
                      KvPoolDev pool, const int32_t* cos, const int32_t* sin, cudaStream_t st) {
-	const size_t sm = 34 * 8 + 64 + d.hidden + d.kv_hidden;
+	const size_t sm = 34 * 8 + 64 + (size_t)((d.hidden + d.kv_hidden + 15) & ~15) +
+	                  (size_t)(d.qkv_rows + d.head_dim) * 4;
 	k_qkv_post<<<b.m, kRowThreads, sm, st>>>(b, d, layer, layer_index, pool, cos, sin);
 }
 void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
-	k_ctx_funnel<<<b.m, kRowThreads, 34 * 8, st>>>(b, d, layer);
+	k_ctx_funnel<<<b.m, kRowThreads, 34 * 8 + (size_t)d.hidden * 4, st>>>(b, d, layer);
 }
 void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
-	k_res1<<<b.m, kRowThreads, smem_wide(d) + 2 * d.hidden, st>>>(b, d, layer);
+	k_res1<<<b.m, kRowThreads, res_smem_bytes(d), st>>>(b, d, layer);
 }
 void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev* next,
                  cudaStream_t st) {
-	k_res2<<<b.m, kRowThreads, smem_wide(d) + 2 * d.hidden, st>>>(b, d, layer, next);
+	k_res2<<<b.m, kRowThreads, res_smem_bytes(d), st>>>(b, d, layer, next);
 }
 size_t act_smem_bytes(const Dims& d) { return 36 * 8 + 1028 * 4 + (size_t)d.inter * 4; }
 cudaError_t rows_configure(const Dims& d) {
-	return cudaFuncSetAttribute(k_act, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)act_smem_bytes(d));
+	cudaError_t e = cudaFuncSetAttribute(k_act, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)act_smem_bytes(d));
+	if (e != cudaSuccess) return e;
+	// Every kernel of a step asks for the same (largest) shared-memory carve-out as the
+	// tensor-core GEMM between them, so consecutive launches never make the SMs re-split
+	// their L1 / shared memory.
+	const void* all[] = {(const void*)k_begin, (const void*)k_rmsnorm, (const void*)k_qkv_post, (const void*)k_ctx_funnel,
+	                     (const void*)k_res1,  (const void*)k_res2,    (const void*)k_act,      (const void*)k_scatter};
+	for (const void* f : all) {
+		e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+		if (e != cudaSuccess) return e;
+	}
+	const int res = (int)res_smem_bytes(d);
+	if (res > 227 * 1024) return cudaErrorInvalidConfiguration;
+	e = cudaFuncSetAttribute(k_res1, cudaFuncAttributeMaxDynamicSharedMemorySize, res);
+	if (e != cudaSuccess) return e;
+	return cudaFuncSetAttribute(k_res2, cudaFuncAttributeMaxDynamicSharedMemorySize, res);
 }
 void launch_act(const RowBatch& b, const Dims& d, const LayerDev* layer, const int32_t* silu,
                 cudaStream_t st) {

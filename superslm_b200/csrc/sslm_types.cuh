@@ -12,7 +12,7 @@ namespace sslm {
 
 constexpr int kPageTokens = 16;       // KV page = 16 token positions of one (layer, kv head, K|V)
 constexpr int kMaxLoraRank = 64;
-constexpr int kRowThreads = 256;      // block size of the per-row kernels
+constexpr int kRowThreads = 256;     // block size of the per-row kernels
 
 struct LoraProjDev {
 	const int8_t* a;      // [rank, in]   lora_A

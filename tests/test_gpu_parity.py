@@ -250,6 +250,8 @@ LINEAR_CASES = [  # (K, N, M): every M class, ragged N, the real 1.5B K/V and hi
     (1536, 256, 1), (1536, 256, 16), (1536, 256, 128), (1536, 1536, 1), (1536, 1536, 5), (1536, 1536, 130),
     (8960, 1536, 1), (8960, 1536, 16), (1536, 8960, 2), (1536, 8960, 64), (128, 77, 3), (16, 1, 1), (256, 333, 257),
     (1536, 4099, 9),
+    # few output tiles and a long K: the tensor-core kernel splits K across blocks (3 to 16 slices)
+    (8960, 1536, 256), (8960, 100, 200), (1536, 2048, 256), (4096, 64, 129),
 ]
 
 
