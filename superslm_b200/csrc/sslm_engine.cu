@@ -36,6 +36,8 @@ sslm_status map_forward_status(int32_t st) {
 	// MapForwardStatus, src/sslm_abi.cpp:1352-1370
 	if (st == kOk) return SSLM_OK;
 	if (st == kSoftmaxKernelRefused) return SSLM_NUMERIC_STEP_REFUSED;
+	// not a reference status: a bounded device-side wait of this implementation ran out
+	if (st == kInternalWaitTimeout) return SSLM_ALLOCATION_FAILED;
 	return SSLM_ARTIFACT_REJECTED;
 }
 
@@ -88,6 +90,9 @@ extern "C" sslm_status sslm_model_map(const void* data, size_t size, sslm_model*
 	// the kernels' vector widths
 	if (c.kv_precision != 0) return SSLM_ARTIFACT_REJECTED;
 	if (v.has(kSecBiases)) return SSLM_ARTIFACT_REJECTED;
+	// header flags bit 0 selects the fused wide K landing (RopeApplyPairWide,
+	// src/forward/forward_sites.cpp:1349-1395); only the legacy landing is implemented
+	if (v.flags() & 1u) return SSLM_ARTIFACT_REJECTED;
 	if (c.hidden % 16 || c.inter % 16 || c.head_dim % 16 || c.head_dim > 128 ||
 	    (128 % c.head_dim) != 0 || c.heads / c.kv_heads > 8 || c.kv_heads > 16)
 		return SSLM_ARTIFACT_REJECTED;
