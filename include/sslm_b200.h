@@ -199,6 +199,29 @@ SSLM_API sslm_status sslm_b200_capture_logits(sslm_workspace ws, int32_t* host_r
 /* Bytes of HBM held by the model's weights, tables and constants. */
 SSLM_API size_t sslm_b200_model_device_bytes(sslm_model model);
 
+/* The layer of sslm_b200_linear for operands that are already in device memory, for callers
+ * that may not allocate (all HBM already assigned to their own pools, or no device-wide stall
+ * allowed where they call from). This entry point has no counterpart in the reference. It
+ * allocates nothing on the host or the device: the only scratch the layer needs, the per-row
+ * peak of the folded accumulators, lives in a fixed array inside the library's device image
+ * (SSLM_B200_RESIDENT_MAX_ROWS rows). Every pointer is a device pointer on the calling
+ * thread's current device; x, w and out_folded 16-byte aligned; out_folded is required
+ * ([M,N] int32), out_codes / out_scales / row_status may be NULL. The work is enqueued on
+ * `stream` (a cudaStream_t, NULL = the default stream) and the call returns without waiting.
+ *  - M > SSLM_B200_RESIDENT_MAX_ROWS or K > 16384: SSLM_INVALID_ARGUMENT, nothing is launched.
+ *  - The first call on a device also looks up the array's address (set-up): make that call
+ *    before any stream capture begins.
+ *  - All calls on a device share the array. It reads zero at load time and every call leaves
+ *    it zero again; calls whose kernels may overlap in time (other streams or threads) race
+ *    on it and must be ordered by the caller.
+ * Always the streaming dp4a kernel (the tensor-core path keeps host-side caches). */
+#define SSLM_B200_RESIDENT_MAX_ROWS 256
+SSLM_API sslm_status sslm_b200_linear_resident(const int8_t* d_x, const int8_t* d_w, const int32_t* d_fold,
+                                               int32_t M, int32_t N, int32_t K, const int64_t* d_in_scales,
+                                               int64_t site_m, int64_t site_e, int32_t* d_out_folded,
+                                               int8_t* d_out_codes, int64_t* d_out_scales,
+                                               int32_t* d_row_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,7 +8,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsslm_b200.so")
-SOURCES = ["sslm_rows.cu", "sslm_gemv.cu", "sslm_attn.cu", "sslm_gemm_tc.cu", "sslm_engine.cu", "sslm_artifact.cpp"]
+SOURCES = ["sslm_rows.cu", "sslm_gemv.cu", "sslm_attn.cu", "sslm_gemm_tc.cu", "sslm_engine.cu", "sslm_noalloc.cu",
+           "sslm_artifact.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=hidden"]
