@@ -10,6 +10,9 @@
 
 namespace sslm {
 
+// per-row lookup tables indexed by an int8 code: 256 int64 values + 256 flag bytes
+constexpr int kLutBytes = 256 * 8 + 256;
+
 // ------------------------------------------------------------ block reductions
 __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
 #pragma unroll
@@ -118,7 +121,7 @@ __device__ int32_t block_funnel(const WT* w, int n, const Scale* incoming, int n
 // root = max(isqrt(floor((sum h^2) << 32 / n)), 1); wide_i = floor((h_i << 32) / root) * g_i;
 // funnel with no incoming scale. wide: shared int64[n].
 __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Scale site, int64_t* wide,
-                                 int8_t* out_g, Scale* out_scale, unsigned long long* red) {
+                                 int8_t* out_g, Scale* out_scale, int64_t* lut, unsigned long long* red) {
 	long long ss = 0;
 	for (int i = threadIdx.x; i < n; i += blockDim.x) {
 		const int v = h[i];
@@ -127,10 +130,11 @@ __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Sca
 	ss = block_sum_i64(ss, red);
 	int64_t root = isqrt64(floor_div((int64_t)ss << 32, (int64_t)n));
 	if (root < 1) root = 1;
+	// floor((h << 32) / root) depends only on the code: one division per code value, not per element
 	const double inv_root = 1.0 / (double)root;
-	for (int i = threadIdx.x; i < n; i += blockDim.x) {
-		wide[i] = floor_div_h32((int)h[i], root, inv_root) * (int64_t)gain[i];
-	}
+	for (int t = threadIdx.x; t < 255; t += blockDim.x) lut[t] = floor_div_h32(t - 127, root, inv_root);
+	__syncthreads();
+	for (int i = threadIdx.x; i < n; i += blockDim.x) wide[i] = lut[(int)h[i] + 127] * (int64_t)gain[i];
 	__syncthreads();
 	return block_funnel<int64_t>(wide, n, nullptr, 0, site, out_g, nullptr, out_scale, red);
 }
@@ -148,7 +152,8 @@ k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource*
         const LayerDev* layer) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
-	int64_t* wide = (int64_t*)(smem + 34 * 8);
+	int64_t* lut = (int64_t*)(smem + 34 * 8);
+	int64_t* wide = (int64_t*)(smem + 34 * 8 + kLutBytes);
 	const int r = blockIdx.x, n = d.hidden;
 	int8_t* x = b.x + (size_t)r * n;
 	if (threadIdx.x == 0) {
@@ -169,7 +174,7 @@ k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource*
 	__syncthreads();
 	if (st == kOk && layer != nullptr) {
 		st = block_rmsnorm(x, layer->g_attn, n, layer->c_attn_norm, wide, b.nrm + (size_t)r * n,
-		                   &b.ns[r], red);
+		                   &b.ns[r], lut, red);
 	}
 	set_status(b, r, st);
 }
@@ -179,11 +184,12 @@ __global__ void __launch_bounds__(kRowThreads)
 k_rmsnorm(RowBatch b, Dims d, const int8_t* gain, Scale site) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
-	int64_t* wide = (int64_t*)(smem + 34 * 8);
+	int64_t* lut = (int64_t*)(smem + 34 * 8);
+	int64_t* wide = (int64_t*)(smem + 34 * 8 + kLutBytes);
 	const int r = blockIdx.x, n = d.hidden;
 	if (b.status[r] != 0) return;
 	const int32_t st = block_rmsnorm(b.x + (size_t)r * n, gain, n, site, wide, b.nrm + (size_t)r * n,
-	                                 &b.ns[r], red);
+	                                 &b.ns[r], lut, red);
 	set_status(b, r, st);
 }
 
@@ -347,18 +353,26 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 // shared memory: wide_i = LandingRescale(branch_i, S[branch], Recip(S[stream].m), ...) + stream_i.
 __device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t* stream, Scale ss, int n,
                                   Scale site, int64_t* wide, int8_t* out_g, int8_t* out_s,
-                                  Scale* out_scale, unsigned long long* red) {
+                                  Scale* out_scale, int64_t* lut, unsigned long long* red) {
 	if (!fits_i32(ss.m)) return kCarriedScaleMantissaOutOfDomain;
 	const int64_t r_h = dyn_recip(ss.m);
+	// the rescaled branch value depends only on the branch code: one LandingRescale per code value.
+	// lex marks the codes whose rescaled magnitude left int64 (the site refuses a row that uses one).
+	uint8_t* lex = (uint8_t*)(lut + 256);
+	for (int t = threadIdx.x; t < 255; t += blockDim.x) {
+		bool ex;
+		lut[t] = landing_rescale((int64_t)(t - 127), bs.m, r_h, bs.e, ss.e, nullptr, &ex);
+		lex[t] = ex ? 1 : 0;
+	}
+	__syncthreads();
 	long long bad = 0;
 	for (int i = threadIdx.x; i < n; i += blockDim.x) {
-		bool ex;
-		const int64_t v = landing_rescale((int64_t)branch_s[i], bs.m, r_h, bs.e, ss.e, nullptr, &ex);
-		if (ex) {
+		const int c = (int)branch_s[i] + 127;
+		if (lex[c]) {
 			bad = 1;
 			wide[i] = 0;
 		} else {
-			wide[i] = v + (int64_t)stream[i];
+			wide[i] = lut[c] + (int64_t)stream[i];
 		}
 	}
 	bad = block_sum_i64(bad, red);
@@ -371,7 +385,8 @@ __global__ void __launch_bounds__(kRowThreads)
 k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
-	int64_t* wide = (int64_t*)(smem + 34 * 8);
+	int64_t* lut = (int64_t*)(smem + 34 * 8);
+	int64_t* wide = (int64_t*)(smem + 34 * 8 + kLutBytes);
 	int8_t* so = (int8_t*)(wide + d.hidden);
 	int8_t* sa = so + d.hidden;
 	int8_t* sx = sa + d.hidden;                  // staged stream row
@@ -399,11 +414,11 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 		}
 		__syncthreads();
 		st = block_residual(so, fp.out, vec ? sx : b.x + (size_t)r * n, xs, n, c_res, wide,
-		                    b.a + (size_t)r * n, sa, &b.as[r], red);
+		                    b.a + (size_t)r * n, sa, &b.as[r], lut, red);
 	}
 	if (st == kOk) {
 		__syncthreads();
-		st = block_rmsnorm(sa, vec ? sg : lw.g_mlp, n, c_norm, wide, b.nrm + (size_t)r * n, &b.ns[r], red);
+		st = block_rmsnorm(sa, vec ? sg : lw.g_mlp, n, c_norm, wide, b.nrm + (size_t)r * n, &b.ns[r], lut, red);
 	}
 	set_status(b, r, st);
 }
@@ -414,7 +429,8 @@ __global__ void __launch_bounds__(kRowThreads)
 k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
-	int64_t* wide = (int64_t*)(smem + 34 * 8);
+	int64_t* lut = (int64_t*)(smem + 34 * 8);
+	int64_t* wide = (int64_t*)(smem + 34 * 8 + kLutBytes);
 	int8_t* sd = (int8_t*)(wide + d.hidden);
 	int8_t* sx = sd + d.hidden;
 	int8_t* sa = sx + d.hidden;                  // staged stream row (after the attention residual)
@@ -444,12 +460,12 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 		}
 		__syncthreads();
 		st = block_residual(sd, fp.out, vec ? sa : b.a + (size_t)r * n, rs, n, c_res, wide,
-		                    b.x + (size_t)r * n, sx, &b.xs[r], red);
+		                    b.x + (size_t)r * n, sx, &b.xs[r], lut, red);
 	}
 	if (st == kOk && next_layer != nullptr) {
 		__syncthreads();
 		st = block_rmsnorm(sx, vec ? sg : next_layer->g_attn, n, c_norm, wide,
-		                   b.nrm + (size_t)r * n, &b.ns[r], red);
+		                   b.nrm + (size_t)r * n, &b.ns[r], lut, red);
 	}
 	set_status(b, r, st);
 }
@@ -459,10 +475,9 @@ __global__ void __launch_bounds__(kRowThreads, 1024 / kRowThreads)
 k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
-	int32_t* tab = (int32_t*)(smem + 36 * 8);          // 1025 entries, padded to 1028
-	int32_t* wide = tab + 1028;                         // inter
+	int32_t* gsil = (int32_t*)(smem + 36 * 8);         // g * sigmoid(g) for the 255 gate codes, this row's scale
+	int32_t* wide = gsil + 256;                         // inter
 	const int r = blockIdx.x, n = d.inter;
-	for (int i = threadIdx.x; i < 1025; i += blockDim.x) tab[i] = silu_table[i];
 	if (threadIdx.x == 0) {
 		red[33] = b.rowmax[r * 4 + 1];
 		red[34] = b.rowmax[r * 4 + 2];
@@ -483,6 +498,13 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 		return;
 	}
 	const int ge = (int)fg.out.e;
+	// the sigmoid depends only on the gate code and the row's gate scale: 255 evaluations per
+	// row instead of one per element
+	for (int t = threadIdx.x; t < 255; t += blockDim.x) {
+		const int g = t - 127;
+		gsil[t] = g * silu_sigmoid_q15(silu_table, g, fg.out.m, ge);
+	}
+	__syncthreads();
 	// products g * sigmoid(g) * u, |.| <= 127 * 2^15 * 127 < 2^29, staged in shared memory
 	// with their running maximum so that the funnel below needs no second pass for it
 	uint32_t lmax = 0;
@@ -499,7 +521,7 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 			for (int j = 0; j < 4; ++j) {
 				const int g = requant_code((int64_t)gs[j], fg.r, fg.s);
 				const int u = requant_code((int64_t)us[j], fu.r, fu.s);
-				pr[j] = g * silu_sigmoid_q15(tab, g, fg.out.m, ge) * u;
+				pr[j] = gsil[g + 127] * u;
 				const uint32_t a = pr[j] < 0 ? 0u - (uint32_t)pr[j] : (uint32_t)pr[j];
 				lmax = a > lmax ? a : lmax;
 			}
@@ -509,7 +531,7 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 		for (int i = threadIdx.x; i < n; i += blockDim.x) {
 			const int g = requant_code(load_wide(b, r, i), fg.r, fg.s);
 			const int u = requant_code(load_wide(b, r, n + i), fu.r, fu.s);
-			const int p = g * silu_sigmoid_q15(tab, g, fg.out.m, ge) * u;
+			const int p = gsil[g + 127] * u;
 			wide[i] = p;
 			const uint32_t a = p < 0 ? 0u - (uint32_t)p : (uint32_t)p;
 			lmax = a > lmax ? a : lmax;
@@ -550,9 +572,9 @@ k_scatter(RowBatch b, Dims d, const RowSink* sink) {
 }
 
 // ------------------------------------------------------------------ launchers
-static size_t smem_wide(const Dims& d) { return 34 * 8 + (size_t)d.hidden * 8; }
+static size_t smem_wide(const Dims& d) { return 34 * 8 + kLutBytes + (size_t)d.hidden * 8; }
 // reductions, the int64 staging row, four code rows and the staged int32 projection row
-static size_t res_smem_bytes(const Dims& d) { return 34 * 8 + (size_t)d.hidden * 16; }
+static size_t res_smem_bytes(const Dims& d) { return 34 * 8 + kLutBytes + (size_t)d.hidden * 16; }
 
 void launch_begin(const RowBatch& b, const Dims& d, const int8_t* embed, Scale c_embed,
                   const RowSource* src, const LayerDev* layer, cudaStream_t st) {
@@ -577,7 +599,7 @@ void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const 
                  cudaStream_t st) {
 	k_res2<<<b.m, kRowThreads, res_smem_bytes(d), st>>>(b, d, layer, next);
 }
-size_t act_smem_bytes(const Dims& d) { return 36 * 8 + 1028 * 4 + (size_t)d.inter * 4; }
+size_t act_smem_bytes(const Dims& d) { return 36 * 8 + 256 * 4 + (size_t)d.inter * 4; }
 cudaError_t rows_configure(const Dims& d) {
 	cudaError_t e = cudaFuncSetAttribute(k_act, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)act_smem_bytes(d));
 	if (e != cudaSuccess) return e;
