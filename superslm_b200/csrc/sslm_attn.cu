@@ -84,16 +84,18 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a2, 
 // The HD/16 words of a head-dim row that lane column c (= lane & 3) feeds to the HD/32
 // score MMAs: MMA j takes words 2j (k slots 4c..4c+3) and 2j+1 (k slots 16+4c..). Any
 // assignment of head-dim bytes to k slots is valid as long as q and K use the same one.
+// (Plain loads, not the read-only path: q and the newest K / V rows were written by the kernel
+// just before this one, which may still have been running when this block was placed.)
 template <int HD>
 __device__ __forceinline__ void load_row_words(const int8_t* row, int c, uint32_t (&w)[HD / 16]) {
 	if constexpr (HD == 32) {
-		const int2 x = __ldg((const int2*)(row + c * 8));
+		const int2 x = *(const int2*)(row + c * 8);
 		w[0] = (uint32_t)x.x; w[1] = (uint32_t)x.y;
 	} else {
-		const int4 x = __ldg((const int4*)(row + c * 16));
+		const int4 x = *(const int4*)(row + c * 16);
 		w[0] = (uint32_t)x.x; w[1] = (uint32_t)x.y; w[2] = (uint32_t)x.z; w[3] = (uint32_t)x.w;
 		if constexpr (HD == 128) {
-			const int4 y = __ldg((const int4*)(row + 64 + c * 16));
+			const int4 y = *(const int4*)(row + 64 + c * 16);
 			w[4] = (uint32_t)y.x; w[5] = (uint32_t)y.y; w[6] = (uint32_t)y.z; w[7] = (uint32_t)y.w;
 		}
 	}
@@ -125,6 +127,8 @@ __global__ void __launch_bounds__(2 * HD, HD == 128 ? 4 : 8)
 k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int wp) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	const int r = blockIdx.y, kvh = blockIdx.x;
+	pdl_wait();
+	pdl_release();
 	if (b.status[r] != 0) return;
 	constexpr int kAttnThreads = 2 * HD, kAttnWarps = kAttnThreads / 32;
 	const int G = d.heads / d.kv_heads;
@@ -303,7 +307,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 				vv[u][i] = make_int4(0, 0, 0, 0);
 				if (live) {
 					const int ch = (warp * NDB + i) * 8 + g;
-					vv[u][i] = __ldg((const int4*)(vplane + s.pbase[page] + ch * kPageTokens));
+					vv[u][i] = *(const int4*)(vplane + s.pbase[page] + ch * kPageTokens);
 				}
 			}
 		}
@@ -345,7 +349,7 @@ static int pad_width(int w) { return (w + 63) / 64 * 64; }
 template <int HD>
 static void launch_attn(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index, KvPoolDev pool,
                         int wp, size_t sm, cudaStream_t st) {
-	k_attention<HD><<<dim3(d.kv_heads, b.m), 2 * HD, sm, st>>>(b, d, layer, layer_index, pool, wp);
+	launch_pdl(k_attention<HD>, dim3(d.kv_heads, b.m), dim3(2 * HD), sm, st, b, d, layer, layer_index, pool, wp);
 }
 
 cudaError_t attn_configure(const Dims& d) {

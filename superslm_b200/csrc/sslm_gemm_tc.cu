@@ -238,6 +238,10 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 	__syncthreads();
 	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 	const uint32_t tmem_base = *tmem_slot;
+	// everything above touched only this block's shared and tensor memory; from here on the
+	// kernel reads what earlier kernels wrote
+	pdl_wait();
+	pdl_release();
 
 	if (warp == 0) {
 		if (lane == 0) {
@@ -584,7 +588,7 @@ bool launch_cfg(const LinearArgs& a_in, cudaStream_t st) {
 	a.splits = pick_splits<MT, BN>(a, tiles);
 	const int items = tiles * a.splits;
 	const int grid = items < sm_count() ? items : sm_count();
-	k_linear_tc<MT, BN><<<grid, kTcThreads, Cfg::kSmemBytes, st>>>(ma, mb, a);
+	launch_pdl(k_linear_tc<MT, BN>, dim3(grid), dim3(kTcThreads), Cfg::kSmemBytes, st, ma, mb, a);
 	return true;
 }
 

@@ -33,6 +33,8 @@ k_gemv(LinearArgs a) {
 	const int m0 = blockIdx.y * MT;
 	const int mcount = min(MT, a.M - m0);
 	const int K = a.K, kv = K / 16;
+	pdl_wait();
+	pdl_release();
 	for (int i = threadIdx.x; i < MT * kv; i += blockDim.x) {
 		const int m = i / kv, c = i - m * kv;
 		int4 v = make_int4(0, 0, 0, 0);
@@ -147,7 +149,7 @@ static void launch_one(const LinearArgs& a, int grid_x, int grid_y, cudaStream_t
 		cudaFuncSetAttribute(k_gemv<MT, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
 		configured = true;
 	}
-	k_gemv<MT, RPW><<<dim3(grid_x, grid_y), kGemvThreads, smem, st>>>(a);
+	launch_pdl(k_gemv<MT, RPW>, dim3(grid_x, grid_y), dim3(kGemvThreads), smem, st, a);
 }
 
 template <int MT>
@@ -176,6 +178,8 @@ void launch_linear_gemv(const LinearArgs& a, cudaStream_t st) {
 __global__ void k_lora_u(RowBatch b, const int8_t* x, int k_in, int layer, int s0, int s1, int s2) {
 	const int r = blockIdx.x, pj = blockIdx.y;
 	const int slot = pj == 0 ? s0 : (pj == 1 ? s1 : s2);
+	pdl_wait();
+	pdl_release();
 	const LoraLayerDev* ll = b.rows[r].lora;
 	if (ll == nullptr) return;
 	const LoraLayerDev& L = ll[layer];
@@ -198,7 +202,7 @@ __global__ void k_lora_u(RowBatch b, const int8_t* x, int k_in, int layer, int s
 
 void launch_lora_u(const RowBatch& b, const int8_t* x, int k_in, int layer, int nproj,
                    const int* slots, cudaStream_t st) {
-	k_lora_u<<<dim3(b.m, nproj), 256, 0, st>>>(b, x, k_in, layer, slots[0], nproj > 1 ? slots[1] : 0,
+	launch_pdl(k_lora_u, dim3(b.m, nproj), dim3(256), 0, st, b, x, k_in, layer, slots[0], nproj > 1 ? slots[1] : 0,
 	                                            nproj > 2 ? slots[2] : 0);
 }
 

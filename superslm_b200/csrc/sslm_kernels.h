@@ -4,9 +4,48 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+#include <utility>
+
 #include "sslm_types.cuh"
 
 namespace sslm {
+
+// ---- programmatic dependent launch
+// A step is a chain of ~285 short dependent kernels. Each is launched with the programmatic
+// stream-serialization attribute: its blocks may be placed on the SMs, and run whatever does
+// not depend on earlier kernels (index arithmetic, barrier and tensor-memory set-up), while
+// the previous kernel is still running. Every kernel calls pdl_wait() before its first access
+// to global memory -- it returns once the previous kernel has completed and its writes are
+// visible -- and then pdl_release(), which lets the NEXT kernel's blocks be placed. Releasing
+// only after the wait keeps the look-ahead to one kernel. A kernel launched without the
+// attribute (or after a memcpy / memset) sees both calls as no-ops and plain stream order.
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+// SSLM_B200_PDL=0 in the environment turns the attribute off (plain stream order).
+inline bool pdl_enabled() {
+	static const bool on = [] {
+		const char* e = getenv("SSLM_B200_PDL");
+		return !(e && e[0] == '0');
+	}();
+	return on;
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = grid;
+	cfg.blockDim = block;
+	cfg.dynamicSmemBytes = smem;
+	cfg.stream = st;
+	cudaLaunchAttribute attr[1];
+	attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+	attr[0].val.programmaticStreamSerializationAllowed = 1;
+	cfg.attrs = attr;
+	cfg.numAttrs = pdl_enabled() ? 1 : 0;
+	return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 struct RowSource { const int8_t* hidden; const Scale* scale; };  // nullptr hidden: embed rows[r].token
 struct RowSink { int8_t* hidden; Scale* scale; };                // nullptr hidden: drop

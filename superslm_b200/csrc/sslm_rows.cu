@@ -150,6 +150,8 @@ __device__ __forceinline__ void set_status(const RowBatch& b, int row, int32_t s
 __global__ void __launch_bounds__(kRowThreads)
 k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource* src,
         const LayerDev* layer) {
+	pdl_wait();
+	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
 	int64_t* lut = (int64_t*)(smem + 34 * 8);
@@ -182,6 +184,8 @@ k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource*
 // RMSNorm of the stream with the given gain (used for the final norm before the head).
 __global__ void __launch_bounds__(kRowThreads)
 k_rmsnorm(RowBatch b, Dims d, const int8_t* gain, Scale site) {
+	pdl_wait();
+	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
 	int64_t* lut = (int64_t*)(smem + 34 * 8);
@@ -201,6 +205,8 @@ k_rmsnorm(RowBatch b, Dims d, const int8_t* gain, Scale site) {
 __global__ void __launch_bounds__(kRowThreads)
 k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool,
            const int32_t* rope_cos, const int32_t* rope_sin) {
+	pdl_wait();
+	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;      // 34 words
 	int32_t* st_kv = (int32_t*)(smem + 34 * 8);                // 16 ints
@@ -318,6 +324,8 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 // Attention-context funnel (forward_sites.cpp:1898-1903): empty incoming, attn_ctx constant.
 __global__ void __launch_bounds__(kRowThreads)
 k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
+	pdl_wait();
+	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
 	int32_t* sw = (int32_t*)(smem + 34 * 8);
@@ -383,6 +391,8 @@ __device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t
 // o-projection funnel -> attention residual -> MLP RMSNorm (forward_sites.cpp:1906-1937)
 __global__ void __launch_bounds__(kRowThreads)
 k_res1(RowBatch b, Dims d, const LayerDev* layer) {
+	pdl_wait();
+	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
 	int64_t* lut = (int64_t*)(smem + 34 * 8);
@@ -427,6 +437,8 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 // (forward_sites.cpp:1968-1987, :1694-1698)
 __global__ void __launch_bounds__(kRowThreads)
 k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
+	pdl_wait();
+	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
 	int64_t* lut = (int64_t*)(smem + 34 * 8);
@@ -473,6 +485,8 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 // gate / up funnels -> SwiGLU activation site (MlpActSite, forward_sites.cpp:796-864)
 __global__ void __launch_bounds__(kRowThreads, 1024 / kRowThreads)
 k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
+	pdl_wait();
+	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
 	unsigned long long* red = (unsigned long long*)smem;
 	int32_t* gsil = (int32_t*)(smem + 36 * 8);         // g * sigmoid(g) for the 255 gate codes, this row's scale
@@ -563,6 +577,8 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 // End of a call: hand each row's stream back to its sequence (or nowhere).
 __global__ void __launch_bounds__(kRowThreads)
 k_scatter(RowBatch b, Dims d, const RowSink* sink) {
+	pdl_wait();
+	pdl_release();
 	const int r = blockIdx.x, n = d.hidden;
 	const RowSink s = sink[r];
 	if (s.hidden == nullptr || b.status[r] != 0) return;
@@ -578,26 +594,26 @@ static size_t res_smem_bytes(const Dims& d) { return 34 * 8 + kLutBytes + (size_
 
 void launch_begin(const RowBatch& b, const Dims& d, const int8_t* embed, Scale c_embed,
                   const RowSource* src, const LayerDev* layer, cudaStream_t st) {
-	k_begin<<<b.m, kRowThreads, smem_wide(d), st>>>(b, d, embed, c_embed, src, layer);
+	launch_pdl(k_begin, dim3(b.m), dim3(kRowThreads), smem_wide(d), st, b, d, embed, c_embed, src, layer);
 }
 void launch_rmsnorm(const RowBatch& b, const Dims& d, const int8_t* gain, Scale site, cudaStream_t st) {
-	k_rmsnorm<<<b.m, kRowThreads, smem_wide(d), st>>>(b, d, gain, site);
+	launch_pdl(k_rmsnorm, dim3(b.m), dim3(kRowThreads), smem_wide(d), st, b, d, gain, site);
 }
 void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
                      KvPoolDev pool, const int32_t* cos, const int32_t* sin, cudaStream_t st) {
 	const size_t sm = 34 * 8 + 64 + (size_t)((d.hidden + d.kv_hidden + 15) & ~15) +
 	                  (size_t)(d.qkv_rows + d.head_dim) * 4;
-	k_qkv_post<<<b.m, kRowThreads, sm, st>>>(b, d, layer, layer_index, pool, cos, sin);
+	launch_pdl(k_qkv_post, dim3(b.m), dim3(kRowThreads), sm, st, b, d, layer, layer_index, pool, cos, sin);
 }
 void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
-	k_ctx_funnel<<<b.m, kRowThreads, 34 * 8 + (size_t)d.hidden * 4, st>>>(b, d, layer);
+	launch_pdl(k_ctx_funnel, dim3(b.m), dim3(kRowThreads), 34 * 8 + (size_t)d.hidden * 4, st, b, d, layer);
 }
 void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
-	k_res1<<<b.m, kRowThreads, res_smem_bytes(d), st>>>(b, d, layer);
+	launch_pdl(k_res1, dim3(b.m), dim3(kRowThreads), res_smem_bytes(d), st, b, d, layer);
 }
 void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev* next,
                  cudaStream_t st) {
-	k_res2<<<b.m, kRowThreads, res_smem_bytes(d), st>>>(b, d, layer, next);
+	launch_pdl(k_res2, dim3(b.m), dim3(kRowThreads), res_smem_bytes(d), st, b, d, layer, next);
 }
 size_t act_smem_bytes(const Dims& d) { return 36 * 8 + 256 * 4 + (size_t)d.inter * 4; }
 cudaError_t rows_configure(const Dims& d) {
@@ -620,10 +636,10 @@ cudaError_t rows_configure(const Dims& d) {
 }
 void launch_act(const RowBatch& b, const Dims& d, const LayerDev* layer, const int32_t* silu,
                 cudaStream_t st) {
-	k_act<<<b.m, kRowThreads, act_smem_bytes(d), st>>>(b, d, layer, silu);
+	launch_pdl(k_act, dim3(b.m), dim3(kRowThreads), act_smem_bytes(d), st, b, d, layer, silu);
 }
 void launch_scatter(const RowBatch& b, const Dims& d, const RowSink* sink, cudaStream_t st) {
-	k_scatter<<<b.m, kRowThreads, 0, st>>>(b, d, sink);
+	launch_pdl(k_scatter, dim3(b.m), dim3(kRowThreads), 0, st, b, d, sink);
 }
 
 }  // namespace sslm
