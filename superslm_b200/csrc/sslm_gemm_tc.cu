@@ -607,9 +607,13 @@ static bool tc_refuse(int reason) {
 
 bool launch_linear_tc(const LinearArgs& a, cudaStream_t st) {
 	if (a.K % 16 != 0 || ((uintptr_t)a.x & 15) || ((uintptr_t)a.w & 15)) return tc_refuse(1);
-	// two accumulators per weight tile once there is more than one 128-row group; narrower
-	// weight tiles when there would otherwise be fewer tiles than SMs
-	const bool two = a.M > BM;
+	// two accumulators per weight tile once there is more than one 128-row group -- unless the
+	// output is so small that even 128-row tiles leave SMs idle: then the smaller tile doubles
+	// the blocks and halves each block's main loop bytes and epilogue (the second read of a
+	// weight tile hits L2). Narrower weight tiles when there would otherwise be fewer tiles
+	// than SMs.
+	const int n128 = (a.N + 127) / 128;
+	const bool two = a.M > BM && n128 * ((a.M + 127) / 128) >= sm_count();
 	const int tiles128 = ((a.N + 127) / 128) * ((a.M + (two ? 255 : 127)) / (two ? 256 : 128));
 	const bool narrow = tiles128 < sm_count();
 	bool ok;
