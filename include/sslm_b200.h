@@ -146,6 +146,23 @@ SSLM_API sslm_status sslm_seq_set_adapter(sslm_seq seq, sslm_adapter adapter /* 
  *      [layer][K|V][kv_head][position][head_dim] order. */
 SSLM_API sslm_status sslm_seq_save(sslm_seq seq, void* buf, size_t* n);
 
+/* ---- state import and restart: sslm_abi_functions_g5_comparable.inc (sslm_seq_restore,
+ *      sslm_seq_reset); src/sslm_abi.cpp:2722-2990, :1820-1860.
+ *      Restore accepts the blobs sslm_seq_save writes here AND the ones the reference's CPU
+ *      library writes (SSB3, and its SSB2 predecessor), so a sequence saved on either side
+ *      continues bit-exactly on the other. Validation order and statuses follow the
+ *      reference: bad magic / lengths -> SSLM_INVALID_ARGUMENT, other model ->
+ *      SSLM_RESTORE_MODEL_MISMATCH, other KV precision -> SSLM_RESTORE_KV_MISMATCH, any
+ *      schema binding -> SSLM_RESTORE_SCHEMA_MISMATCH (this library maps no schemas), pool of
+ *      another model -> SSLM_INVALID_ARGUMENT, no free block -> SSLM_KV_POOL_EXHAUSTED.
+ *      A blob that carries damped-greedy history (sslm_decode_step_v2 state) is refused with
+ *      SSLM_INVALID_ARGUMENT: that decode mode is not part of this library.
+ *      Reset returns a sequence to the state of a freshly created one (an attached adapter
+ *      stays attached); mid-token -> SSLM_SEQ_RESET_MIDTOKEN_REJECTED. */
+SSLM_API sslm_status sslm_seq_restore(sslm_model model, sslm_kv_pool* pool, const void* buf, size_t n,
+                                      sslm_seq* out);
+SSLM_API sslm_status sslm_seq_reset(sslm_seq seq);
+
 /* ======================================================================================
  * Entry points below have no counterpart in the reference; they exist for device
  * selection, for the standalone linear-layer workload and for measurement.

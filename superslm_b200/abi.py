@@ -81,6 +81,8 @@ class SslmLib:
         "sslm_adapter_residency": (C.c_size_t, [_H]),
         "sslm_seq_set_adapter": (C.c_int, [_H, _H]),
         "sslm_seq_save": (C.c_int, [_H, C.c_void_p, C.POINTER(C.c_size_t)]),
+        "sslm_seq_restore": (C.c_int, [_H, C.POINTER(_H), C.c_void_p, C.c_size_t, C.POINTER(_H)]),
+        "sslm_seq_reset": (C.c_int, [_H]),
     }
 
     def __init__(self, path: str):
@@ -220,6 +222,21 @@ class Sequence:
         buf = (C.c_uint8 * n.value)()
         _chk("sslm_seq_save", self.eng.lib.sslm_seq_save(self.handle, buf, C.byref(n)))
         return bytes(buf[:n.value])
+
+    def reset(self):
+        _chk("sslm_seq_reset", self.eng.lib.sslm_seq_reset(self.handle))
+
+    @classmethod
+    def restore(cls, eng: "Engine", blob: bytes) -> "Sequence":
+        """A new sequence of `eng` from a save blob (either library's)."""
+        s = cls.__new__(cls)
+        s.eng = eng
+        s.handle = _H()
+        raw = np.frombuffer(blob, dtype=np.uint8)
+        _chk("sslm_seq_restore", eng.lib.sslm_seq_restore(eng.model, C.byref(eng.pool), raw.ctypes.data, raw.size,
+                                                          C.byref(s.handle)))
+        eng.seqs.append(s)
+        return s
 
     def release(self):
         if self.handle:

@@ -419,4 +419,39 @@ void launch_kv_export(const Dims& d, KvPoolDev pool, const int32_t* pages, int c
 	k_kv_export<<<148 * 4, 256, 0, st>>>(d, pool, pages, context_length, layer_index, out);
 }
 
+// The inverse: scatter a canonical block (a save blob's K/V) into the sequence's pages.
+// Only the valid positions are written; everything else in the pages is never read.
+__global__ void k_kv_import(Dims d, KvPoolDev pool, const int32_t* pages, int context_length,
+                            int layer_index, const int8_t* in) {
+	const int hd = d.head_dim, vec = hd / 16;
+	const int64_t per_plane = (int64_t)d.context_cap * vec;
+	const int64_t total = (int64_t)d.layers * 2 * d.kv_heads * per_plane;
+	for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+	     i += (int64_t)gridDim.x * blockDim.x) {
+		const int64_t plane = i / per_plane, within = i - plane * per_plane;
+		const int pos = (int)(within / vec), v = (int)(within % vec);
+		const int kvh = (int)(plane % d.kv_heads);
+		const int is_v = (int)((plane / d.kv_heads) % 2);
+		const int layer = (int)(plane / (2 * d.kv_heads));
+		const int valid = context_length + (layer < layer_index ? 1 : 0);
+		if (pos >= valid) continue;
+		const int4 val = ((const int4*)in)[i];
+		int8_t* dst = pool.base + kv_plane_offset(d, pool, layer, kvh, is_v) +
+		              (int64_t)pages[pos / kPageTokens] * (kPageTokens * hd);
+		const int slot = pos % kPageTokens;
+		if (!is_v) {
+			*((int4*)(dst + slot * hd) + v) = val;
+		} else {
+			const uint32_t w[4] = {(uint32_t)val.x, (uint32_t)val.y, (uint32_t)val.z, (uint32_t)val.w};
+			for (int j = 0; j < 16; ++j)
+				dst[(v * 16 + j) * kPageTokens + slot] = (int8_t)((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+		}
+	}
+}
+
+void launch_kv_import(const Dims& d, KvPoolDev pool, const int32_t* pages, int context_length,
+                      int layer_index, const int8_t* in, cudaStream_t st) {
+	k_kv_import<<<148 * 4, 256, 0, st>>>(d, pool, pages, context_length, layer_index, in);
+}
+
 }  // namespace sslm
