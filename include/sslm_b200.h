@@ -35,6 +35,7 @@ extern "C" {
 typedef struct sslm_model_s* sslm_model;
 typedef struct sslm_seq_s* sslm_seq;
 typedef struct sslm_adapter_s* sslm_adapter;
+typedef struct sslm_prefix_s* sslm_prefix;
 typedef struct sslm_kv_pool_s* sslm_kv_pool;
 typedef struct sslm_workspace_s* sslm_workspace;
 
@@ -162,6 +163,25 @@ SSLM_API sslm_status sslm_seq_save(sslm_seq seq, void* buf, size_t* n);
 SSLM_API sslm_status sslm_seq_restore(sslm_model model, sslm_kv_pool* pool, const void* buf, size_t n,
                                       sslm_seq* out);
 SSLM_API sslm_status sslm_seq_reset(sslm_seq seq);
+
+/* ---- shared prompt prefixes: sslm_abi_functions_g5_comparable.inc (sslm_prefix_begin,
+ *      sslm_prefix_prefill, sslm_prefix_freeze, sslm_prefix_release, sslm_seq_adopt_prefix);
+ *      src/sslm_abi.cpp:1584-1694, :1870-1925.
+ *      A prefix holds one block credit of the pool, is prefilled like a sequence, frozen, and
+ *      then adopted by any number of sequences, each of which continues as if it had prefilled
+ *      the same tokens itself (same tokens, same save blobs). The reference copies the whole KV
+ *      block at adoption; this library shares the prefix's full 16-token pages between the
+ *      prefix and its adopters and copies only the last, partly filled page. Prefill of a frozen
+ *      prefix -> SSLM_PREFIX_FROZEN_REJECTED; adopting a prefix that is not frozen, or one of
+ *      another model -> SSLM_INVALID_ARGUMENT. A prefix may be released while sequences that
+ *      adopted it live on. */
+SSLM_API sslm_status sslm_prefix_begin(sslm_model model, sslm_kv_pool* pool, sslm_prefix* out);
+SSLM_API sslm_status sslm_prefix_prefill(sslm_model model, sslm_prefix prefix, const int32_t* tokens, int32_t count,
+                                         int32_t chunk_budget, sslm_span_kind kind, sslm_workspace ws,
+                                         int32_t* consumed);
+SSLM_API sslm_status sslm_prefix_freeze(sslm_prefix prefix);
+SSLM_API sslm_status sslm_prefix_release(sslm_prefix prefix);
+SSLM_API sslm_status sslm_seq_adopt_prefix(sslm_seq seq, sslm_prefix prefix);
 
 /* ======================================================================================
  * Entry points below have no counterpart in the reference; they exist for device

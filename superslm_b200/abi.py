@@ -83,6 +83,12 @@ class SslmLib:
         "sslm_seq_save": (C.c_int, [_H, C.c_void_p, C.POINTER(C.c_size_t)]),
         "sslm_seq_restore": (C.c_int, [_H, C.POINTER(_H), C.c_void_p, C.c_size_t, C.POINTER(_H)]),
         "sslm_seq_reset": (C.c_int, [_H]),
+        "sslm_prefix_begin": (C.c_int, [_H, C.POINTER(_H), C.POINTER(_H)]),
+        "sslm_prefix_prefill": (C.c_int, [_H, _H, C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_int, _H,
+                                          C.POINTER(C.c_int32)]),
+        "sslm_prefix_freeze": (C.c_int, [_H]),
+        "sslm_prefix_release": (C.c_int, [_H]),
+        "sslm_seq_adopt_prefix": (C.c_int, [_H, _H]),
     }
 
     def __init__(self, path: str):

@@ -449,6 +449,20 @@ __global__ void k_kv_import(Dims d, KvPoolDev pool, const int32_t* pages, int co
 	}
 }
 
+// Copy one page id to another in every (layer, kv head, K|V) plane: the private copy a
+// sequence takes of an adopted prefix's last, partly filled page.
+__global__ void k_page_copy(Dims d, KvPoolDev pool, int src_page, int dst_page) {
+	const int64_t page_bytes = (int64_t)kPageTokens * d.head_dim;
+	const int64_t plane_stride = pool.num_pages * page_bytes;
+	int8_t* plane = pool.base + (int64_t)blockIdx.x * plane_stride;
+	const int4* src = (const int4*)(plane + (int64_t)src_page * page_bytes);
+	int4* dst = (int4*)(plane + (int64_t)dst_page * page_bytes);
+	for (int i = threadIdx.x; i < (int)(page_bytes / 16); i += blockDim.x) dst[i] = src[i];
+}
+void launch_page_copy(const Dims& d, KvPoolDev pool, int src_page, int dst_page, cudaStream_t st) {
+	k_page_copy<<<d.layers * d.kv_heads * 2, 128, 0, st>>>(d, pool, src_page, dst_page);
+}
+
 void launch_kv_import(const Dims& d, KvPoolDev pool, const int32_t* pages, int context_length,
                       int layer_index, const int8_t* in, cudaStream_t st) {
 	k_kv_import<<<148 * 4, 256, 0, st>>>(d, pool, pages, context_length, layer_index, in);

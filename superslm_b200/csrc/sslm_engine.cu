@@ -305,6 +305,7 @@ extern "C" sslm_status sslm_kv_pool_create(sslm_model model, void* buf, size_t b
 	try {
 		p->free_pages.reserve(p->dev.num_pages);
 		for (int64_t i = p->dev.num_pages - 1; i >= 0; --i) p->free_pages.push_back((int32_t)i);
+		p->page_refs.assign((size_t)p->dev.num_pages, 0u);
 	} catch (const std::bad_alloc&) {
 		cudaFree(p->dev.base);
 		delete p;

@@ -102,6 +102,9 @@ struct sslm_kv_pool_s {
 	sslm::KvPoolDev dev{};
 	std::mutex mutex;
 	std::vector<int32_t> free_pages;
+	// holders per page: a frozen prefix's full pages are shared, read-only, by every sequence
+	// that adopted it; a page returns to the free list when its last holder lets go
+	std::vector<uint32_t> page_refs;
 	std::atomic<uint32_t> live_refs{0};
 };
 
@@ -132,4 +135,11 @@ struct sslm_seq_s {
 
 	int8_t* hidden(int slot) const { return (int8_t*)(d_state + (size_t)slot * state_stride); }
 	sslm::Scale* scale(int slot) const { return (sslm::Scale*)(d_state + (size_t)slot * state_stride + scale_off); }
+};
+
+// A prefix is a sequence that can be prefilled, then frozen and adopted by sequences
+// (sslm_prefix_s, src/sslm_abi.cpp:1584-1694).
+struct sslm_prefix_s {
+	sslm_seq_s* inner = nullptr;
+	bool frozen = false;
 };

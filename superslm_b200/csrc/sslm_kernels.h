@@ -117,6 +117,8 @@ void launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, i
 // [layer][K|V][kv_head][position][head_dim]; positions beyond `valid(layer)` are zero
 void launch_kv_export(const Dims& d, KvPoolDev pool, const int32_t* pages, int context_length,
                       int layer_index, int8_t* out, cudaStream_t st);
+// copy page src_page to dst_page in every (layer, kv head, K|V) plane
+void launch_page_copy(const Dims& d, KvPoolDev pool, int src_page, int dst_page, cudaStream_t st);
 // the inverse: scatter a canonical block into the sequence's pages (valid positions only)
 void launch_kv_import(const Dims& d, KvPoolDev pool, const int32_t* pages, int context_length,
                       int layer_index, const int8_t* in, cudaStream_t st);
