@@ -15,9 +15,9 @@
  *    allocated by the call (SSLM_ALLOCATION_FAILED if the device cannot provide it).
  *  - sslm_kv_block_size still returns layers*context_cap*kv_heads*head_dim*2 bytes; a
  *    pool of N blocks holds N full-length sequences, stored as 16-token pages.
- *  - q/k/v bias sections (BIA1) and the int16 KV precision are rejected at map time with
- *    SSLM_ARTIFACT_REJECTED; the Option-G header flag is ignored, as the reference's CPU
- *    ABI path ignores it.
+ *  - the int16 KV precision is rejected at map time with SSLM_ARTIFACT_REJECTED; the
+ *    Option-G header flag is ignored, as the reference's CPU ABI path ignores it
+ *    (src/sslm_abi.cpp:1539, :2256 always run the legacy K landing).
  * There is no CPU fallback: every compute verb fails with SSLM_ALLOCATION_FAILED if no
  * CUDA device is usable.
  */

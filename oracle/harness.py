@@ -54,7 +54,7 @@ class Layer(C.Structure):
     _fields_ = ([(n, C.c_void_p) for n in
                  ("q_w", "k_w", "v_w", "o_w", "gate_w", "up_w", "down_w", "attn_gain", "mlp_gain",
                   "q_fold", "k_fold", "v_fold", "o_fold", "gate_fold", "up_fold", "down_fold",
-                  "ctx_fold", "k_recip", "v_recip", "softmax_khead")] +
+                  "ctx_fold", "k_recip", "v_recip", "softmax_khead", "q_bias", "k_bias", "v_bias")] +
                 [(n, Scale) for n in
                  ("c_attn_norm", "c_q", "c_o", "c_ctx", "c_attn_res", "c_mlp_norm", "c_gate", "c_up",
                   "c_act", "c_down", "c_mlp_res")])
@@ -188,6 +188,7 @@ class PortModel:
         rope = v.tensors(A.SEC_ROPE, np.int64)
         cc = v.constants(A.SEC_COMPOSITION)
         rec = v.constants(A.SEC_KV_RECIP)
+        bia = v.tensors(A.SEC_BIASES, np.int64) if A.SEC_BIASES in v.sections else {}
         silu = np.frombuffer(v.sections[A.SEC_SIGMOID_LUT], dtype=np.int32, offset=16).copy()
         L = cfg["num_hidden_layers"]
         KVH = cfg["num_key_value_heads"]
@@ -211,6 +212,9 @@ class PortModel:
             ly.v_recip = keep(np.array([rec["%s.v_head%d" % (p, h)] for h in range(KVH)], dtype=np.int64))
             ly.softmax_khead = keep(np.array([cc["%s.softmax_khead%d" % (p, h)] for h in range(KVH)],
                                              dtype=np.int64))
+            for proj in ("q", "k", "v"):      # BIA1: optional, per projection
+                bt = bia.get("%s.%s_proj" % (p, proj))
+                setattr(ly, proj + "_bias", keep(np.ascontiguousarray(bt, dtype=np.int64)) if bt is not None else None)
             for field, key in (("c_attn_norm", "attn_norm"), ("c_q", "q_proj"), ("c_o", "o_proj"),
                                ("c_ctx", "attn_ctx"), ("c_attn_res", "attn_residual"),
                                ("c_mlp_norm", "mlp_norm"), ("c_gate", "gate_proj"), ("c_up", "up_proj"),

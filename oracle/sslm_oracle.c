@@ -444,7 +444,56 @@ static void lora_delta(const int8_t* in, size_t k_in, const osc_lora_proj* p, ui
 	}
 }
 
-/* ProjectAndFunnel (forward_sites.cpp:1148-1164, :1114-1146), no bias */
+/* BiasReconcileWide (src/intmath.cpp:397-418) with RoundingDivideByPOTWide (:365-378) */
+int osc_bias_reconcile(int64_t b, int64_t r_a, int64_t e_a, int64_t* out) {
+	*out = 0;
+	if (e_a < -92 || e_a > -29) return 0;       /* 0 <= 30 + 62 + e_a <= 63 */
+	const int exponent = (int)(92 + e_a);
+	const s128 wide = (s128)b * (s128)r_a;
+	const uint64_t mask = ((uint64_t)1 << exponent) - 1u;
+	const uint64_t rem = (uint64_t)wide & mask;
+	const uint64_t thr = (mask >> 1) + (wide < 0 ? 1u : 0u);
+	s128 r = wide >> exponent;
+	if (rem > thr) r += 1;
+	*out = (int64_t)r;
+	return r >= (s128)INT64_MIN && r <= (s128)INT64_MAX;
+}
+
+/* ApplyBiasReconcileRow (src/forward/forward_sites.cpp:1015-1036): exponent gate, then a
+ * checking pass over every element (term fits, acc + term fits), then the add */
+int osc_apply_bias_row(int64_t* acc, size_t n, const int64_t* bias, int64_t in_scale_m, int64_t in_scale_e) {
+	if (in_scale_e < -92 || in_scale_e > -29) return OSC_RDIVPOT_EXPONENT_OUT_OF_DOMAIN;
+	const int64_t r_a = osc_dyn_recip(in_scale_m);
+	for (size_t i = 0; i < n; ++i) {
+		int64_t term;
+		if (!osc_bias_reconcile(bias[i], r_a, in_scale_e, &term)) return OSC_BIAS_RECONCILE_PRODUCT_OUT_OF_DOMAIN;
+		int64_t sum;
+		if (__builtin_add_overflow(acc[i], term, &sum)) return OSC_BIAS_RECONCILE_PRODUCT_OUT_OF_DOMAIN;
+	}
+	for (size_t i = 0; i < n; ++i) {
+		int64_t term;
+		osc_bias_reconcile(bias[i], r_a, in_scale_e, &term);
+		acc[i] += term;
+	}
+	return OSC_OK;
+}
+
+/* ProjectAndFunnel (forward_sites.cpp:1148-1164, :1114-1146): fold, LoRA delta, bias, funnel */
+static int project_funnel_bias(const int8_t* in, osc_scale in_scale, const int8_t* w, size_t k_in,
+                               size_t n_out, const int32_t* fold, osc_scale c, const osc_lora_proj* lp,
+                               uint32_t rank, const int64_t* bias, int8_t* out, osc_scale* out_scale) {
+	int64_t* acc = (int64_t*)malloc(n_out * sizeof(int64_t));
+	osc_gemm(in, w, 1, k_in, n_out, acc);
+	for (size_t i = 0; i < n_out; ++i) acc[i] = osc_fold(acc[i], fold[3 * i], fold[3 * i + 1], fold[3 * i + 2]);
+	lora_delta(in, k_in, lp, rank, n_out, acc);
+	int st = OSC_OK;
+	if (bias != NULL) st = osc_apply_bias_row(acc, n_out, bias, in_scale.m, in_scale.e);
+	if (st == OSC_OK) st = osc_funnel(acc, n_out, &in_scale, 1, c, out, out_scale);
+	free(acc);
+	return st;
+}
+
+/* the same for the projections that never carry a bias (o, gate, up, down) */
 static int project_funnel(const int8_t* in, osc_scale in_scale, const int8_t* w, size_t k_in,
                           size_t n_out, const int32_t* fold, osc_scale c, const osc_lora_proj* lp,
                           uint32_t rank, int8_t* out, osc_scale* out_scale) {
@@ -496,8 +545,8 @@ static int one_layer(const osc_model* m, const osc_lora_layer* lora, uint32_t l,
 	osc_scale s_n, s_q, s_ctx, s_o, s_a, s_n2, s_g, s_u, s_act, s_d;
 
 	if ((st = osc_rmsnorm_site(hidden, lw->attn_gain, H, lw->c_attn_norm, normed, &s_n))) goto done;
-	if ((st = project_funnel(normed, s_n, lw->q_w, H, H, lw->q_fold, lw->c_q, lora ? &lora->q : NULL,
-	                         rank, q, &s_q))) goto done;
+	if ((st = project_funnel_bias(normed, s_n, lw->q_w, H, H, lw->q_fold, lw->c_q, lora ? &lora->q : NULL,
+	                              rank, lw->q_bias, q, &s_q))) goto done;
 	/* K/V projection + landing (LandTokenKVRow, forward_sites.cpp:1281-1418, legacy branch) */
 	osc_gemm(normed, lw->k_w, 1, H, kvh, kacc);
 	osc_gemm(normed, lw->v_w, 1, H, kvh, vacc);
@@ -507,6 +556,8 @@ static int one_layer(const osc_model* m, const osc_lora_layer* lora, uint32_t l,
 	}
 	lora_delta(normed, H, lora ? &lora->k : NULL, rank, kvh, kacc);
 	lora_delta(normed, H, lora ? &lora->v : NULL, rank, kvh, vacc);
+	if (lw->k_bias != NULL && (st = osc_apply_bias_row(kacc, kvh, lw->k_bias, s_n.m, s_n.e))) goto done;
+	if (lw->v_bias != NULL && (st = osc_apply_bias_row(vacc, kvh, lw->v_bias, s_n.m, s_n.e))) goto done;
 	for (size_t h = 0; h < KVH; ++h) {
 		int8_t* krow = kv_row(m, kv, l, 0, h, position);
 		int8_t* vrow = kv_row(m, kv, l, 1, h, position);

@@ -42,7 +42,8 @@ enum {
 	OSC_KV_CAPACITY_EXHAUSTED = 11,
 	OSC_SOFTMAX_KERNEL_REFUSED = 20,
 	OSC_RESIDUAL_MAGNITUDE_OUT_OF_DOMAIN = 21,
-	OSC_IEXP_SCALE_DERIVATION_OUT_OF_DOMAIN = 23
+	OSC_IEXP_SCALE_DERIVATION_OUT_OF_DOMAIN = 23,
+	OSC_BIAS_RECONCILE_PRODUCT_OUT_OF_DOMAIN = 24
 };
 
 /* ---- scalar primitives ------------------------------------------------- */
@@ -58,6 +59,11 @@ int64_t osc_isqrt(int64_t n);                               /* src/intmath.cpp:5
 int64_t osc_floor_div(int64_t a, int64_t b);                /* src/forward/forward_sites.cpp:399-408 */
 void osc_rope_pair(int32_t x, int32_t y, int32_t c, int32_t s, int64_t* ox, int64_t* oy); /* src/intmath.cpp:782-792 */
 int64_t osc_fold(int64_t acc, int32_t identity, int32_t mult, int32_t shift);      /* forward_sites.cpp:461-470 */
+/* BiasReconcileWide with q_B = 30 (src/intmath.cpp:397-418): 1 and *out = round_half_away(b * r_a / 2^(92 + e_a))
+ * when the exponent is in [0,63] and the result fits int64, else 0 */
+int osc_bias_reconcile(int64_t b, int64_t r_a, int64_t e_a, int64_t* out);
+/* ApplyBiasReconcileRow (src/forward/forward_sites.cpp:1015-1036): status; acc untouched on refusal */
+int osc_apply_bias_row(int64_t* acc, size_t n, const int64_t* bias, int64_t in_scale_m, int64_t in_scale_e);
 int64_t osc_amp_fold(int64_t acc, int32_t identity, int32_t mult, int32_t exponent); /* forward_sites.cpp:472-481 */
 osc_scale osc_combine(osc_scale a, osc_scale b);            /* src/forward/checked_chain_funnel.cpp:157-180 */
 int64_t osc_landing_rescale(int64_t code, int64_t m_a, int64_t r_t, int64_t e_a, int64_t e_t,
@@ -103,6 +109,7 @@ typedef struct {
 	const int32_t *ctx_fold;                                        /* [heads,3] */
 	const int64_t *k_recip, *v_recip;                               /* [kv_heads,3] (m_t,e_t,R_t) */
 	const int64_t *softmax_khead;                                   /* [kv_heads,2] (m,e) */
+	const int64_t *q_bias, *k_bias, *v_bias;                        /* BIA1 codes (Q30) or NULL: [hidden], [kv_hidden] x2 */
 	osc_scale c_attn_norm, c_q, c_o, c_ctx, c_attn_res, c_mlp_norm, c_gate, c_up, c_act, c_down,
 	    c_mlp_res;
 } osc_layer;

@@ -288,8 +288,11 @@ def _fold_rows(seed, name, n, shift_lo, shift_hi) -> np.ndarray:
 
 
 def build_synthetic_model(shape: Shape | str, seed: int, context_cap: int,
-                          shift_lo: int = 8, shift_hi: int = 20) -> bytes:
-    """A loadable base artifact of the given architecture (header flags 0, no BIA1)."""
+                          shift_lo: int = 8, shift_hi: int = 20, bias_bits: int = 0,
+                          flags: int = 0) -> bytes:
+    """A loadable base artifact of the given architecture (header flags 0). bias_bits > 0 adds a
+    BIA1 section: int64 q/k/v bias codes (Q30 against the projection's input scale, as the
+    converter writes them for Qwen2.5's q/k/v biases), uniform in +-2^bias_bits."""
     sh = SHAPES[shape] if isinstance(shape, str) else shape
     H, L, I, KV = sh.hidden, sh.layers, sh.inter, sh.kv_hidden
     weights: list[tuple[str, np.ndarray]] = []
@@ -297,6 +300,7 @@ def build_synthetic_model(shape: Shape | str, seed: int, context_cap: int,
     consts: list[tuple[str, tuple[int, ...]]] = []
     kv_scales: list[tuple[str, tuple[int, ...]]] = []
     kv_recips: list[tuple[str, tuple[int, ...]]] = []
+    biases: list[tuple[str, np.ndarray]] = []
 
     weights.append(("embed", stream_int8(seed, "embed", sh.vocab * H).reshape(sh.vocab, H)))
     weights.append(("final_norm.gain", stream_int8(seed, "final_norm.gain", H)))
@@ -318,6 +322,13 @@ def build_synthetic_model(shape: Shape | str, seed: int, context_cap: int,
         ctx = np.zeros((sh.heads, 3), dtype=np.int32)
         ctx[:, 0] = 1
         wsc.append((p + ".ctx_fold", ctx))
+        if bias_bits > 0:
+            for proj, n_out in (("q_proj", H), ("k_proj", KV), ("v_proj", KV)):
+                nm = "%s.%s" % (p, proj)
+                lo_bits = max(bias_bits - 20, 0)
+                hi = stream_uniform(seed, nm + ".bias_hi", n_out, -(1 << min(bias_bits, 20)), 1 << min(bias_bits, 20))
+                lo = stream_uniform(seed, nm + ".bias_lo", n_out, 0, (1 << lo_bits) - 1) if lo_bits else 0
+                biases.append((nm, (hi * (1 << lo_bits) + lo).astype(np.int64)))
 
         s_norm_in = _s_ref(H, 0.58)
         consts.append((p + ".attn_norm", norm_c))
@@ -350,7 +361,9 @@ def build_synthetic_model(shape: Shape | str, seed: int, context_cap: int,
         (SEC_KV_SCALES, keyed_constants(kv_scales, 2)),
         (SEC_KV_RECIP, keyed_constants(kv_recips, 3)),
     ]
-    return build_container(sections)
+    if biases:
+        sections.insert(3, (SEC_BIASES, tensor_manifest(b"BIA1", 8, biases)))
+    return build_container(sections, flags)
 
 
 def build_synthetic_adapter(base: bytes, seed: int, rank: int = 16,

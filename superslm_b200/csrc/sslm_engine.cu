@@ -86,13 +86,13 @@ extern "C" sslm_status sslm_model_map(const void* data, size_t size, sslm_model*
 		return SSLM_ALLOCATION_FAILED;
 	}
 	const ConfigView& c = v.config();
-	// what this implementation does not run: int16 KV, q/k/v biases, geometries outside
-	// the kernels' vector widths
+	// what this implementation does not run: int16 KV, geometries outside the kernels'
+	// vector widths
 	if (c.kv_precision != 0) return SSLM_ARTIFACT_REJECTED;
-	if (v.has(kSecBiases)) return SSLM_ARTIFACT_REJECTED;
-	// header flags bit 0 selects the fused wide K landing (RopeApplyPairWide,
-	// src/forward/forward_sites.cpp:1349-1395); only the legacy landing is implemented
-	if (v.flags() & 1u) return SSLM_ARTIFACT_REJECTED;
+	// Header flags bit 0 (fused wide K landing, RopeApplyPairWide) is deliberately not looked
+	// at: the reference's sslm_prefill / sslm_decode_step always run the legacy landing
+	// whatever the flag says (src/sslm_abi.cpp:1539 passes option_g_fused_k_landing = false,
+	// :2256 calls the overload without it), and so does this library.
 	if (c.hidden % 16 || c.inter % 16 || c.head_dim % 16 || c.head_dim > 128 ||
 	    (128 % c.head_dim) != 0 || c.heads / c.kv_heads > 8 || c.kv_heads > 16)
 		return SSLM_ARTIFACT_REJECTED;
@@ -120,7 +120,8 @@ extern "C" sslm_status sslm_model_map(const void* data, size_t size, sslm_model*
 	bytes += L * 12 * ((H + 2 * KV) + H + 2 * I + H + c.heads);
 	bytes += L * (2 * c.kv_heads * 3 * 8 + c.kv_heads * 2 * 8);
 	bytes += 2 * (size_t)c.context_cap * (c.head_dim / 2) * 4 + 1025 * 4 + L * sizeof(LayerDev);
-	bytes += (L * 24 + 64) * 256;
+	bytes += L * (H + 2 * KV) * 8;                       // q/k/v bias codes, when the artifact has them
+	bytes += (L * 28 + 64) * 256;
 	if (!cuda_ok(cudaMalloc((void**)&m->arena.base, bytes))) {
 		delete m;
 		return SSLM_ALLOCATION_FAILED;
@@ -230,6 +231,13 @@ extern "C" sslm_status sslm_model_map(const void* data, size_t size, sslm_model*
 		ld.k_recip = (const int64_t*)up.put(kr.data(), kr.size() * 8);
 		ld.v_recip = (const int64_t*)up.put(vr.data(), vr.size() * 8);
 		ld.sm_khead = (const int64_t*)up.put(sk.data(), sk.size() * 8);
+		// BIA1 (layer_marshal.h:247-253): each of the three is optional on its own
+		const TensorView *qb = v.bias(p + "q_proj"), *kb = v.bias(p + "k_proj"), *vb = v.bias(p + "v_proj");
+		if ((qb && qb->elem_count != H) || (kb && kb->elem_count != KV) || (vb && vb->elem_count != KV))
+			return fail(SSLM_ARTIFACT_REJECTED);
+		ld.b_q = qb ? (const int64_t*)up.put(qb->data, H * 8) : nullptr;
+		ld.b_k = kb ? (const int64_t*)up.put(kb->data, KV * 8) : nullptr;
+		ld.b_v = vb ? (const int64_t*)up.put(vb->data, KV * 8) : nullptr;
 		ld.c_attn_norm = read_scale(v, p + "attn_norm", &ok);
 		ld.c_q = read_scale(v, p + "q_proj", &ok);
 		ld.c_o = read_scale(v, p + "o_proj", &ok);

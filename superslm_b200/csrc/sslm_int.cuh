@@ -30,11 +30,13 @@ enum Status : int32_t {
 	kLogitNarrowingOverflow = 2,
 	kCarriedScaleMantissaOutOfDomain = 4,
 	kSiluScaleOutOfDomain = 5,
+	kRoundingDivideExponentOutOfDomain = 6,
 	kSoftmaxRowWidthOutOfDomain = 7,
 	kTokenIdOutOfRange = 8,
 	kSoftmaxKernelRefused = 20,
 	kResidualMagnitudeOutOfDomain = 21,
 	kIExpScaleDerivationOutOfDomain = 23,
+	kBiasReconcileProductOutOfDomain = 24,
 	kInternalWaitTimeout = 100,  // this implementation only: a bounded device-side wait ran out
 };
 
@@ -324,6 +326,46 @@ SSLM_HD int64_t isqrt64(int64_t n) {
 		bit >>= 2;
 	}
 	return root;
+}
+
+// -------------------------------------------------------------- q/k/v bias (BIA1)
+// C28 bias reconciliation: acc_i += round_half_away(B_i * R_a / 2^(q_B + 62 + e_a)) with
+// q_B = 30, R_a = Recip(S[input].m), e_a = S[input].e (ApplyBiasReconcileRow,
+// src/forward/forward_sites.cpp:1015-1036; BiasReconcileWide, src/intmath.cpp:397-418).
+// The composed exponent must lie in [0, 63] (RoundingDivideByPotComposedExponentInDomain,
+// src/intmath.cpp:381-395).
+SSLM_HD bool bias_exponent_in_domain(int64_t e_a, int* exponent) {
+	if (e_a < -92 || e_a > -29) return false;
+	*exponent = (int)(92 + e_a);
+	return true;
+}
+// false when the rounded term does not fit int64 (the reference refuses the row)
+SSLM_HD bool bias_reconcile(int64_t b, int64_t r_a, int exponent, int64_t* term) {
+	const U128 w = smul64(b, r_a);
+	const uint64_t mask = ((uint64_t)1 << exponent) - 1u;     // exponent <= 63
+	const bool neg = (int64_t)w.hi < 0;
+	const uint64_t rem = w.lo & mask;
+	const uint64_t thr = (mask >> 1) + (neg ? 1u : 0u);
+	U128 sh;                                                   // arithmetic shift right by exponent
+	if (exponent == 0) {
+		sh = w;
+	} else {
+		sh.lo = (w.lo >> exponent) | (w.hi << (64 - exponent));
+		sh.hi = (uint64_t)((int64_t)w.hi >> exponent);
+	}
+	if (rem > thr) {
+		sh.lo += 1u;
+		if (sh.lo == 0u) sh.hi += 1u;
+	}
+	*term = (int64_t)sh.lo;
+	return sh.hi == ((int64_t)sh.lo < 0 ? ~0ull : 0ull);
+}
+// acc + term, false on int64 overflow (CheckBiasAccumulateMagnitudeDomain,
+// src/forward/checked_chain_funnel.cpp:454-482)
+SSLM_HD bool bias_accumulate(int64_t acc, int64_t term, int64_t* out) {
+	const uint64_t ua = (uint64_t)acc, ub = (uint64_t)term, sum = ua + ub;
+	*out = (int64_t)sum;
+	return !((((ua ^ ub) >> 63) == 0) && (((ua ^ sum) >> 63) != 0));
 }
 
 // ---------------------------------------------------------------- site scalars

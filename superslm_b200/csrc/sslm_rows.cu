@@ -231,24 +231,87 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	const unsigned long long mx = take_rowmax(b, r, 0, red);
 	if (b.status[r] != 0) return;
 
-	const FunnelParams fp = funnel_params(mx, &ns, 1, c_q);
+	auto wv = [&](int i) -> int64_t { return vec ? (int64_t)sw[i] : load_wide(b, r, i); };
+	// q/k/v bias (BIA1): term_i = round(B_i * Recip(S[x].m) / 2^(92 + S[x].e)) joins the folded
+	// accumulator (after the LoRA delta) before the q funnel and before the K/V landing
+	// (ApplyBiasReconcileRow, forward_sites.cpp:1015-1036). The exponent gate and R_a are per
+	// row; a term or a sum that leaves int64 refuses the row.
+	const bool any_bias = lw.b_q != nullptr || lw.b_k != nullptr || lw.b_v != nullptr;
+	int bexp = 0;
+	int64_t r_a = 0;
+	bool bias_gate = true;
+	if (any_bias) {
+		r_a = dyn_recip(ns.m);
+		bias_gate = bias_exponent_in_domain(ns.e, &bexp);
+	}
+	auto biased = [&](int64_t acc, const int64_t* bias, int i, bool* ok) -> int64_t {
+		int64_t term, sum;
+		const bool t_ok = bias_reconcile(bias[i], r_a, bexp, &term);
+		const bool s_ok = bias_accumulate(acc, term, &sum);
+		*ok = t_ok && s_ok;
+		return sum;
+	};
+	unsigned long long mxq = mx;
+	if (lw.b_q != nullptr) {
+		if (!bias_gate) {
+			set_status(b, r, kRoundingDivideExponentOutOfDomain);
+			return;
+		}
+		// the row maximum the GEMM reduced does not include the bias: take it here
+		unsigned long long lmx = 0;
+		long long bad = 0;
+		for (int i = threadIdx.x; i < H; i += blockDim.x) {
+			bool ok;
+			const unsigned long long a = abs_u64(biased(wv(i), lw.b_q, i, &ok));
+			if (!ok) bad = 1;
+			lmx = a > lmx ? a : lmx;
+		}
+		bad = block_sum_i64(bad, red);
+		if (bad != 0) {
+			set_status(b, r, kBiasReconcileProductOutOfDomain);
+			return;
+		}
+		mxq = block_max_u64(lmx, red);
+	}
+	const FunnelParams fp = funnel_params(mxq, &ns, 1, c_q);
 	if (fp.status != kOk) {
 		set_status(b, r, fp.status);
 		return;
 	}
-	auto wv = [&](int i) -> int64_t { return vec ? (int64_t)sw[i] : load_wide(b, r, i); };
-	for (int i = threadIdx.x; i < H; i += blockDim.x) sq[i] = requant_code(wv(i), fp.r, fp.s);
+	if (lw.b_q != nullptr) {
+		for (int i = threadIdx.x; i < H; i += blockDim.x) {
+			bool ok;
+			sq[i] = requant_code(biased(wv(i), lw.b_q, i, &ok), fp.r, fp.s);
+		}
+	} else {
+		for (int i = threadIdx.x; i < H; i += blockDim.x) sq[i] = requant_code(wv(i), fp.r, fp.s);
+	}
+	if ((lw.b_k != nullptr || lw.b_v != nullptr) && !bias_gate) {
+		set_status(b, r, kRoundingDivideExponentOutOfDomain);
+		return;
+	}
 
 	// K/V landing
 	const int page = b.rows[r].pages[pos / kPageTokens];
 	const int slot = pos % kPageTokens;
-	long long sat = 0;
+	long long sat = 0, kv_bad = 0;
 	for (int i = threadIdx.x; i < d.kv_hidden; i += blockDim.x) {
 		const int h = i / hd, dd = i - h * hd;
 		bool s1, s2;
-		const int64_t kraw = landing_rescale(wv(H + i), ns.m, lw.k_recip[3 * h + 2], ns.e,
+		int64_t kacc = wv(H + i), vacc = wv(H + d.kv_hidden + i);
+		if (lw.b_k != nullptr) {
+			bool ok;
+			kacc = biased(kacc, lw.b_k, i, &ok);
+			if (!ok) kv_bad = 1;
+		}
+		if (lw.b_v != nullptr) {
+			bool ok;
+			vacc = biased(vacc, lw.b_v, i, &ok);
+			if (!ok) kv_bad = 1;
+		}
+		const int64_t kraw = landing_rescale(kacc, ns.m, lw.k_recip[3 * h + 2], ns.e,
 		                                     lw.k_recip[3 * h + 1], &s1, nullptr);
-		const int64_t vraw = landing_rescale(wv(H + d.kv_hidden + i), ns.m,
+		const int64_t vraw = landing_rescale(vacc, ns.m,
 		                                     lw.v_recip[3 * h + 2], ns.e, lw.v_recip[3 * h + 1], &s2, nullptr);
 		sat += (s1 ? 1 : 0) + (s2 ? 1 : 0);
 		sk[i] = (int8_t)clamp127(kraw);
@@ -260,6 +323,13 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	}
 	sat = block_sum_i64(sat, red);   // also orders the sq / sk writes before the reads below
 	if (threadIdx.x == 0) b.sat[r] += (unsigned long long)sat;
+	if (lw.b_k != nullptr || lw.b_v != nullptr) {
+		kv_bad = block_sum_i64(kv_bad, red);
+		if (kv_bad != 0) {
+			set_status(b, r, kBiasReconcileProductOutOfDomain);
+			return;
+		}
+	}
 
 	// RoPE: interleaved pairs (2i, 2i+1), table row = position
 	int8_t* qrot = b.qrot + (size_t)r * H;

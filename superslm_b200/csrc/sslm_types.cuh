@@ -43,6 +43,9 @@ struct LayerDev {
 	const int64_t* k_recip;   // [kv_heads][3] (m_t, e_t, R_t)
 	const int64_t* v_recip;
 	const int64_t* sm_khead;  // [kv_heads][2] (m, e)
+	const int64_t* b_q;       // [hidden]     q/k/v bias codes (BIA1, Q30), each nullptr when absent
+	const int64_t* b_k;       // [kv_hidden]
+	const int64_t* b_v;       // [kv_hidden]
 	Scale c_attn_norm, c_q, c_o, c_ctx, c_attn_res, c_mlp_norm, c_gate, c_up, c_act, c_down, c_mlp_res;
 };
 

@@ -23,13 +23,18 @@ CASES = [
     ("small", "small", 0x53534C4D00000001, 160, 70, 24, None),
     ("small_dense", "small", 0x53534C4D00000002, 96, 40, 10, None),
     ("tiny_lora", "tiny", 0x53534C4D00000003, 64, 18, 10, (11, 12)),
+    # q/k/v biases (BIA1), trailing field = magnitude in bits; with an adapter (delta, then bias);
+    # large enough to saturate the K/V landing
+    ("tiny_bias", "tiny", 0x53534C4D00000004, 64, 20, 12, None, 29),
+    ("tiny_bias_lora", "tiny", 0x53534C4D00000005, 64, 18, 10, (13, 14), 30),
+    ("small_bias_saturating", "small", 0x53534C4D00000006, 96, 40, 10, None, 33),
 ]
 
 
-def run_case(lib, name, shape, seed, cap, npf, ndec, adapters):
+def run_case(lib, name, shape, seed, cap, npf, ndec, adapters, bias_bits=0):
     sh = A.SHAPES[shape]
     lo, hi = (8, 11) if name.endswith("dense") else (8, 20)
-    art = A.build_synthetic_model(shape, seed, cap, lo, hi)
+    art = A.build_synthetic_model(shape, seed, cap, lo, hi, bias_bits)
     prompt = A.stream_uniform(seed ^ 0xABCDEF, "prompt", npf, 0, sh.vocab - 1)
     eng = abi.Engine(lib, art, blocks=1, max_chunk=64)
     s = eng.new_seq()
@@ -47,7 +52,7 @@ def run_case(lib, name, shape, seed, cap, npf, ndec, adapters):
     eng.close()
     return {
         "shape": shape, "seed": seed, "context_cap": cap, "prompt_len": npf, "decode": ndec,
-        "shift_lo": lo, "shift_hi": hi, "adapters": adapters,
+        "shift_lo": lo, "shift_hi": hi, "adapters": adapters, "bias_bits": bias_bits,
         "tokens": toks, "context_length": blob["context_length"],
         "hidden_scale": list(blob["hidden_scale"]), "kv_saturation_count": blob["kv_saturation_count"],
         "kv_sha256": hashlib.sha256(blob["kv"]).hexdigest(),

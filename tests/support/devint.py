@@ -31,6 +31,8 @@ def lib():
         "dev_iexp_scale_constants": (C.c_int, [i64, i64, P64, P64, P64]),
         "dev_softmax_width": (C.c_int, [i64, i64, C.c_uint64, P64]),
         "dev_iexp_element": (C.c_int, [i64] * 5 + [P64]),
+        "dev_bias_reconcile": (C.c_int, [i64] * 3 + [P64]),
+        "dev_bias_accumulate": (C.c_int, [i64] * 2 + [P64]),
     }
     for n, (r, a) in sig.items():
         f = getattr(d, n)

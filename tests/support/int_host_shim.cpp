@@ -47,6 +47,14 @@ int dev_iexp_scale_constants(int64_t m, int64_t e, int64_t* a, int64_t* b, int64
 int dev_softmax_width(int64_t qb, int64_t qc, uint64_t w, int64_t* peak) {
 	return softmax_width_in_domain(qb, qc, w, peak) ? 1 : 0;
 }
+// 1 with *out = the bias term when the exponent gate and the int64 fit both hold, else 0
+int dev_bias_reconcile(int64_t b, int64_t r_a, int64_t e_a, int64_t* out) {
+	int ex = 0;
+	*out = 0;
+	if (!bias_exponent_in_domain(e_a, &ex)) return 0;
+	return bias_reconcile(b, r_a, ex, out) ? 1 : 0;
+}
+int dev_bias_accumulate(int64_t acc, int64_t term, int64_t* out) { return bias_accumulate(acc, term, out) ? 1 : 0; }
 int dev_iexp_element(int64_t q, int64_t ln2, int64_t b, int64_t c, int64_t peak, int64_t* v) {
 	IExpConsts k{ln2, b, c};
 	return iexp_element(q, k, peak, v) ? 1 : 0;

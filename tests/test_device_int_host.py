@@ -91,6 +91,30 @@ def test_folds_and_scale_algebra(port):
         assert (om.value, oe.value) == (c.m, c.e)
 
 
+def test_bias_reconcile(port):
+    d = devint.lib()
+    rnd = random.Random(6)
+    port.osc_bias_reconcile.argtypes = [I64, I64, I64, C.POINTER(I64)]
+    port.osc_bias_reconcile.restype = C.c_int
+    for i in range(60000):
+        b = rnd.choice([ri(rnd, 47), ri(rnd, 30), ri(rnd, 62), 0, 1, -1, (1 << 63) - 1, -(1 << 63)])
+        r_a = rnd.choice([rnd.randrange(1 << 31, (1 << 32) + 1), ri(rnd, 40), ri(rnd, 63), 0])
+        e_a = rnd.choice([rnd.randrange(-60, -30), rnd.randrange(-95, -25), -92, -29, -93, -28, ri(rnd, 63)])
+        v1, v2 = I64(), I64()
+        ok1 = d.dev_bias_reconcile(b, r_a, e_a, C.byref(v1))
+        ok2 = port.osc_bias_reconcile(b, r_a, e_a, C.byref(v2))
+        assert ok1 == ok2, (b, r_a, e_a)
+        if -92 <= e_a <= -29:
+            assert v1.value == v2.value, (b, r_a, e_a)
+    for acc, term in [(1, 2), ((1 << 63) - 1, 1), (-(1 << 63), -1), ((1 << 63) - 1, -(1 << 63)), (-5, 5),
+                      ((1 << 62), (1 << 62)), (-(1 << 62), -(1 << 62)), (-(1 << 62) - 1, -(1 << 62))]:
+        out = I64()
+        fits = -(1 << 63) <= acc + term < (1 << 63)
+        assert bool(d.dev_bias_accumulate(acc, term, C.byref(out))) == fits, (acc, term)
+        if fits:
+            assert out.value == acc + term
+
+
 def test_iexp_constants_and_elements(port):
     d = devint.lib()
     rnd = random.Random(5)

@@ -20,7 +20,8 @@ pytestmark = pytest.mark.gpu
 
 def gpu_record(lib, case, chunk, budget):
     sh = A.SHAPES[case["shape"]]
-    art = A.build_synthetic_model(case["shape"], case["seed"], case["context_cap"], case["shift_lo"], case["shift_hi"])
+    art = A.build_synthetic_model(case["shape"], case["seed"], case["context_cap"], case["shift_lo"], case["shift_hi"],
+                                  case.get("bias_bits", 0))
     prompt = A.stream_uniform(case["seed"] ^ 0xABCDEF, "prompt", case["prompt_len"], 0, sh.vocab - 1)
     eng = abi.Engine(lib, art, blocks=1, max_chunk=64)
     s = eng.new_seq()
@@ -41,7 +42,8 @@ def gpu_record(lib, case, chunk, budget):
             "kv_saturation_count": blob["kv_saturation_count"], "kv_sha256": hashlib.sha256(blob["kv"]).hexdigest()}
 
 
-@pytest.mark.parametrize("name", ["tiny", "small", "small_dense", "tiny_lora"])
+@pytest.mark.parametrize("name", ["tiny", "small", "small_dense", "tiny_lora", "tiny_bias", "tiny_bias_lora",
+                                  "small_bias_saturating"])
 @pytest.mark.parametrize("chunk,budget", [(64, 0), (7, 1), (1, 2), (33, 0)])
 def test_golden_records_at_every_split(gpu_lib, e2e_golden, name, chunk, budget):
     case = e2e_golden[name]
@@ -357,4 +359,17 @@ def test_artifact_rejections(gpu_lib):
     ad = np.frombuffer(A.build_synthetic_adapter(other, 5), dtype=np.uint8)
     h = abi._H()
     assert gpu_lib.sslm_adapter_map(ad.ctypes.data, ad.size, eng.model, C.byref(h)) == abi.ST["SSLM_ADAPTER_MODEL_MISMATCH"]
+    eng.close()
+
+
+def test_option_g_flag_is_ignored_like_the_reference(gpu_lib):
+    sh = A.SHAPES["tiny"]
+    art = A.build_synthetic_model("tiny", 0xF1A6, 48, flags=1)
+    prompt = A.stream_uniform(31, "p", 14, 0, sh.vocab - 1)
+    ptoks, ps = run_port(art, prompt, 8)
+    eng = abi.Engine(gpu_lib, art, blocks=1, max_chunk=16)
+    s = eng.new_seq()
+    s.prefill(prompt, 16)
+    assert s.decode(8, sh.layers) == ptoks
+    assert abi.parse_save_blob(s.save(), sh.hidden)["kv"] == ps.kv.tobytes()
     eng.close()
