@@ -36,6 +36,7 @@ typedef struct sslm_model_s* sslm_model;
 typedef struct sslm_seq_s* sslm_seq;
 typedef struct sslm_adapter_s* sslm_adapter;
 typedef struct sslm_prefix_s* sslm_prefix;
+typedef struct sslm_schema_s* sslm_schema;     /* owned by the model; NULL = no schema */
 typedef struct sslm_kv_pool_s* sslm_kv_pool;
 typedef struct sslm_workspace_s* sslm_workspace;
 
@@ -154,7 +155,7 @@ SSLM_API sslm_status sslm_seq_save(sslm_seq seq, void* buf, size_t* n);
  *      continues bit-exactly on the other. Validation order and statuses follow the
  *      reference: bad magic / lengths -> SSLM_INVALID_ARGUMENT, other model ->
  *      SSLM_RESTORE_MODEL_MISMATCH, other KV precision -> SSLM_RESTORE_KV_MISMATCH, any
- *      schema binding -> SSLM_RESTORE_SCHEMA_MISMATCH (this library maps no schemas), pool of
+ *      schema binding that does not resolve in this model -> SSLM_RESTORE_SCHEMA_MISMATCH, pool of
  *      another model -> SSLM_INVALID_ARGUMENT, no free block -> SSLM_KV_POOL_EXHAUSTED.
  *      A blob that carries damped-greedy history (sslm_decode_step_v2 state) is refused with
  *      SSLM_INVALID_ARGUMENT: that decode mode is not part of this library.
@@ -182,6 +183,27 @@ SSLM_API sslm_status sslm_prefix_prefill(sslm_model model, sslm_prefix prefix, c
 SSLM_API sslm_status sslm_prefix_freeze(sslm_prefix prefix);
 SSLM_API sslm_status sslm_prefix_release(sslm_prefix prefix);
 SSLM_API sslm_status sslm_seq_adopt_prefix(sslm_seq seq, sslm_prefix prefix);
+
+/* ---- constrained decoding: sslm_abi_functions_g5_comparable.inc (sslm_schema_lookup,
+ *      sslm_schema_count, sslm_schema_name, sslm_seq_set_schema, sslm_prefix_set_schema);
+ *      src/sslm_abi.cpp:1236-1264, :1791-1818, :1646-1654, :1486-1512, :2392-2424;
+ *      include/superslm/schema_masks.h (the SCM1 section).
+ *      An artifact may carry decode schemas: DFAs over token ids with one vocab-bit mask page
+ *      per state. A sequence bound to a schema picks each token as the arg-max over the tokens
+ *      its current state allows (the mask is applied inside the vocab-head kernel) and then
+ *      follows the transition; a state that allows nothing yields -2 in out_tokens and the
+ *      sequence stays where it is (later steps report SSLM_ARTIFACT_REJECTED, as the
+ *      reference's do). sslm_prefill with SSLM_SPAN_SCHEMA_CONTENT walks the DFA with the given
+ *      tokens and stops with SSLM_SCHEMA_SPAN_UNREACHABLE at the first one the schema does not
+ *      allow; SSLM_SPAN_PROMPT never moves the walk. The binding, the walk state and the count
+ *      of forced tokens travel in save blobs. Binding is possible only on a fresh (or reset)
+ *      sequence: otherwise SSLM_SCHEMA_BIND_REJECTED. Damped-greedy decoding
+ *      (sslm_decode_step_v2) is not part of this library. */
+SSLM_API sslm_status sslm_schema_lookup(sslm_model model, const char* name, sslm_schema* out);
+SSLM_API size_t sslm_schema_count(sslm_model model);
+SSLM_API sslm_status sslm_schema_name(sslm_model model, int32_t index, char* buf, size_t* n);
+SSLM_API sslm_status sslm_seq_set_schema(sslm_seq seq, sslm_schema schema);
+SSLM_API sslm_status sslm_prefix_set_schema(sslm_prefix prefix, sslm_schema schema);
 
 /* ======================================================================================
  * Entry points below have no counterpart in the reference; they exist for device

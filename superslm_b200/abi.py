@@ -89,6 +89,11 @@ class SslmLib:
         "sslm_prefix_freeze": (C.c_int, [_H]),
         "sslm_prefix_release": (C.c_int, [_H]),
         "sslm_seq_adopt_prefix": (C.c_int, [_H, _H]),
+        "sslm_schema_lookup": (C.c_int, [_H, C.c_char_p, C.POINTER(_H)]),
+        "sslm_schema_count": (C.c_size_t, [_H]),
+        "sslm_schema_name": (C.c_int, [_H, C.c_int32, C.c_char_p, C.POINTER(C.c_size_t)]),
+        "sslm_seq_set_schema": (C.c_int, [_H, _H]),
+        "sslm_prefix_set_schema": (C.c_int, [_H, _H]),
     }
 
     def __init__(self, path: str):

@@ -287,12 +287,77 @@ def _fold_rows(seed, name, n, shift_lo, shift_hi) -> np.ndarray:
     return rows
 
 
+SEC_SCHEMA_MASKS = 30
+
+
+def schema_masks(vocab: int, schemas: list[dict]) -> bytes:
+    """SCM1 section (include/superslm/schema_masks.h): 24-byte header, 56-byte descriptors, name
+    blob, then per schema one vocab-bit mask page per DFA state, the (states + 1) row offsets,
+    the ascending accepting states and the (token, next state) transitions sorted by token
+    inside each state's row. schemas: [{"name": str, "accepting": [state...],
+    "rows": [[(token, next_state), ...] per state]}]. A state's mask page has exactly the bits
+    of its row's tokens (the loader checks that)."""
+    names = b"".join(s["name"].encode() for s in schemas)
+    manifest_end = 24 + 56 * len(schemas) + len(names)
+    page = (vocab + 7) // 8
+    body = bytearray()
+    descs = bytearray()
+    name_off = 0
+
+    def place(chunk: bytes) -> int:
+        off = manifest_end + len(body)
+        body.extend(chunk)
+        body.extend(b"\0" * ((-len(body)) % 8))
+        return off
+
+    for s in schemas:
+        rows = [sorted(r) for r in s["rows"]]
+        n_states = len(rows)
+        pages = np.zeros((n_states, page), dtype=np.uint8)
+        offsets = [0]
+        trans = []
+        for st, row in enumerate(rows):
+            for tok, nxt in row:
+                pages[st, tok >> 3] |= np.uint8(1 << (tok & 7))
+                trans.append((tok, nxt))
+            offsets.append(len(trans))
+        acc = sorted(s["accepting"])
+        nb = s["name"].encode()
+        o_pages = place(pages.tobytes())
+        o_offs = place(np.asarray(offsets, dtype="<u4").tobytes())
+        o_acc = place(np.asarray(acc, dtype="<u4").tobytes())
+        o_tr = place(np.asarray(trans, dtype="<u4").reshape(-1, 2).tobytes() if trans else b"")
+        descs += struct.pack("<IIIIIIQQQQ", name_off, len(nb), n_states, len(acc), len(trans), 0,
+                             o_pages, o_offs, o_acc, o_tr)
+        name_off += len(nb)
+    head = struct.pack("<4sIIIII", b"SCM1", 1, len(schemas), vocab, len(names), 0)
+    return bytes(head + descs + names + body)
+
+
+def synthetic_schemas(seed: int, vocab: int, count: int, states: int = 6, fanout: int = 40) -> list[dict]:
+    """`count` seeded DFAs over the vocabulary: every state but the last allows `fanout` tokens,
+    each leading to a seeded next state; the last state allows nothing (a dead end)."""
+    out = []
+    for k in range(count):
+        rows = []
+        for st in range(states):
+            if st == states - 1:
+                rows.append([])
+                continue
+            toks = np.unique(stream_uniform(seed, "schema%d.s%d.tok" % (k, st), fanout, 0, vocab - 1))
+            nxt = stream_uniform(seed, "schema%d.s%d.next" % (k, st), toks.size, 0, states - 1)
+            rows.append([(int(t), int(n)) for t, n in zip(toks, nxt)])
+        out.append({"name": "schema_%d" % k, "accepting": [states - 2, states - 1], "rows": rows})
+    return out
+
+
 def build_synthetic_model(shape: Shape | str, seed: int, context_cap: int,
                           shift_lo: int = 8, shift_hi: int = 20, bias_bits: int = 0,
-                          flags: int = 0) -> bytes:
+                          flags: int = 0, schemas: int = 0) -> bytes:
     """A loadable base artifact of the given architecture (header flags 0). bias_bits > 0 adds a
     BIA1 section: int64 q/k/v bias codes (Q30 against the projection's input scale, as the
-    converter writes them for Qwen2.5's q/k/v biases), uniform in +-2^bias_bits."""
+    converter writes them for Qwen2.5's q/k/v biases), uniform in +-2^bias_bits. schemas > 0 adds
+    an SCM1 section with that many seeded decode schemas (synthetic_schemas)."""
     sh = SHAPES[shape] if isinstance(shape, str) else shape
     H, L, I, KV = sh.hidden, sh.layers, sh.inter, sh.kv_hidden
     weights: list[tuple[str, np.ndarray]] = []
@@ -363,6 +428,8 @@ def build_synthetic_model(shape: Shape | str, seed: int, context_cap: int,
     ]
     if biases:
         sections.insert(3, (SEC_BIASES, tensor_manifest(b"BIA1", 8, biases)))
+    if schemas > 0:
+        sections.append((SEC_SCHEMA_MASKS, schema_masks(sh.vocab, synthetic_schemas(seed, sh.vocab, schemas))))
     return build_container(sections, flags)
 
 

@@ -34,7 +34,7 @@ struct ConfigView {
 enum : uint32_t {
 	kSecConfig = 0, kSecProvenance = 1, kSecWeights = 2, kSecBiases = 3, kSecRope = 4,
 	kSecWeightScales = 6, kSecComposition = 7, kSecKvScales = 8, kSecKvRecip = 9,
-	kSecSigmoidLut = 12, kSecDeltaFold = 40, kSecUFold = 41,
+	kSecSigmoidLut = 12, kSecSchemaMasks = 30, kSecDeltaFold = 40, kSecUFold = 41,
 };
 
 class ArtifactView {

@@ -253,6 +253,31 @@ extern "C" sslm_status sslm_model_map(const void* data, size_t size, sslm_model*
 	}
 	m->d_layers = (LayerDev*)up.put(m->h_layers.data(), L * sizeof(LayerDev));
 	if (!up.ok) return fail(SSLM_ALLOCATION_FAILED);
+	// decode schemas (src/sslm_abi.cpp:1196-1218): a malformed SCM1 section refuses the artifact
+	if (v.has(kSecSchemaMasks)) {
+		uint64_t ssize = 0;
+		const uint8_t* sdata = v.section_data(kSecSchemaMasks, &ssize);
+		bool sok = false;
+		try {
+			sok = sdata != nullptr && m->schemas.parse(sdata, ssize, c.vocab);
+			if (sok) {
+				m->schema_handles.resize(m->schemas.entries.size());
+				for (size_t i = 0; i < m->schema_handles.size(); ++i) m->schema_handles[i] = sslm_schema_s{m, (uint32_t)i};
+			}
+		} catch (const std::bad_alloc&) {
+			return fail(SSLM_ALLOCATION_FAILED);
+		}
+		if (!sok) return fail(SSLM_ARTIFACT_REJECTED);
+		const size_t pb = m->schemas.page_bytes;
+		if (!cuda_ok(cudaMalloc((void**)&m->d_schema_pages, m->schemas.total_pages() * pb))) return fail(SSLM_ALLOCATION_FAILED);
+		for (const SchemaEntry& e : m->schemas.entries) {
+			if (!cuda_ok(cudaMemcpy(m->d_schema_pages + e.device_page0 * pb, m->schemas.pages(e), (size_t)e.states * pb,
+			                        cudaMemcpyHostToDevice))) {
+				cudaFree(m->d_schema_pages);
+				return fail(SSLM_ALLOCATION_FAILED);
+			}
+		}
+	}
 	m->weight_bytes = m->arena.used;
 	if (!cuda_ok(rows_configure(d)) || !cuda_ok(attn_configure(d))) return fail(SSLM_ARTIFACT_REJECTED);
 	cudaDeviceSynchronize();
@@ -268,6 +293,7 @@ extern "C" sslm_status sslm_model_unmap(sslm_model model) {
 	cudaSetDevice(model->device);
 	if (model->default_ws) destroy_workspace(model->default_ws);
 	cudaFree(model->arena.base);
+	cudaFree(model->d_schema_pages);
 	delete model;
 	return SSLM_OK;
 }
@@ -396,6 +422,8 @@ sslm_workspace_s* create_workspace(sslm_model_s* model, const sslm_config& cfg, 
 	ok = ok && cuda_ok(cudaMalloc((void**)&w->d_rows, rows * sizeof(RowDesc)));
 	ok = ok && cuda_ok(cudaMalloc((void**)&w->d_src, rows * sizeof(RowSource)));
 	ok = ok && cuda_ok(cudaMalloc((void**)&w->d_sink, rows * sizeof(RowSink)));
+	ok = ok && cuda_ok(cudaMallocHost((void**)&w->h_row_mask, rows * sizeof(void*)));
+	ok = ok && cuda_ok(cudaMalloc((void**)&w->d_row_mask, rows * sizeof(void*)));
 	ok = ok && cuda_ok(cudaEventCreate(&w->ev0)) && cuda_ok(cudaEventCreate(&w->ev1));
 	if (ok && rows > 8) {
 		// K slices times tiles never exceeds the SM count, and a tile is at most 256 x 64
@@ -426,6 +454,8 @@ static void destroy_workspace(sslm_workspace_s* w) {
 	cudaFree(w->d_rows);
 	cudaFree(w->d_src);
 	cudaFree(w->d_sink);
+	cudaFree(w->d_row_mask);
+	cudaFreeHost(w->h_row_mask);
 	cudaFreeHost(w->h_rows);
 	cudaFreeHost(w->h_src);
 	cudaFreeHost(w->h_sink);

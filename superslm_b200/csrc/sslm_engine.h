@@ -12,6 +12,7 @@
 #include "../../include/sslm_b200.h"
 #include "sslm_artifact.h"
 #include "sslm_kernels.h"
+#include "sslm_schema.h"
 
 struct DeviceArena {
 	uint8_t* base = nullptr;
@@ -45,6 +46,9 @@ struct sslm_workspace_s {
 	sslm::RowDesc* d_rows = nullptr;
 	sslm::RowSource* d_src = nullptr;
 	sslm::RowSink* d_sink = nullptr;
+	// head rows of constrained sequences: the mask page of the row's DFA state (else nullptr)
+	const uint8_t** h_row_mask = nullptr;   // pinned
+	const uint8_t** d_row_mask = nullptr;
 	// carved row buffers (base pointers for row 0)
 	sslm::RowBatch base{};
 	size_t wide_ld = 0;
@@ -73,6 +77,12 @@ enum ProfClass {
 	kProfLinGateUp, kProfAct, kProfLinDown, kProfRes2, kProfHead, kProfLoraU, kProfOther, kProfClasses
 };
 
+// what sslm_schema_lookup hands out: (model, index into its schema table)
+struct sslm_schema_s {
+	sslm_model_s* model = nullptr;
+	uint32_t index = 0;
+};
+
 struct sslm_model_s {
 	int device = 0;
 	sslm::Dims dims{};
@@ -92,6 +102,11 @@ struct sslm_model_s {
 	std::mutex default_ws_mutex;
 	sslm_workspace_s* default_ws = nullptr;
 	size_t weight_bytes = 0;
+	// decode schemas (SCM1), if the artifact carries any: the parsed table on the host (the DFA
+	// walk runs there, one lookup per produced token) and every state's mask page on the device
+	sslm::SchemaTable schemas;
+	std::vector<sslm_schema_s> schema_handles;
+	uint8_t* d_schema_pages = nullptr;
 };
 
 struct sslm_kv_pool_s {
@@ -131,6 +146,11 @@ struct sslm_seq_s {
 	bool ready_for_logits = false;
 	uint64_t kv_saturation_count = 0;
 	sslm_adapter_s* adapter = nullptr;
+	// constrained decoding: the bound schema (or nullptr), the DFA state the next token is
+	// masked by, and how many tokens were admitted through schema-content prefill spans
+	sslm_schema_s* bound_schema = nullptr;
+	uint32_t dfa_walk_state = sslm::kDfaWalkUnused;
+	int64_t forced_token_count = 0;
 	std::mutex lifecycle_mutex;
 
 	int8_t* hidden(int slot) const { return (int8_t*)(d_state + (size_t)slot * state_stride); }

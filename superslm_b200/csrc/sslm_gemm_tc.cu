@@ -146,6 +146,10 @@ __device__ __forceinline__ void epilogue_chunk(const LinearArgs& a, const uint32
 				v32 = fold(v32, f[0], f[1], f[2]);
 			}
 			if (a.best != nullptr) {   // head: greedy argmax key, lowest index wins ties
+				if (a.row_mask != nullptr) {
+					const uint8_t* page = a.row_mask[row];
+					if (page != nullptr && !((page[n >> 3] >> (n & 7)) & 1u)) v32 = INT32_MIN;
+				}
 				const unsigned long long key =
 				    ((unsigned long long)((uint32_t)v32 ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)n);
 				lbest = key > lbest ? key : lbest;
@@ -419,9 +423,17 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 						if (a.best != nullptr && a.fold == nullptr && a.logits == nullptr && full) {
 							// head: running (value, index) maximum; columns ascend, so a strict
 							// comparison keeps the lowest index among equals
+							uint32_t allowed = 0xFFFFFFFFu;      // the 32 mask bits of this chunk's columns
+							if (a.row_mask != nullptr) {
+								const uint8_t* page = a.row_mask[row];
+								if (page != nullptr) {
+									const uint8_t* pb = page + (nb >> 3);
+									allowed = (uint32_t)pb[0] | ((uint32_t)pb[1] << 8) | ((uint32_t)pb[2] << 16) | ((uint32_t)pb[3] << 24);
+								}
+							}
 #pragma unroll
 							for (int j = 0; j < 32; ++j) {
-								const int v = (int)r[j];
+								const int v = ((allowed >> j) & 1u) ? (int)r[j] : INT32_MIN;
 								const bool gt = v > best_v;
 								best_v = gt ? v : best_v;
 								best_n = gt ? nb + j : best_n;

@@ -105,6 +105,10 @@ k_gemv(LinearArgs a) {
 				}
 			}
 			if (a.best != nullptr) {
+				if (a.row_mask != nullptr) {
+					const uint8_t* page = a.row_mask[row];
+					if (page != nullptr && !((page[n >> 3] >> (n & 7)) & 1u)) v32 = INT32_MIN;
+				}
 				const unsigned long long key =
 				    ((unsigned long long)((uint32_t)v32 ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)n);
 				lbest = key > lbest ? key : lbest;

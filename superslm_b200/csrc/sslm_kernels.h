@@ -87,6 +87,11 @@ struct LinearArgs {
 	// head mode: packed argmax keys instead of a stored row (out may be nullptr)
 	unsigned long long* best;
 	int32_t* logits;      // optional full dump [M, N]
+	// head mode, constrained decoding: per row the vocab-bit mask page of the row's DFA state
+	// (bit n clear = token n not allowed: its logit counts as INT32_MIN, ApplyMaskAndArgmax,
+	// src/forward/forward_sites.cpp:2443-2449), or nullptr for an unconstrained row; the array
+	// itself may be nullptr
+	const uint8_t* const* row_mask;
 	int32_t* status;      // [M] row statuses (a bounded device wait that ran out is reported here), or nullptr
 	// split-K scratch of the tensor-core path (optional): partial accumulators and one
 	// arrival counter per output tile. Counters are zero between launches.
