@@ -14,47 +14,57 @@ namespace sslm {
 constexpr int kLutBytes = 256 * 8 + 256;
 
 // ------------------------------------------------------------ block reductions
+// Every row kernel is a chain of dependent phases, so a reduction's latency is paid in full
+// each time. These cost one barrier: each warp reduces with the warp-reduce instruction and
+// posts its value in one of two alternating banks of shared words, and after the barrier
+// every thread folds the (at most 32) posted values itself. A bank is rewritten only two
+// reductions later, i.e. after a barrier that every reader of its old contents has passed.
+constexpr int kRedBank = 32;                   // one slot per warp
+constexpr int kRedMisc = 2 * kRedBank;         // four more words for single values handed to the block
+constexpr int kRedWords = kRedMisc + 4;
+constexpr int kRedBytes = kRedWords * 8;
+struct Red {
+	unsigned long long* w;
+	int phase;
+};
 __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
-#pragma unroll
-	for (int o = 16; o > 0; o >>= 1) {
-		unsigned long long t = __shfl_xor_sync(0xffffffffu, v, o);
-		v = t > v ? t : v;
-	}
-	return v;
+	const uint32_t hi = (uint32_t)(v >> 32), lo = (uint32_t)v;
+	const uint32_t mh = __reduce_max_sync(0xffffffffu, hi);
+	const uint32_t ml = __reduce_max_sync(0xffffffffu, hi == mh ? lo : 0u);
+	return ((unsigned long long)mh << 32) | ml;
 }
 __device__ __forceinline__ long long warp_sum_i64(long long v) {
 #pragma unroll
 	for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
 	return v;
 }
-// red: shared scratch of at least 33 x 8 bytes. Every thread gets the result.
-__device__ unsigned long long block_max_u64(unsigned long long v, unsigned long long* red) {
+// Every thread gets the result. All threads of the block must call these together.
+__device__ __forceinline__ unsigned long long block_max_u64(unsigned long long v, Red& red) {
 	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+	unsigned long long* bank = red.w + red.phase * kRedBank;
+	red.phase ^= 1;
 	v = warp_max_u64(v);
+	if (lane == 0) bank[warp] = v;
 	__syncthreads();
-	if (lane == 0) red[warp] = v;
-	__syncthreads();
-	if (warp == 0) {
-		unsigned long long t = lane < nw ? red[lane] : 0ull;
-		t = warp_max_u64(t);
-		if (lane == 0) red[32] = t;
+	unsigned long long m = bank[0];
+	for (int w = 1; w < nw; ++w) {
+		const unsigned long long t = bank[w];
+		m = t > m ? t : m;
 	}
-	__syncthreads();
-	return red[32];
+	return m;
 }
-__device__ long long block_sum_i64(long long v, unsigned long long* red) {
+// small: every thread's addend and the warp totals fit 32 bits (a cheaper warp step)
+__device__ __forceinline__ long long block_sum_i64(long long v, Red& red, bool small = false) {
 	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-	v = warp_sum_i64(v);
+	unsigned long long* bank = red.w + red.phase * kRedBank;
+	red.phase ^= 1;
+	if (small) v = (long long)__reduce_add_sync(0xffffffffu, (uint32_t)v);
+	else v = warp_sum_i64(v);
+	if (lane == 0) bank[warp] = (unsigned long long)v;
 	__syncthreads();
-	if (lane == 0) red[warp] = (unsigned long long)v;
-	__syncthreads();
-	if (warp == 0) {
-		long long t = lane < nw ? (long long)red[lane] : 0ll;
-		t = warp_sum_i64(t);
-		if (lane == 0) red[32] = (unsigned long long)t;
-	}
-	__syncthreads();
-	return (long long)red[32];
+	long long s = (long long)bank[0];
+	for (int w = 1; w < nw; ++w) s += (long long)bank[w];
+	return s;
 }
 
 __device__ __forceinline__ unsigned long long abs_u64(int64_t v) {
@@ -64,15 +74,23 @@ __device__ __forceinline__ int64_t load_wide(const RowBatch& b, int row, int col
 	const size_t i = (size_t)row * b.wide_ld + col;
 	return b.wide64 ? ((const int64_t*)b.wide)[i] : (int64_t)((const int32_t*)b.wide)[i];
 }
-// Cooperative 16-byte copy, global -> shared (both 16-byte aligned, bytes a multiple of 16).
-// The kernels below issue all of a row's input copies back to back at their start, so the
-// row pays one memory round trip instead of one per dependent phase.
+// Cooperative asynchronous 16-byte copies, global -> shared (both 16-byte aligned, bytes a
+// multiple of 16), through L2. The kernels below issue all of a row's input copies back to
+// back and wait once (stage_wait + a barrier), so the row pays one memory round trip instead
+// of one per dependent phase, and no registers are held while the copies are in flight.
+//
+// Order against the previous kernel: inputs that were written at least two launches back
+// (the stream row and scales of earlier sites, weights, tables) are fetched BEFORE pdl_wait(),
+// while the projection that feeds this kernel is still running; what that projection writes
+// (its output row, the reduced row maximum) and the row's status word are read only after
+// pdl_wait(), and past the L1 (cp.async.cg / __ldcg), which may hold lines fetched earlier.
 __device__ __forceinline__ void stage16(void* dst, const void* src, int bytes) {
-	const int4* s = (const int4*)src;
-	int4* d = (int4*)dst;
-#pragma unroll 4
-	for (int i = threadIdx.x; i < (bytes >> 4); i += blockDim.x) d[i] = s[i];
+	const char* s = (const char*)src;
+	const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+	for (int i = threadIdx.x * 16; i < bytes; i += blockDim.x * 16)
+		asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + i), "l"(s + i) : "memory");
 }
+__device__ __forceinline__ void stage_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // the row of folded int32 accumulators can be staged with 16-byte copies
 __device__ __forceinline__ bool wide_stageable(const RowBatch& b, int cols) {
 	return !b.wide64 && (b.wide_ld & 3) == 0 && (cols & 3) == 0;
@@ -80,63 +98,89 @@ __device__ __forceinline__ bool wide_stageable(const RowBatch& b, int cols) {
 __device__ __forceinline__ const int32_t* wide_row32(const RowBatch& b, int row) {
 	return (const int32_t*)b.wide + (size_t)row * b.wide_ld;
 }
-// read a GEMM-reduced row maximum and leave the slot zero for its next producer
-__device__ __forceinline__ unsigned long long take_rowmax(const RowBatch& b, int row, int slot,
-                                                          unsigned long long* red) {
-	__syncthreads();
+// After pdl_wait(): thread 0 fetches the GEMM-reduced row maxima of slots [slot, slot + count)
+// (leaving them zero for their next producer) and the row's status word into the misc words;
+// they are readable after the caller's next barrier, which also completes the staged copies.
+__device__ __forceinline__ void fetch_row_words(const RowBatch& b, int row, int slot, int count, Red& red) {
 	if (threadIdx.x == 0) {
-		red[33] = b.rowmax[row * 4 + slot];
-		b.rowmax[row * 4 + slot] = 0ull;
+		for (int i = 0; i < count; ++i) {
+			red.w[kRedMisc + i] = __ldcg(&b.rowmax[row * 4 + slot + i]);
+			b.rowmax[row * 4 + slot + i] = 0ull;
+		}
+		red.w[kRedMisc + 3] = (unsigned long long)(uint32_t)__ldcg(&b.status[row]);
 	}
-	__syncthreads();
-	return red[33];
 }
+__device__ __forceinline__ bool row_refused(const Red& red) { return red.w[kRedMisc + 3] != 0ull; }
 
 // Funnel over a row staged in shared memory (RequantChainChecked,
 // src/forward/checked_chain_funnel.cpp:257-364). Codes go to out_g (global) and, when
 // non-null, out_s (shared). Every thread returns the same status; on failure nothing
 // is written.
+//
+// block_code is the part after the row maximum is known to every thread (the caller's
+// reduction barrier must also have made w[] visible); block_funnel takes the maximum itself.
+template <typename WT>
+__device__ int32_t block_code(const WT* w, int n, unsigned long long mx, const Scale* incoming, int n_incoming,
+                              Scale site, int8_t* out_g, int8_t* out_s, Scale* out_scale) {
+	const FunnelParams fp = funnel_params(mx, incoming, n_incoming, site);
+	if (fp.status != kOk) return fp.status;
+	if ((n & 3) == 0) {
+		// four codes per thread and pass: word stores to global and shared memory
+		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+			uint32_t pk = 0;
+#pragma unroll
+			for (int j = 0; j < 4; ++j) pk |= (uint32_t)(uint8_t)requant_code((int64_t)w[4 * i + j], fp.r, fp.s) << (8 * j);
+			if (out_g) ((uint32_t*)out_g)[i] = pk;
+			if (out_s) ((uint32_t*)out_s)[i] = pk;
+		}
+	} else {
+		for (int i = threadIdx.x; i < n; i += blockDim.x) {
+			const int8_t c = requant_code((int64_t)w[i], fp.r, fp.s);
+			if (out_g) out_g[i] = c;
+			if (out_s) out_s[i] = c;
+		}
+	}
+	if (threadIdx.x == 0 && out_scale) *out_scale = fp.out;
+	return kOk;
+}
 template <typename WT>
 __device__ int32_t block_funnel(const WT* w, int n, const Scale* incoming, int n_incoming, Scale site,
-                                int8_t* out_g, int8_t* out_s, Scale* out_scale,
-                                unsigned long long* red) {
+                                int8_t* out_g, int8_t* out_s, Scale* out_scale, Red& red) {
 	unsigned long long mx = 0;
 	for (int i = threadIdx.x; i < n; i += blockDim.x) {
 		unsigned long long a = abs_u64((int64_t)w[i]);
 		mx = a > mx ? a : mx;
 	}
 	mx = block_max_u64(mx, red);
-	const FunnelParams fp = funnel_params(mx, incoming, n_incoming, site);
-	if (fp.status != kOk) return fp.status;
-	for (int i = threadIdx.x; i < n; i += blockDim.x) {
-		const int8_t c = requant_code((int64_t)w[i], fp.r, fp.s);
-		if (out_g) out_g[i] = c;
-		if (out_s) out_s[i] = c;
-	}
-	if (threadIdx.x == 0 && out_scale) *out_scale = fp.out;
-	return kOk;
+	return block_code<WT>(w, n, mx, incoming, n_incoming, site, out_g, out_s, out_scale);
 }
 
 // RmsNormSite (src/forward/forward_sites.cpp:410-459) on codes h[n] (global or shared):
 // root = max(isqrt(floor((sum h^2) << 32 / n)), 1); wide_i = floor((h_i << 32) / root) * g_i;
 // funnel with no incoming scale. wide: shared int64[n].
 __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Scale site, int64_t* wide,
-                                 int8_t* out_g, Scale* out_scale, int64_t* lut, unsigned long long* red) {
+                                 int8_t* out_g, Scale* out_scale, int64_t* lut, Red& red) {
 	long long ss = 0;
 	for (int i = threadIdx.x; i < n; i += blockDim.x) {
 		const int v = h[i];
 		ss += v * v;
 	}
-	ss = block_sum_i64(ss, red);
+	ss = block_sum_i64(ss, red, n <= (1 << 20));   // 127^2 * 2^20 / warps fits 32 bits per warp
 	int64_t root = isqrt64(floor_div((int64_t)ss << 32, (int64_t)n));
 	if (root < 1) root = 1;
 	// floor((h << 32) / root) depends only on the code: one division per code value, not per element
 	const double inv_root = 1.0 / (double)root;
 	for (int t = threadIdx.x; t < 255; t += blockDim.x) lut[t] = floor_div_h32(t - 127, root, inv_root);
 	__syncthreads();
-	for (int i = threadIdx.x; i < n; i += blockDim.x) wide[i] = lut[(int)h[i] + 127] * (int64_t)gain[i];
-	__syncthreads();
-	return block_funnel<int64_t>(wide, n, nullptr, 0, site, out_g, nullptr, out_scale, red);
+	unsigned long long mx = 0;
+	for (int i = threadIdx.x; i < n; i += blockDim.x) {
+		const int64_t v = lut[(int)h[i] + 127] * (int64_t)gain[i];
+		wide[i] = v;
+		const unsigned long long a = abs_u64(v);
+		mx = a > mx ? a : mx;
+	}
+	mx = block_max_u64(mx, red);   // its barrier also publishes wide[]
+	return block_code<int64_t>(wide, n, mx, nullptr, 0, site, out_g, nullptr, out_scale);
 }
 
 __device__ __forceinline__ void set_status(const RowBatch& b, int row, int32_t st) {
@@ -153,9 +197,9 @@ k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource*
 	pdl_wait();
 	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
-	unsigned long long* red = (unsigned long long*)smem;
-	int64_t* lut = (int64_t*)(smem + 34 * 8);
-	int64_t* wide = (int64_t*)(smem + 34 * 8 + kLutBytes);
+	Red red{(unsigned long long*)smem, 0};
+	int64_t* lut = (int64_t*)(smem + kRedBytes);
+	int64_t* wide = (int64_t*)(smem + kRedBytes + kLutBytes);
 	const int r = blockIdx.x, n = d.hidden;
 	int8_t* x = b.x + (size_t)r * n;
 	if (threadIdx.x == 0) {
@@ -187,9 +231,9 @@ k_rmsnorm(RowBatch b, Dims d, const int8_t* gain, Scale site) {
 	pdl_wait();
 	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
-	unsigned long long* red = (unsigned long long*)smem;
-	int64_t* lut = (int64_t*)(smem + 34 * 8);
-	int64_t* wide = (int64_t*)(smem + 34 * 8 + kLutBytes);
+	Red red{(unsigned long long*)smem, 0};
+	int64_t* lut = (int64_t*)(smem + kRedBytes);
+	int64_t* wide = (int64_t*)(smem + kRedBytes + kLutBytes);
 	const int r = blockIdx.x, n = d.hidden;
 	if (b.status[r] != 0) return;
 	const int32_t st = block_rmsnorm(b.x + (size_t)r * n, gain, n, site, wide, b.nrm + (size_t)r * n,
@@ -205,19 +249,18 @@ k_rmsnorm(RowBatch b, Dims d, const int8_t* gain, Scale site) {
 __global__ void __launch_bounds__(kRowThreads)
 k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool,
            const int32_t* rope_cos, const int32_t* rope_sin) {
-	pdl_wait();
-	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
-	unsigned long long* red = (unsigned long long*)smem;      // 34 words
-	int32_t* st_kv = (int32_t*)(smem + 34 * 8);                // 16 ints
-	int8_t* sq = (int8_t*)(smem + 34 * 8 + 64);                // hidden
+	Red red{(unsigned long long*)smem, 0};
+	int32_t* st_kv = (int32_t*)(smem + kRedBytes);             // 16 ints
+	int8_t* sq = (int8_t*)(smem + kRedBytes + 64);             // hidden
 	int8_t* sk = sq + d.hidden;                                // kv_hidden
 	const int r = blockIdx.x, H = d.hidden, hd = d.head_dim, half = hd / 2;
-	int32_t* sw = (int32_t*)(smem + 34 * 8 + 64 + ((H + d.kv_hidden + 15) & ~15));   // staged q|k|v row
-	int32_t* s_cos = sw + d.qkv_rows;                                                 // staged RoPE row
+	int32_t* sw = (int32_t*)(smem + kRedBytes + 64 + ((H + d.kv_hidden + 15) & ~15));   // staged q|k|v row
+	int32_t* s_cos = sw + d.qkv_rows;                                                    // staged RoPE row
 	int32_t* s_sin = s_cos + half;
 	const bool vec = wide_stageable(b, d.qkv_rows) && (half & 3) == 0;
-	if (vec) stage16(sw, wide_row32(b, r), d.qkv_rows * 4);
+	// ahead of the projection: the normed row's scale (written by the previous residual site),
+	// the position, its RoPE row and page, the site constant
 	const LayerDev& lw = *layer;
 	const Scale ns = b.ns[r];
 	const Scale c_q = lw.c_q;
@@ -228,8 +271,16 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	}
 	const int32_t* cos_row = vec ? s_cos : rope_cos + (size_t)pos * half;   // table row = position
 	const int32_t* sin_row = vec ? s_sin : rope_sin + (size_t)pos * half;
-	const unsigned long long mx = take_rowmax(b, r, 0, red);
-	if (b.status[r] != 0) return;
+	const int page = b.rows[r].pages[pos / kPageTokens];
+	const int slot = pos % kPageTokens;
+	pdl_wait();
+	pdl_release();
+	if (vec) stage16(sw, wide_row32(b, r), d.qkv_rows * 4);
+	fetch_row_words(b, r, 0, 1, red);
+	stage_wait();
+	__syncthreads();
+	const unsigned long long mx = red.w[kRedMisc];
+	if (row_refused(red)) return;
 
 	auto wv = [&](int i) -> int64_t { return vec ? (int64_t)sw[i] : load_wide(b, r, i); };
 	// q/k/v bias (BIA1): term_i = round(B_i * Recip(S[x].m) / 2^(92 + S[x].e)) joins the folded
@@ -259,14 +310,14 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		}
 		// the row maximum the GEMM reduced does not include the bias: take it here
 		unsigned long long lmx = 0;
-		long long bad = 0;
+		int bad = 0;
 		for (int i = threadIdx.x; i < H; i += blockDim.x) {
 			bool ok;
 			const unsigned long long a = abs_u64(biased(wv(i), lw.b_q, i, &ok));
 			if (!ok) bad = 1;
 			lmx = a > lmx ? a : lmx;
 		}
-		bad = block_sum_i64(bad, red);
+		bad = __syncthreads_or(bad);
 		if (bad != 0) {
 			set_status(b, r, kBiasReconcileProductOutOfDomain);
 			return;
@@ -278,13 +329,47 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		set_status(b, r, fp.status);
 		return;
 	}
-	if (lw.b_q != nullptr) {
-		for (int i = threadIdx.x; i < H; i += blockDim.x) {
-			bool ok;
-			sq[i] = requant_code(biased(wv(i), lw.b_q, i, &ok), fp.r, fp.s);
+	// softmax constants per kv head: sm = Combine(S[q], softmax_khead) -> C30 constants -> width gate.
+	// A serial scalar derivation that needs only the q scale: the last warp's first lanes run it
+	// now, while the other warps code the q row, instead of after everything else.
+	const int kv_lane = (int)threadIdx.x - ((int)blockDim.x - 32);
+	if (kv_lane >= 0 && kv_lane < d.kv_heads) {
+		const int h = kv_lane;
+		int32_t st = kOk;
+		const Scale kh = Scale{lw.sm_khead[2 * h], lw.sm_khead[2 * h + 1]};
+		SoftmaxConsts sc;
+		sc.c = IExpConsts{0, 0, 0};
+		sc.peak = 0;
+		if (!fits_i32(fp.out.m) || !fits_i32(kh.m)) {
+			st = kCarriedScaleMantissaOutOfDomain;
+		} else {
+			const Scale sm = combine(fp.out, kh);
+			if (!fits_i32(sm.m)) {
+				st = kCarriedScaleMantissaOutOfDomain;
+			} else if (iexp_scale_constants(sm.m, sm.e, &sc.c) != 0) {
+				st = kIExpScaleDerivationOutOfDomain;
+			} else if (!softmax_width_in_domain(sc.c.q_b, sc.c.q_c, (uint64_t)pos + 1, &sc.peak)) {
+				st = kSoftmaxRowWidthOutOfDomain;
+			} else if (sc.c.q_ln2 < 1 || sc.c.q_ln2 > sc.c.q_b) {
+				// q_ln2 == 0: every element's construction is refused by the reference
+				// (IExpConstruct's q_ln2 >= 1 check) -> SoftmaxKernelRefused
+				st = kSoftmaxKernelRefused;
+			}
 		}
-	} else {
-		for (int i = threadIdx.x; i < H; i += blockDim.x) sq[i] = requant_code(wv(i), fp.r, fp.s);
+		st_kv[h] = st;
+		b.smc[(size_t)r * d.kv_heads + h] = sc;
+	}
+
+	const int q_threads = blockDim.x > 32 ? (int)blockDim.x - 32 : (int)blockDim.x;   // the other warps
+	if ((int)threadIdx.x < q_threads) {
+		if (lw.b_q != nullptr) {
+			for (int i = threadIdx.x; i < H; i += q_threads) {
+				bool ok;
+				sq[i] = requant_code(biased(wv(i), lw.b_q, i, &ok), fp.r, fp.s);
+			}
+		} else {
+			for (int i = threadIdx.x; i < H; i += q_threads) sq[i] = requant_code(wv(i), fp.r, fp.s);
+		}
 	}
 	if ((lw.b_k != nullptr || lw.b_v != nullptr) && !bias_gate) {
 		set_status(b, r, kRoundingDivideExponentOutOfDomain);
@@ -292,9 +377,8 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	}
 
 	// K/V landing
-	const int page = b.rows[r].pages[pos / kPageTokens];
-	const int slot = pos % kPageTokens;
-	long long sat = 0, kv_bad = 0;
+	long long sat = 0;
+	int kv_bad = 0;
 	for (int i = threadIdx.x; i < d.kv_hidden; i += blockDim.x) {
 		const int h = i / hd, dd = i - h * hd;
 		bool s1, s2;
@@ -321,10 +405,10 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		               ((int64_t)page * hd + dd) * kPageTokens + slot;
 		*vdst = (int8_t)clamp127(vraw);
 	}
-	sat = block_sum_i64(sat, red);   // also orders the sq / sk writes before the reads below
+	sat = block_sum_i64(sat, red, d.kv_hidden <= (1 << 20));   // also orders the sq / sk writes before the reads below
 	if (threadIdx.x == 0) b.sat[r] += (unsigned long long)sat;
 	if (lw.b_k != nullptr || lw.b_v != nullptr) {
-		kv_bad = block_sum_i64(kv_bad, red);
+		kv_bad = __syncthreads_or(kv_bad);
 		if (kv_bad != 0) {
 			set_status(b, r, kBiasReconcileProductOutOfDomain);
 			return;
@@ -352,33 +436,6 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		kdst[1] = oy;
 	}
 
-	// softmax constants per kv head: sm = Combine(S[q], softmax_khead) -> C30 constants -> width gate
-	if (threadIdx.x < d.kv_heads) {
-		const int h = threadIdx.x;
-		int32_t st = kOk;
-		const Scale kh = Scale{lw.sm_khead[2 * h], lw.sm_khead[2 * h + 1]};
-		SoftmaxConsts sc;
-		sc.c = IExpConsts{0, 0, 0};
-		sc.peak = 0;
-		if (!fits_i32(fp.out.m) || !fits_i32(kh.m)) {
-			st = kCarriedScaleMantissaOutOfDomain;
-		} else {
-			const Scale sm = combine(fp.out, kh);
-			if (!fits_i32(sm.m)) {
-				st = kCarriedScaleMantissaOutOfDomain;
-			} else if (iexp_scale_constants(sm.m, sm.e, &sc.c) != 0) {
-				st = kIExpScaleDerivationOutOfDomain;
-			} else if (!softmax_width_in_domain(sc.c.q_b, sc.c.q_c, (uint64_t)pos + 1, &sc.peak)) {
-				st = kSoftmaxRowWidthOutOfDomain;
-			} else if (sc.c.q_ln2 < 1 || sc.c.q_ln2 > sc.c.q_b) {
-				// q_ln2 == 0: every element's construction is refused by the reference
-				// (IExpConstruct's q_ln2 >= 1 check) -> SoftmaxKernelRefused
-				st = kSoftmaxKernelRefused;
-			}
-		}
-		st_kv[h] = st;
-		b.smc[(size_t)r * d.kv_heads + h] = sc;
-	}
 	__syncthreads();
 	if (threadIdx.x == 0) {
 		if (b.xs != nullptr) { /* q scale is consumed only through smc */ }
@@ -394,17 +451,20 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 // Attention-context funnel (forward_sites.cpp:1898-1903): empty incoming, attn_ctx constant.
 __global__ void __launch_bounds__(kRowThreads)
 k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
-	pdl_wait();
-	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
-	unsigned long long* red = (unsigned long long*)smem;
-	int32_t* sw = (int32_t*)(smem + 34 * 8);
+	Red red{(unsigned long long*)smem, 0};
+	int32_t* sw = (int32_t*)(smem + kRedBytes);
 	const int r = blockIdx.x, n = d.hidden;
 	const bool vec = (n & 3) == 0;
-	if (vec) stage16(sw, b.ctxw + (size_t)r * n, n * 4);
 	const Scale c_ctx = layer->c_ctx;
-	const unsigned long long mx = take_rowmax(b, r, 3, red);
-	if (b.status[r] != 0) return;
+	pdl_wait();
+	pdl_release();
+	if (vec) stage16(sw, b.ctxw + (size_t)r * n, n * 4);
+	fetch_row_words(b, r, 3, 1, red);
+	stage_wait();
+	__syncthreads();
+	const unsigned long long mx = red.w[kRedMisc];
+	if (row_refused(red)) return;
 	const FunnelParams fp = funnel_params(mx, nullptr, 0, c_ctx);
 	if (fp.status != kOk) {
 		set_status(b, r, fp.status);
@@ -431,7 +491,7 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 // shared memory: wide_i = LandingRescale(branch_i, S[branch], Recip(S[stream].m), ...) + stream_i.
 __device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t* stream, Scale ss, int n,
                                   Scale site, int64_t* wide, int8_t* out_g, int8_t* out_s,
-                                  Scale* out_scale, int64_t* lut, unsigned long long* red) {
+                                  Scale* out_scale, int64_t* lut, Red& red) {
 	if (!fits_i32(ss.m)) return kCarriedScaleMantissaOutOfDomain;
 	const int64_t r_h = dyn_recip(ss.m);
 	// the rescaled branch value depends only on the branch code: one LandingRescale per code value.
@@ -443,30 +503,33 @@ __device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t
 		lex[t] = ex ? 1 : 0;
 	}
 	__syncthreads();
-	long long bad = 0;
+	// one reduction carries both the row maximum and "some code's rescaled magnitude left
+	// int64": no in-range sum has magnitude 2^64 - 1, which stands for the latter
+	unsigned long long mx = 0;
 	for (int i = threadIdx.x; i < n; i += blockDim.x) {
 		const int c = (int)branch_s[i] + 127;
 		if (lex[c]) {
-			bad = 1;
+			mx = ~0ull;
 			wide[i] = 0;
 		} else {
-			wide[i] = lut[c] + (int64_t)stream[i];
+			const int64_t v = lut[c] + (int64_t)stream[i];
+			wide[i] = v;
+			const unsigned long long a = abs_u64(v);
+			mx = a > mx ? a : mx;
 		}
 	}
-	bad = block_sum_i64(bad, red);
-	if (bad != 0) return kResidualMagnitudeOutOfDomain;
-	return block_funnel<int64_t>(wide, n, &ss, 1, site, out_g, out_s, out_scale, red);
+	mx = block_max_u64(mx, red);   // its barrier also publishes wide[]
+	if (mx == ~0ull) return kResidualMagnitudeOutOfDomain;
+	return block_code<int64_t>(wide, n, mx, &ss, 1, site, out_g, out_s, out_scale);
 }
 
 // o-projection funnel -> attention residual -> MLP RMSNorm (forward_sites.cpp:1906-1937)
 __global__ void __launch_bounds__(kRowThreads)
 k_res1(RowBatch b, Dims d, const LayerDev* layer) {
-	pdl_wait();
-	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
-	unsigned long long* red = (unsigned long long*)smem;
-	int64_t* lut = (int64_t*)(smem + 34 * 8);
-	int64_t* wide = (int64_t*)(smem + 34 * 8 + kLutBytes);
+	Red red{(unsigned long long*)smem, 0};
+	int64_t* lut = (int64_t*)(smem + kRedBytes);
+	int64_t* wide = (int64_t*)(smem + kRedBytes + kLutBytes);
 	int8_t* so = (int8_t*)(wide + d.hidden);
 	int8_t* sa = so + d.hidden;
 	int8_t* sx = sa + d.hidden;                  // staged stream row
@@ -475,15 +538,22 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	const int r = blockIdx.x, n = d.hidden;
 	const LayerDev& lw = *layer;
 	const bool vec = wide_stageable(b, n) && (n & 15) == 0;
+	// ahead of the o-projection: the stream row and its scale, the context scale (written by the
+	// context funnel, which ran before that projection), the gain and the site constants
 	if (vec) {
-		stage16(wraw, wide_row32(b, r), n * 4);
 		stage16(sx, b.x + (size_t)r * n, n);
 		stage16(sg, lw.g_mlp, n);
 	}
 	const Scale cs = b.cs[r], xs = b.xs[r];
 	const Scale c_o = lw.c_o, c_res = lw.c_attn_res, c_norm = lw.c_mlp_norm;
-	const unsigned long long mx = take_rowmax(b, r, 0, red);
-	if (b.status[r] != 0) return;
+	pdl_wait();
+	pdl_release();
+	if (vec) stage16(wraw, wide_row32(b, r), n * 4);
+	fetch_row_words(b, r, 0, 1, red);
+	stage_wait();
+	__syncthreads();
+	const unsigned long long mx = red.w[kRedMisc];
+	if (row_refused(red)) return;
 	const FunnelParams fp = funnel_params(mx, &cs, 1, c_o);
 	int32_t st = fp.status;
 	if (st == kOk) {
@@ -507,12 +577,10 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 // (forward_sites.cpp:1968-1987, :1694-1698)
 __global__ void __launch_bounds__(kRowThreads)
 k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
-	pdl_wait();
-	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
-	unsigned long long* red = (unsigned long long*)smem;
-	int64_t* lut = (int64_t*)(smem + 34 * 8);
-	int64_t* wide = (int64_t*)(smem + 34 * 8 + kLutBytes);
+	Red red{(unsigned long long*)smem, 0};
+	int64_t* lut = (int64_t*)(smem + kRedBytes);
+	int64_t* wide = (int64_t*)(smem + kRedBytes + kLutBytes);
 	int8_t* sd = (int8_t*)(wide + d.hidden);
 	int8_t* sx = sd + d.hidden;
 	int8_t* sa = sx + d.hidden;                  // staged stream row (after the attention residual)
@@ -521,8 +589,9 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	const int r = blockIdx.x, n = d.hidden;
 	const LayerDev& lw = *layer;
 	const bool vec = wide_stageable(b, n) && (n & 15) == 0;
+	// ahead of the down-projection: the stream row after the attention residual and its scale,
+	// the activation scale (written before that projection ran), the next gain, the constants
 	if (vec) {
-		stage16(wraw, wide_row32(b, r), n * 4);
 		stage16(sa, b.a + (size_t)r * n, n);
 		if (next_layer != nullptr) stage16(sg, next_layer->g_attn, n);
 	}
@@ -530,8 +599,14 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	const Scale c_down = lw.c_down, c_res = lw.c_mlp_res;
 	Scale c_norm = Scale{0, 0};
 	if (next_layer != nullptr) c_norm = next_layer->c_attn_norm;
-	const unsigned long long mx = take_rowmax(b, r, 0, red);
-	if (b.status[r] != 0) return;
+	pdl_wait();
+	pdl_release();
+	if (vec) stage16(wraw, wide_row32(b, r), n * 4);
+	fetch_row_words(b, r, 0, 1, red);
+	stage_wait();
+	__syncthreads();
+	const unsigned long long mx = red.w[kRedMisc];
+	if (row_refused(red)) return;
 	const FunnelParams fp = funnel_params(mx, &as, 1, c_down);
 	int32_t st = fp.status;
 	if (st == kOk) {
@@ -555,29 +630,39 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 // gate / up funnels -> SwiGLU activation site (MlpActSite, forward_sites.cpp:796-864)
 __global__ void __launch_bounds__(kRowThreads, 1024 / kRowThreads)
 k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
-	pdl_wait();
-	pdl_release();
 	extern __shared__ __align__(16) unsigned char smem[];
-	unsigned long long* red = (unsigned long long*)smem;
-	int32_t* gsil = (int32_t*)(smem + 36 * 8);         // g * sigmoid(g) for the 255 gate codes, this row's scale
-	int32_t* wide = gsil + 256;                         // inter
+	Red red{(unsigned long long*)smem, 0};
+	int32_t* gsil = (int32_t*)(smem + kRedBytes);      // g * sigmoid(g) for the 255 gate codes, this row's scale
+	int32_t* wide = gsil + 256;                         // inter: the gate row, then the products in place
+	int32_t* urow = wide + d.inter;                     // inter: the up row
 	const int r = blockIdx.x, n = d.inter;
-	if (threadIdx.x == 0) {
-		red[33] = b.rowmax[r * 4 + 1];
-		red[34] = b.rowmax[r * 4 + 2];
-		b.rowmax[r * 4 + 1] = 0ull;
-		b.rowmax[r * 4 + 2] = 0ull;
-	}
-	__syncthreads();
-	const unsigned long long mxg = red[33], mxu = red[34];
-	if (b.status[r] != 0) return;
+	const bool vec = !b.wide64 && (n & 3) == 0 && (b.wide_ld & 3) == 0;
+	// ahead of the gate/up projection: the normed row's scale (written by the residual site
+	// before that projection ran) and the site constants
 	const LayerDev& lw = *layer;
 	const Scale ns = b.ns[r];
-	const FunnelParams fg = funnel_params(mxg, &ns, 1, lw.c_gate);
-	const FunnelParams fu = funnel_params(mxu, &ns, 1, lw.c_up);
+	const Scale c_gate = lw.c_gate, c_up = lw.c_up, c_act = lw.c_act;
+	pdl_wait();
+	pdl_release();
+	if (vec) {
+		// the whole gate | up row lands in shared memory while the scalar derivations below run
+		const int32_t* gp = (const int32_t*)b.wide + (size_t)r * b.wide_ld;
+		stage16(wide, gp, n * 4);
+		stage16(urow, gp + n, n * 4);
+	}
+	fetch_row_words(b, r, 1, 2, red);
+	__syncthreads();
+	const unsigned long long mxg = red.w[kRedMisc], mxu = red.w[kRedMisc + 1];
+	if (row_refused(red)) {
+		stage_wait();
+		return;
+	}
+	const FunnelParams fg = funnel_params(mxg, &ns, 1, c_gate);
+	const FunnelParams fu = funnel_params(mxu, &ns, 1, c_up);
 	int32_t st = fg.status != kOk ? fg.status : fu.status;
 	if (st == kOk && !silu_scale_in_domain(fg.out)) st = kSiluScaleOutOfDomain;
 	if (st != kOk) {
+		stage_wait();
 		set_status(b, r, st);
 		return;
 	}
@@ -588,14 +673,14 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 		const int g = t - 127;
 		gsil[t] = g * silu_sigmoid_q15(silu_table, g, fg.out.m, ge);
 	}
+	stage_wait();
 	__syncthreads();
-	// products g * sigmoid(g) * u, |.| <= 127 * 2^15 * 127 < 2^29, staged in shared memory
+	// products g * sigmoid(g) * u, |.| <= 127 * 2^15 * 127 < 2^29, left in shared memory
 	// with their running maximum so that the funnel below needs no second pass for it
 	uint32_t lmax = 0;
-	const bool vec = !b.wide64 && (n & 3) == 0 && (b.wide_ld & 3) == 0;
 	if (vec) {
-		const int4* gp = (const int4*)((const int32_t*)b.wide + (size_t)r * b.wide_ld);
-		const int4* up = gp + (n >> 2);
+		const int4* gp = (const int4*)wide;
+		const int4* up = (const int4*)urow;
 #pragma unroll 2
 		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
 			const int4 gv = gp[i], uv = up[i];
@@ -623,7 +708,7 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	}
 	const unsigned long long mx = block_max_u64((unsigned long long)lmax, red);
 	const Scale inc[2] = {fg.out, fu.out};
-	const FunnelParams fp = funnel_params(mx, inc, 2, lw.c_act);
+	const FunnelParams fp = funnel_params(mx, inc, 2, c_act);
 	if (fp.status != kOk) {
 		set_status(b, r, fp.status);
 		return;
@@ -658,9 +743,9 @@ k_scatter(RowBatch b, Dims d, const RowSink* sink) {
 }
 
 // ------------------------------------------------------------------ launchers
-static size_t smem_wide(const Dims& d) { return 34 * 8 + kLutBytes + (size_t)d.hidden * 8; }
+static size_t smem_wide(const Dims& d) { return kRedBytes + kLutBytes + (size_t)d.hidden * 8; }
 // reductions, the int64 staging row, four code rows and the staged int32 projection row
-static size_t res_smem_bytes(const Dims& d) { return 34 * 8 + kLutBytes + (size_t)d.hidden * 16; }
+static size_t res_smem_bytes(const Dims& d) { return kRedBytes + kLutBytes + (size_t)d.hidden * 16; }
 
 void launch_begin(const RowBatch& b, const Dims& d, const int8_t* embed, Scale c_embed,
                   const RowSource* src, const LayerDev* layer, cudaStream_t st) {
@@ -671,12 +756,12 @@ void launch_rmsnorm(const RowBatch& b, const Dims& d, const int8_t* gain, Scale 
 }
 void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
                      KvPoolDev pool, const int32_t* cos, const int32_t* sin, cudaStream_t st) {
-	const size_t sm = 34 * 8 + 64 + (size_t)((d.hidden + d.kv_hidden + 15) & ~15) +
+	const size_t sm = kRedBytes + 64 + (size_t)((d.hidden + d.kv_hidden + 15) & ~15) +
 	                  (size_t)(d.qkv_rows + d.head_dim) * 4;
 	launch_pdl(k_qkv_post, dim3(b.m), dim3(kRowThreads), sm, st, b, d, layer, layer_index, pool, cos, sin);
 }
 void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
-	launch_pdl(k_ctx_funnel, dim3(b.m), dim3(kRowThreads), 34 * 8 + (size_t)d.hidden * 4, st, b, d, layer);
+	launch_pdl(k_ctx_funnel, dim3(b.m), dim3(kRowThreads), kRedBytes + (size_t)d.hidden * 4, st, b, d, layer);
 }
 void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
 	launch_pdl(k_res1, dim3(b.m), dim3(kRowThreads), res_smem_bytes(d), st, b, d, layer);
@@ -685,7 +770,7 @@ void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const 
                  cudaStream_t st) {
 	launch_pdl(k_res2, dim3(b.m), dim3(kRowThreads), res_smem_bytes(d), st, b, d, layer, next);
 }
-size_t act_smem_bytes(const Dims& d) { return 36 * 8 + 256 * 4 + (size_t)d.inter * 4; }
+size_t act_smem_bytes(const Dims& d) { return kRedBytes + 256 * 4 + (size_t)d.inter * 8; }
 cudaError_t rows_configure(const Dims& d) {
 	cudaError_t e = cudaFuncSetAttribute(k_act, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)act_smem_bytes(d));
 	if (e != cudaSuccess) return e;
