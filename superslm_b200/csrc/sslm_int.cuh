@@ -105,6 +105,37 @@ SSLM_HD bool sge(U128 a, U128 b) {  // signed a >= b
 }
 SSLM_HD U128 sfrom64(int64_t v) { return U128{(uint64_t)v, v < 0 ? ~0ull : 0ull}; }
 
+// ------------------------------------------------ floating-point ESTIMATES only
+// 1/x and sqrt(x) to nearly full double precision without the IEEE division / square-root
+// routines (hundreds of cycles each on a path where one thread block waits on one scalar).
+// Nothing that reaches an output is taken from these: every caller turns the estimate into
+// an integer quotient or root and repairs it with exact integer arithmetic, so their
+// accuracy only bounds how many repair steps run (none or one).
+SSLM_HD double rcp_estimate(double x) {  // x >= 1
+#if defined(__CUDA_ARCH__)
+	double r;
+	asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(r) : "d"(x));
+	r = fma(r, fma(-x, r, 1.0), r);
+	r = fma(r, fma(-x, r, 1.0), r);
+	return r;
+#else
+	return 1.0 / x;
+#endif
+}
+SSLM_HD double sqrt_estimate(double x) {  // x >= 1
+#if defined(__CUDA_ARCH__)
+	double y;
+	asm("rsqrt.approx.ftz.f64 %0, %1;" : "=d"(y) : "d"(x));
+	double s = x * y;
+	const double h = 0.5 * y;
+	s = fma(fma(-s, s, x), h, s);
+	s = fma(fma(-s, s, x), h, s);
+	return s;
+#else
+	return sqrt(x);
+#endif
+}
+
 // ------------------------------------------------- gemmlowp-style requant prims
 // SaturatingRoundingDoublingHighMul (src/intmath.cpp:230-236)
 SSLM_HD int32_t srdhm(int32_t a, int32_t b) {
@@ -160,7 +191,7 @@ SSLM_HD int64_t dyn_recip(int64_t dn) {
 	// multiplies; every other operand still takes the reference's operation sequence.
 	if ((uint64_t)(dn - ((int64_t)1 << 30)) < ((uint64_t)1 << 30)) {
 		const uint64_t num = ((uint64_t)1 << 62) + ((uint64_t)dn >> 1);
-		uint64_t q = (uint64_t)((double)num / (double)dn);
+		uint64_t q = (uint64_t)((double)num * rcp_estimate((double)dn));
 		int64_t r = (int64_t)(num - q * (uint64_t)dn);
 		while (r < 0) { --q; r += dn; }
 		while (r >= dn) { ++q; r -= dn; }
@@ -208,6 +239,52 @@ SSLM_HD int8_t requant_code(int64_t x, int64_t r, int s) {
 	uint64_t mag = sh.lo > 127u ? 127u : sh.lo;
 	int32_t q = (int32_t)mag;
 	return (int8_t)(x < 0 ? -q : q);
+}
+// The same code with 32-bit words, for the operands a funnel hands over once its domain
+// check passed: |x| <= 2^31, 2^31 < R < 2^32 and an exponent E >= 33. With p = |x| * R =
+// hi * 2^32 + lo, floor(p * 127 / 2^32) = hi * 127 + floor(lo * 127 / 2^32) =: a (< 2^38), and
+// the code is min(127, floor((a + 2^(E-33)) / 2^(E-32))) as derived above. Anything outside
+// those ranges (R = 2^32 when the row maximum is a power of two, E = 32 when it is 1) takes
+// requant_code. A Coder is per row; code_of is the per-element step.
+struct Coder {
+	int64_t r;
+	int s;
+	uint32_t r32;
+	int sh;        // E - 32, in [1, 31] when narrow
+	bool narrow;
+};
+SSLM_HD Coder make_coder(int64_t r, int s) {
+	Coder c;
+	c.r = r;
+	c.s = s;
+	c.r32 = (uint32_t)r;
+	c.sh = 30 - s;
+	c.narrow = (62 - s) >= 33 && (62 - s) <= 63 && r > 0 && (uint64_t)r < ((uint64_t)1 << 32);
+	return c;
+}
+SSLM_HD uint32_t umulhi32(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+	return __umulhi(a, b);
+#else
+	return (uint32_t)(((uint64_t)a * b) >> 32);
+#endif
+}
+SSLM_HD int32_t code_narrow(uint32_t ax, bool neg, const Coder& c) {
+	const uint32_t hi = umulhi32(ax, c.r32), lo = ax * c.r32;
+	const uint64_t a = (uint64_t)hi * 127u + umulhi32(lo, 127u);
+	uint64_t mag = (a + ((uint64_t)1 << (c.sh - 1))) >> c.sh;
+	if (mag > 127u) mag = 127u;
+	const int32_t q = (int32_t)mag;
+	return neg ? -q : q;
+}
+SSLM_HD int8_t code_of(int32_t x, const Coder& c) {
+	if (c.narrow) return (int8_t)code_narrow(x < 0 ? 0u - (uint32_t)x : (uint32_t)x, x < 0, c);
+	return requant_code((int64_t)x, c.r, c.s);
+}
+SSLM_HD int8_t code_of(int64_t x, const Coder& c) {
+	const uint64_t ax = x < 0 ? (~(uint64_t)x + 1u) : (uint64_t)x;
+	if (c.narrow && ax <= ((uint64_t)1 << 31)) return (int8_t)code_narrow((uint32_t)ax, x < 0, c);
+	return requant_code(x, c.r, c.s);
 }
 SSLM_HD int64_t sat_add64(int64_t a, int64_t b) {
 	int64_t out = (int64_t)((uint64_t)a + (uint64_t)b);
@@ -309,7 +386,8 @@ SSLM_HD int64_t isqrt64(int64_t n) {
 	if (n >= 0) {
 		// the digit recurrence below yields floor(sqrt(n)); so does a double-precision
 		// estimate repaired with exact integer squares (the estimate is within 1)
-		uint64_t r = (uint64_t)sqrt((double)n);
+		if (n == 0) return 0;
+		uint64_t r = (uint64_t)sqrt_estimate((double)n);
 		while (r * r > (uint64_t)n) --r;
 		while ((r + 1) * (r + 1) <= (uint64_t)n) ++r;
 		return (int64_t)r;

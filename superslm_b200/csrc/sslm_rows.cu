@@ -98,6 +98,17 @@ __device__ __forceinline__ bool wide_stageable(const RowBatch& b, int cols) {
 __device__ __forceinline__ const int32_t* wide_row32(const RowBatch& b, int row) {
 	return (const int32_t*)b.wide + (size_t)row * b.wide_ld;
 }
+// codes of a staged int32 row, four per thread and pass (src 16-byte, dst 4-byte aligned)
+__device__ __forceinline__ void code_words(const int32_t* src, int n4, const Coder& cd, int8_t* dst) {
+	for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+		const int4 p = ((const int4*)src)[i];
+		const uint32_t c0 = (uint8_t)code_of(p.x, cd);
+		const uint32_t c1 = (uint8_t)code_of(p.y, cd);
+		const uint32_t c2 = (uint8_t)code_of(p.z, cd);
+		const uint32_t c3 = (uint8_t)code_of(p.w, cd);
+		((uint32_t*)dst)[i] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+	}
+}
 // After pdl_wait(): thread 0 fetches the GEMM-reduced row maxima of slots [slot, slot + count)
 // (leaving them zero for their next producer) and the row's status word into the misc words;
 // they are readable after the caller's next barrier, which also completes the staged copies.
@@ -124,18 +135,19 @@ __device__ int32_t block_code(const WT* w, int n, unsigned long long mx, const S
                               Scale site, int8_t* out_g, int8_t* out_s, Scale* out_scale) {
 	const FunnelParams fp = funnel_params(mx, incoming, n_incoming, site);
 	if (fp.status != kOk) return fp.status;
+	const Coder cd = make_coder(fp.r, fp.s);
 	if ((n & 3) == 0) {
 		// four codes per thread and pass: word stores to global and shared memory
 		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
 			uint32_t pk = 0;
 #pragma unroll
-			for (int j = 0; j < 4; ++j) pk |= (uint32_t)(uint8_t)requant_code((int64_t)w[4 * i + j], fp.r, fp.s) << (8 * j);
+			for (int j = 0; j < 4; ++j) pk |= (uint32_t)(uint8_t)code_of(w[4 * i + j], cd) << (8 * j);
 			if (out_g) ((uint32_t*)out_g)[i] = pk;
 			if (out_s) ((uint32_t*)out_s)[i] = pk;
 		}
 	} else {
 		for (int i = threadIdx.x; i < n; i += blockDim.x) {
-			const int8_t c = requant_code((int64_t)w[i], fp.r, fp.s);
+			const int8_t c = code_of(w[i], cd);
 			if (out_g) out_g[i] = c;
 			if (out_s) out_s[i] = c;
 		}
@@ -160,24 +172,52 @@ __device__ int32_t block_funnel(const WT* w, int n, const Scale* incoming, int n
 // funnel with no incoming scale. wide: shared int64[n].
 __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Scale site, int64_t* wide,
                                  int8_t* out_g, Scale* out_scale, int64_t* lut, Red& red) {
+	// four codes per word where the rows allow it: these passes are short dependent chains,
+	// and a quarter of the iterations is a quarter of the latency
+	const bool vec = (n & 3) == 0 && ((((uintptr_t)h) | ((uintptr_t)gain)) & 3) == 0;
+	const double inv_n = rcp_estimate((double)n);
 	long long ss = 0;
-	for (int i = threadIdx.x; i < n; i += blockDim.x) {
-		const int v = h[i];
-		ss += v * v;
+	if (vec) {
+		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+			const uint32_t w = ((const uint32_t*)h)[i];
+			const int v0 = (int8_t)w, v1 = (int8_t)(w >> 8), v2 = (int8_t)(w >> 16), v3 = (int8_t)(w >> 24);
+			ss += v0 * v0 + v1 * v1 + v2 * v2 + v3 * v3;
+		}
+	} else {
+		for (int i = threadIdx.x; i < n; i += blockDim.x) {
+			const int v = h[i];
+			ss += v * v;
+		}
 	}
 	ss = block_sum_i64(ss, red, n <= (1 << 20));   // 127^2 * 2^20 / warps fits 32 bits per warp
-	int64_t root = isqrt64(floor_div((int64_t)ss << 32, (int64_t)n));
+	// floor((sum << 32) / n): non-negative operands, an estimated quotient repaired exactly
+	int64_t root = isqrt64((int64_t)udiv_small_quotient((uint64_t)ss << 32, (uint64_t)n, inv_n));
 	if (root < 1) root = 1;
 	// floor((h << 32) / root) depends only on the code: one division per code value, not per element
-	const double inv_root = 1.0 / (double)root;
+	const double inv_root = rcp_estimate((double)root);
 	for (int t = threadIdx.x; t < 255; t += blockDim.x) lut[t] = floor_div_h32(t - 127, root, inv_root);
 	__syncthreads();
 	unsigned long long mx = 0;
-	for (int i = threadIdx.x; i < n; i += blockDim.x) {
-		const int64_t v = lut[(int)h[i] + 127] * (int64_t)gain[i];
-		wide[i] = v;
-		const unsigned long long a = abs_u64(v);
-		mx = a > mx ? a : mx;
+	if (vec) {
+		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+			const uint32_t hw = ((const uint32_t*)h)[i], gw = ((const uint32_t*)gain)[i];
+			int64_t v[4];
+#pragma unroll
+			for (int j = 0; j < 4; ++j) {
+				v[j] = lut[(int)(int8_t)(hw >> (8 * j)) + 127] * (int64_t)(int8_t)(gw >> (8 * j));
+				const unsigned long long a = abs_u64(v[j]);
+				mx = a > mx ? a : mx;
+			}
+			*(longlong2*)&wide[4 * i] = make_longlong2(v[0], v[1]);
+			*(longlong2*)&wide[4 * i + 2] = make_longlong2(v[2], v[3]);
+		}
+	} else {
+		for (int i = threadIdx.x; i < n; i += blockDim.x) {
+			const int64_t v = lut[(int)h[i] + 127] * (int64_t)gain[i];
+			wide[i] = v;
+			const unsigned long long a = abs_u64(v);
+			mx = a > mx ? a : mx;
+		}
 	}
 	mx = block_max_u64(mx, red);   // its barrier also publishes wide[]
 	return block_code<int64_t>(wide, n, mx, nullptr, 0, site, out_g, nullptr, out_scale);
@@ -362,13 +402,23 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 
 	const int q_threads = blockDim.x > 32 ? (int)blockDim.x - 32 : (int)blockDim.x;   // the other warps
 	if ((int)threadIdx.x < q_threads) {
+		const Coder cd = make_coder(fp.r, fp.s);
 		if (lw.b_q != nullptr) {
 			for (int i = threadIdx.x; i < H; i += q_threads) {
 				bool ok;
-				sq[i] = requant_code(biased(wv(i), lw.b_q, i, &ok), fp.r, fp.s);
+				sq[i] = code_of(biased(wv(i), lw.b_q, i, &ok), cd);
+			}
+		} else if (vec) {
+			for (int i = threadIdx.x; i < (H >> 2); i += q_threads) {
+				const int4 p = ((const int4*)sw)[i];
+				const uint32_t c0 = (uint8_t)code_of(p.x, cd);
+				const uint32_t c1 = (uint8_t)code_of(p.y, cd);
+				const uint32_t c2 = (uint8_t)code_of(p.z, cd);
+				const uint32_t c3 = (uint8_t)code_of(p.w, cd);
+				((uint32_t*)sq)[i] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
 			}
 		} else {
-			for (int i = threadIdx.x; i < H; i += q_threads) sq[i] = requant_code(wv(i), fp.r, fp.s);
+			for (int i = threadIdx.x; i < H; i += q_threads) sq[i] = code_of(wv(i), cd);
 		}
 	}
 	if ((lw.b_k != nullptr || lw.b_v != nullptr) && !bias_gate) {
@@ -417,6 +467,25 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 
 	// RoPE: interleaved pairs (2i, 2i+1), table row = position
 	int8_t* qrot = b.qrot + (size_t)r * H;
+	if (vec && (H & 3) == 0 && (d.kv_hidden & 3) == 0) {
+		// two pairs (one word of codes) per thread and pass
+		auto rope_word = [&](uint32_t w4, int pi) -> uint32_t {
+			const int2 c = *(const int2*)&cos_row[pi], s = *(const int2*)&sin_row[pi];
+			int8_t o0, o1, o2, o3;
+			rope_pair_clamped((int8_t)w4, (int8_t)(w4 >> 8), c.x, s.x, &o0, &o1);
+			rope_pair_clamped((int8_t)(w4 >> 16), (int8_t)(w4 >> 24), c.y, s.y, &o2, &o3);
+			return (uint32_t)(uint8_t)o0 | ((uint32_t)(uint8_t)o1 << 8) | ((uint32_t)(uint8_t)o2 << 16) |
+			       ((uint32_t)(uint8_t)o3 << 24);
+		};
+		for (int w = threadIdx.x; w < (H >> 2); w += blockDim.x)
+			((uint32_t*)qrot)[w] = rope_word(((const uint32_t*)sq)[w], (2 * w) % half);
+		for (int w = threadIdx.x; w < (d.kv_hidden >> 2); w += blockDim.x) {
+			const int h = (4 * w) / hd, dd = 4 * w - h * hd;
+			int8_t* kdst = pool.base + kv_plane_offset(d, pool, layer_index, h, 0) +
+			               ((int64_t)page * kPageTokens + slot) * hd + dd;
+			*(uint32_t*)kdst = rope_word(((const uint32_t*)sk)[w], dd / 2);
+		}
+	} else {
 	for (int p = threadIdx.x; p < H / 2; p += blockDim.x) {
 		const int pi = p % half;
 		const int32_t c = cos_row[pi], s = sin_row[pi];
@@ -434,6 +503,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		               ((int64_t)page * kPageTokens + slot) * hd + dd;
 		kdst[0] = ox;
 		kdst[1] = oy;
+	}
 	}
 
 	__syncthreads();
@@ -471,18 +541,19 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 		return;
 	}
 	int8_t* out = b.ctx + (size_t)r * n;
+	const Coder cd = make_coder(fp.r, fp.s);
 	if (vec) {
 		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
 			const int4 p = ((const int4*)sw)[i];
-			const uint32_t c0 = (uint8_t)requant_code((int64_t)p.x, fp.r, fp.s);
-			const uint32_t c1 = (uint8_t)requant_code((int64_t)p.y, fp.r, fp.s);
-			const uint32_t c2 = (uint8_t)requant_code((int64_t)p.z, fp.r, fp.s);
-			const uint32_t c3 = (uint8_t)requant_code((int64_t)p.w, fp.r, fp.s);
+			const uint32_t c0 = (uint8_t)code_of(p.x, cd);
+			const uint32_t c1 = (uint8_t)code_of(p.y, cd);
+			const uint32_t c2 = (uint8_t)code_of(p.z, cd);
+			const uint32_t c3 = (uint8_t)code_of(p.w, cd);
 			((uint32_t*)out)[i] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
 		}
 	} else {
 		const int32_t* w = b.ctxw + (size_t)r * n;
-		for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = requant_code((int64_t)w[i], fp.r, fp.s);
+		for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = code_of(w[i], cd);
 	}
 	if (threadIdx.x == 0) b.cs[r] = fp.out;
 }
@@ -506,16 +577,33 @@ __device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t
 	// one reduction carries both the row maximum and "some code's rescaled magnitude left
 	// int64": no in-range sum has magnitude 2^64 - 1, which stands for the latter
 	unsigned long long mx = 0;
-	for (int i = threadIdx.x; i < n; i += blockDim.x) {
-		const int c = (int)branch_s[i] + 127;
-		if (lex[c]) {
-			mx = ~0ull;
-			wide[i] = 0;
-		} else {
-			const int64_t v = lut[c] + (int64_t)stream[i];
-			wide[i] = v;
-			const unsigned long long a = abs_u64(v);
-			mx = a > mx ? a : mx;
+	if ((n & 3) == 0 && ((((uintptr_t)branch_s) | ((uintptr_t)stream)) & 3) == 0) {
+		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+			const uint32_t bw = ((const uint32_t*)branch_s)[i], sw = ((const uint32_t*)stream)[i];
+			int64_t v[4];
+#pragma unroll
+			for (int j = 0; j < 4; ++j) {
+				const int c = (int)(int8_t)(bw >> (8 * j)) + 127;
+				const bool ex = lex[c] != 0;
+				v[j] = ex ? 0 : lut[c] + (int64_t)(int8_t)(sw >> (8 * j));
+				const unsigned long long a = ex ? ~0ull : abs_u64(v[j]);
+				mx = a > mx ? a : mx;
+			}
+			*(longlong2*)&wide[4 * i] = make_longlong2(v[0], v[1]);
+			*(longlong2*)&wide[4 * i + 2] = make_longlong2(v[2], v[3]);
+		}
+	} else {
+		for (int i = threadIdx.x; i < n; i += blockDim.x) {
+			const int c = (int)branch_s[i] + 127;
+			if (lex[c]) {
+				mx = ~0ull;
+				wide[i] = 0;
+			} else {
+				const int64_t v = lut[c] + (int64_t)stream[i];
+				wide[i] = v;
+				const unsigned long long a = abs_u64(v);
+				mx = a > mx ? a : mx;
+			}
 		}
 	}
 	mx = block_max_u64(mx, red);   // its barrier also publishes wide[]
@@ -557,10 +645,11 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	const FunnelParams fp = funnel_params(mx, &cs, 1, c_o);
 	int32_t st = fp.status;
 	if (st == kOk) {
+		const Coder cd = make_coder(fp.r, fp.s);
 		if (vec) {
-			for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = requant_code((int64_t)wraw[i], fp.r, fp.s);
+			code_words(wraw, n >> 2, cd, so);
 		} else {
-			for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+			for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = code_of(load_wide(b, r, i), cd);
 		}
 		__syncthreads();
 		st = block_residual(so, fp.out, vec ? sx : b.x + (size_t)r * n, xs, n, c_res, wide,
@@ -610,10 +699,11 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	const FunnelParams fp = funnel_params(mx, &as, 1, c_down);
 	int32_t st = fp.status;
 	if (st == kOk) {
+		const Coder cd = make_coder(fp.r, fp.s);
 		if (vec) {
-			for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = requant_code((int64_t)wraw[i], fp.r, fp.s);
+			code_words(wraw, n >> 2, cd, sd);
 		} else {
-			for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = requant_code(load_wide(b, r, i), fp.r, fp.s);
+			for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = code_of(load_wide(b, r, i), cd);
 		}
 		__syncthreads();
 		st = block_residual(sd, fp.out, vec ? sa : b.a + (size_t)r * n, rs, n, c_res, wide,
@@ -625,6 +715,50 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 		                   b.nrm + (size_t)r * n, &b.ns[r], lut, red);
 	}
 	set_status(b, r, st);
+}
+
+// The activation row is the longest a row kernel walks (intermediate width, three codes per
+// element), and its passes are bound by instruction issue: the row's coders are checked once
+// and the passes below are compiled for the 32-bit coder and for the general one.
+template <bool NARROW>
+__device__ __forceinline__ int code_sel(int32_t x, const Coder& c) {
+	if (NARROW) return code_narrow(x < 0 ? 0u - (uint32_t)x : (uint32_t)x, x < 0, c);
+	return (int)requant_code((int64_t)x, c.r, c.s);
+}
+// wide[] holds the gate row on entry and g * sigmoid(g) * u on exit; returns this thread's
+// largest product magnitude
+template <bool NARROW>
+__device__ __forceinline__ uint32_t act_products(int32_t* wide, const int32_t* urow, const int32_t* gsil, int n4,
+                                                 const Coder& cg, const Coder& cu) {
+	uint32_t lmax = 0;
+#pragma unroll 2
+	for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+		const int4 gv = ((const int4*)wide)[i], uv = ((const int4*)urow)[i];
+		const int gs[4] = {gv.x, gv.y, gv.z, gv.w}, us[4] = {uv.x, uv.y, uv.z, uv.w};
+		int pr[4];
+#pragma unroll
+		for (int j = 0; j < 4; ++j) {
+			const int g = code_sel<NARROW>(gs[j], cg);
+			const int u = code_sel<NARROW>(us[j], cu);
+			pr[j] = gsil[g + 127] * u;
+			const uint32_t a = pr[j] < 0 ? 0u - (uint32_t)pr[j] : (uint32_t)pr[j];
+			lmax = a > lmax ? a : lmax;
+		}
+		((int4*)wide)[i] = make_int4(pr[0], pr[1], pr[2], pr[3]);
+	}
+	return lmax;
+}
+template <bool NARROW>
+__device__ __forceinline__ void code_row4(const int32_t* wide, int n4, const Coder& c, int8_t* out) {
+#pragma unroll 2
+	for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+		const int4 p = ((const int4*)wide)[i];
+		const uint32_t c0 = (uint8_t)code_sel<NARROW>(p.x, c);
+		const uint32_t c1 = (uint8_t)code_sel<NARROW>(p.y, c);
+		const uint32_t c2 = (uint8_t)code_sel<NARROW>(p.z, c);
+		const uint32_t c3 = (uint8_t)code_sel<NARROW>(p.w, c);
+		((uint32_t*)out)[i] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+	}
 }
 
 // gate / up funnels -> SwiGLU activation site (MlpActSite, forward_sites.cpp:796-864)
@@ -679,23 +813,9 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	// with their running maximum so that the funnel below needs no second pass for it
 	uint32_t lmax = 0;
 	if (vec) {
-		const int4* gp = (const int4*)wide;
-		const int4* up = (const int4*)urow;
-#pragma unroll 2
-		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
-			const int4 gv = gp[i], uv = up[i];
-			const int gs[4] = {gv.x, gv.y, gv.z, gv.w}, us[4] = {uv.x, uv.y, uv.z, uv.w};
-			int pr[4];
-#pragma unroll
-			for (int j = 0; j < 4; ++j) {
-				const int g = requant_code((int64_t)gs[j], fg.r, fg.s);
-				const int u = requant_code((int64_t)us[j], fu.r, fu.s);
-				pr[j] = gsil[g + 127] * u;
-				const uint32_t a = pr[j] < 0 ? 0u - (uint32_t)pr[j] : (uint32_t)pr[j];
-				lmax = a > lmax ? a : lmax;
-			}
-			((int4*)wide)[i] = make_int4(pr[0], pr[1], pr[2], pr[3]);
-		}
+		const Coder cg = make_coder(fg.r, fg.s), cu = make_coder(fu.r, fu.s);
+		lmax = (cg.narrow && cu.narrow) ? act_products<true>(wide, urow, gsil, n >> 2, cg, cu)
+		                                : act_products<false>(wide, urow, gsil, n >> 2, cg, cu);
 	} else {
 		for (int i = threadIdx.x; i < n; i += blockDim.x) {
 			const int g = requant_code(load_wide(b, r, i), fg.r, fg.s);
@@ -715,14 +835,9 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	}
 	int8_t* out = b.act + (size_t)r * n;
 	if ((n & 3) == 0) {
-		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
-			const int4 p = ((const int4*)wide)[i];
-			const uint32_t c0 = (uint8_t)requant_code((int64_t)p.x, fp.r, fp.s);
-			const uint32_t c1 = (uint8_t)requant_code((int64_t)p.y, fp.r, fp.s);
-			const uint32_t c2 = (uint8_t)requant_code((int64_t)p.z, fp.r, fp.s);
-			const uint32_t c3 = (uint8_t)requant_code((int64_t)p.w, fp.r, fp.s);
-			((uint32_t*)out)[i] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
-		}
+		const Coder ca = make_coder(fp.r, fp.s);
+		if (ca.narrow) code_row4<true>(wide, n >> 2, ca, out);
+		else code_row4<false>(wide, n >> 2, ca, out);
 	} else {
 		for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = requant_code((int64_t)wide[i], fp.r, fp.s);
 	}

@@ -22,7 +22,9 @@ def lib():
         "dev_srdhm": (i32, [i32, i32]), "dev_rdivpot32": (i32, [i32, C.c_int]), "dev_rdivpot64": (i64, [i64, C.c_int]),
         "dev_fold": (i32, [i32] * 4), "dev_amp_fold": (i32, [i32] * 4),
         "dev_normalize_scale": (None, [i64, P64, PI]), "dev_dyn_recip": (i64, [i64]),
-        "dev_requant_code": (C.c_int8, [i64, i64, C.c_int]), "dev_combine": (None, [i64] * 4 + [P64, P64]),
+        "dev_requant_code": (C.c_int8, [i64, i64, C.c_int]),
+        "dev_code_of64": (C.c_int8, [i64, i64, C.c_int]), "dev_code_of32": (C.c_int8, [i32, i64, C.c_int]),
+        "dev_combine": (None, [i64] * 4 + [P64, P64]),
         "dev_funnel_params": (C.c_int, [C.c_uint64, C.c_void_p, C.c_int, i64, i64, P64, PI, P64, P64]),
         "dev_floor_div": (i64, [i64, i64]), "dev_floor_div_h32": (i64, [C.c_int, i64]), "dev_udiv_small": (C.c_uint64, [C.c_uint64] * 2),
         "dev_isqrt": (i64, [i64]), "dev_landing_rescale": (i64, [i64] * 5 + [PI, PI]),

@@ -12,6 +12,8 @@ int32_t dev_amp_fold(int32_t a, int32_t id, int32_t m, int32_t s) { return amp_f
 void dev_normalize_scale(int64_t d, int64_t* dn, int* s) { normalize_scale(d, dn, s); }
 int64_t dev_dyn_recip(int64_t dn) { return dyn_recip(dn); }
 int8_t dev_requant_code(int64_t x, int64_t r, int s) { return requant_code(x, r, s); }
+int8_t dev_code_of64(int64_t x, int64_t r, int s) { return code_of(x, make_coder(r, s)); }
+int8_t dev_code_of32(int32_t x, int64_t r, int s) { return code_of(x, make_coder(r, s)); }
 void dev_combine(int64_t am, int64_t ae, int64_t bm, int64_t be, int64_t* om, int64_t* oe) {
 	Scale c = combine(Scale{am, ae}, Scale{bm, be});
 	*om = c.m; *oe = c.e;

@@ -27,6 +27,28 @@ def test_reciprocal_and_requant(port):
         assert d.dev_requant_code(x, r, s) == port.osc_requant_code_wide(x, r, s), (x, r, s)
 
 
+def test_narrow_coder_equals_the_wide_one(port):
+    # the per-row coder's 32-bit path against RequantTokenCodeWide, with the edges of its
+    # window: R = 2^32 and R just below, exponent 32/33/63, |x| = 2^31 and 2^31 + 1, rounding ties
+    d = devint.lib()
+    rnd = random.Random(11)
+    for i in range(150000):
+        s = rnd.choice([rnd.randrange(-1, 31), -1, 0, 29, 30])
+        dn = rnd.choice([rnd.randrange(1 << 30, 1 << 31), 1 << 30, (1 << 30) + 1, (1 << 31) - 1])
+        r = port.osc_dyn_recip(dn) if i % 10 else rnd.choice([1 << 32, (1 << 32) - 1, (1 << 31) + 1, rnd.randrange(1, 1 << 34)])
+        x = rnd.choice([ri(rnd, 31), ri(rnd, 31), ri(rnd, 20), ri(rnd, 8), 1 << 31, -(1 << 31), (1 << 31) + 1,
+                        -(1 << 31) - 1, (1 << 31) - 1, 0, 1, -1, ri(rnd, 40)])
+        if i % 5 == 0 and 62 - s >= 33:
+            # a value whose scaled magnitude sits next to a rounding tie
+            k = rnd.randrange(0, 128)
+            x = ((2 * k + 1) << (62 - s - 1)) // (r * 127) + rnd.choice([-1, 0, 1])
+            x = rnd.choice([x, -x])
+        want = port.osc_requant_code_wide(x, r, s)
+        assert d.dev_code_of64(x, r, s) == want, (x, r, s)
+        if -(1 << 31) <= x < (1 << 31):
+            assert d.dev_code_of32(x, r, s) == want, (x, r, s)
+
+
 def test_landing_rescale_fast_and_general(port):
     d = devint.lib()
     rnd = random.Random(2)
