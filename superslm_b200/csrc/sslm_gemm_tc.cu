@@ -52,7 +52,7 @@ struct TcCfg {
 	static constexpr uint32_t kStageBytes = (uint32_t)(MT * BM + BN) * BK;
 	static constexpr int kStages = (kSmemBudget / (int)kStageBytes) > 8 ? 8 : (kSmemBudget / (int)kStageBytes);
 	static constexpr uint32_t kTmemCols = 2u * MT * BN;                       // two accumulator stages
-	static constexpr uint32_t kFoldBytes = 2u * BN * 3 * 4;                   // double-buffered fold triples
+	static constexpr uint32_t kFoldBytes = 2u * BN * 16;                      // double-buffered per-column fold words
 	static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kFoldBytes + 1024 /*align*/ + 256 /*barriers*/;
 	// s8 x s8 -> s32, A and B K-major, M = 128, N = BN
 	static constexpr uint32_t kInstrDesc =
@@ -125,10 +125,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 // One 32-column chunk of one output row: fold, LoRA delta, store, row max / argmax key.
-// sfold: this tile's fold triples in shared memory (or nullptr: no fold), indexed by column
-// offset inside the tile.
+// sfold: this tile's fold words in shared memory, {multiplier, shift, rounding half, identity}
+// per column (or nullptr: no fold), indexed by column offset inside the tile.
 __device__ __forceinline__ void epilogue_chunk(const LinearArgs& a, const uint32_t (&r)[32], int row, int n_base,
-                                               int col_in_tile, const int32_t* sfold, const LoraLayerDev* lora,
+                                               int col_in_tile, const int4* sfold, const LoraLayerDev* lora,
                                                bool vec_ok, unsigned long long (&lmax)[3], unsigned long long& lbest) {
 #pragma unroll
 	for (int j4 = 0; j4 < 32; j4 += 4) {
@@ -142,8 +142,8 @@ __device__ __forceinline__ void epilogue_chunk(const LinearArgs& a, const uint32
 			if (n >= a.N) continue;
 			int32_t v32 = (int32_t)r[j4 + jj];
 			if (sfold != nullptr) {
-				const int32_t* f = sfold + 3 * (col_in_tile + j4 + jj);
-				v32 = fold(v32, f[0], f[1], f[2]);
+				const int4 f = sfold[col_in_tile + j4 + jj];
+				v32 = fold(v32, f.w, f.x, f.y);
 			}
 			if (a.best != nullptr) {   // head: greedy argmax key, lowest index wins ties
 				if (a.row_mask != nullptr) {
@@ -201,7 +201,7 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 	const uint32_t raw = smem_u32(smem_raw);
 	const uint32_t base = (raw + 1023u) & ~1023u;            // SW128 tiles want 1024-byte alignment
 	unsigned char* smem = smem_raw + (base - raw);
-	int32_t* sfold = (int32_t*)(smem + S * Cfg::kStageBytes);                       // [2][BN*3]
+	int4* sfold = (int4*)(smem + S * Cfg::kStageBytes);                             // [2][BN]
 	const uint32_t bars = base + S * Cfg::kStageBytes + Cfg::kFoldBytes;            // 8-byte slots
 	auto full_bar = [&](int s) { return bars + 8u * s; };
 	auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
@@ -312,16 +312,32 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 			const uint32_t as = tc & 1u;
 			const int t = w % tiles, ks = w / tiles;
 			const int m0 = (t % m_groups) * MT * BM, n0 = (t / m_groups) * BN;
-			int32_t* sf = nullptr;
+			int4* sf = nullptr;
+			uint32_t odd_column = 0;                           // a column the one-rounding fold does not cover
 			if (a.fold != nullptr) {
-				sf = sfold + as * BN * 3;
-				for (int i = et; i < BN * 3; i += kEpiThreads) {
-					const int n = n0 + i / 3;
-					sf[i] = n < a.N ? a.fold[(size_t)n0 * 3 + i] : 0;
+				sf = sfold + as * BN;
+				for (int i = et; i < BN; i += kEpiThreads) {
+					const int n = n0 + i;
+					int4 f = make_int4(0, 0, 0, 0);
+					if (n < a.N) {
+						const int32_t* g = a.fold + (size_t)n * 3;
+						const int32_t idn = g[0], mult = g[1], shift = g[2];
+						const bool plain = fold_is_plain(idn, mult, shift);
+						f = make_int4(mult, shift, (plain && shift > 0) ? (int)(1u << (shift - 1)) : 0, idn);
+						if (!plain) odd_column = 1u;
+					}
+					sf[i] = f;
 				}
 			}
 			if (et == 0) s_stop[as] = s_timeout;               // one thread decides, so all eight warps agree
-			asm volatile("bar.sync 1, 256;" ::: "memory");     // fold triples + stop flag visible to the epilogue warps
+			// fold words + stop flag visible to the epilogue warps; the barrier also tells every
+			// thread whether any column of the tile needs the two-step fold
+			uint32_t any_odd;
+			asm volatile(
+			    "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.or.pred p, 1, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+			    : "=r"(any_odd)
+			    : "r"(odd_column)
+			    : "memory");
 			if (s_stop[as] != 0) {
 				if (a.status != nullptr) {
 					for (int mt = 0; mt < MT; ++mt) {
@@ -442,8 +458,10 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 						}
 						int seg = 0;
 						while (seg + 1 < a.nseg && nb >= a.seg_end[seg]) ++seg;
-						if (fast_ok && full && nb + 32 <= a.seg_end[seg]) {
-							// one segment, whole chunk inside N: no branches, so the 32 elements interleave
+						if (fast_ok && any_odd == 0u && full && nb + 32 <= a.seg_end[seg]) {
+							// one segment, whole chunk inside N, every column on the one-rounding fold:
+							// no branches, one shared-memory word load per element, and the fold's
+							// magnitude doubles as the row-maximum candidate
 							uint32_t mx = 0;
 							int32_t* dst = (int32_t*)a.out + (size_t)row * a.out_ld + nb;
 #pragma unroll
@@ -451,12 +469,10 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 								int v[4];
 #pragma unroll
 								for (int jj = 0; jj < 4; ++jj) {
-									const int32_t* f = sf + 3 * (c0 + j4 + jj);
-									const int32_t acc = (int32_t)r[j4 + jj];
-									const int32_t fv = rdivpot32(srdhm(acc, f[1]), f[2]);
-									v[jj] = f[0] != 0 ? acc : fv;
-									const uint32_t ab = v[jj] < 0 ? 0u - (uint32_t)v[jj] : (uint32_t)v[jj];
-									mx = ab > mx ? ab : mx;
+									const int4 f = sf[c0 + j4 + jj];
+									uint32_t mag;
+									v[jj] = fold_plain((int32_t)r[j4 + jj], f.x, f.y, (uint32_t)f.z, &mag);
+									mx = mag > mx ? mag : mx;
 								}
 								*(int4*)(dst + j4) = make_int4(v[0], v[1], v[2], v[3]);
 							}

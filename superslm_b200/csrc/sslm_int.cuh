@@ -14,9 +14,16 @@
 
 #if defined(__CUDACC__)
 #define SSLM_HD __host__ __device__ __forceinline__
+#define SSLM_HD_OUTLINE inline __host__ __device__ __noinline__
 #else
 #define SSLM_HD inline
+#define SSLM_HD_OUTLINE inline __attribute__((noinline))
 #endif
+// SSLM_HD_OUTLINE marks the general (rare-operand) halves of functions whose common case has a
+// short exact form, and the per-row scalar derivations that a kernel calls several times. Kept
+// out of line they exist once per module instead of once per call site and unrolled pass: a
+// row kernel executes most of its instructions once per block, so its speed is set by how many
+// instruction-cache lines it touches, and the inlined general paths made those kernels ~100 KB.
 
 namespace sslm {
 
@@ -160,6 +167,26 @@ SSLM_HD int32_t fold(int32_t acc, int32_t identity, int32_t mult, int32_t shift)
 	if (identity != 0) return acc;
 	return rdivpot32(srdhm(acc, mult), shift);
 }
+// The same fold for the GEMM epilogue, where it runs once per output element. For a column
+// that is not an identity, has 0 <= shift <= 31 and a multiplier other than INT32_MIN (the
+// only operand that can saturate the doubling high multiply) the two rounding steps are
+//   t = (acc * mult + 2^30) >> 31                       (no saturation possible)
+//   fold = sign(t) * ((|t| + half) >> shift),  half = shift ? 2^(shift-1) : 0
+// because rounding half away from zero equals the reference's mask / threshold test:
+// for t >= 0 the test adds one iff the remainder >= 2^(shift-1); for t = -u it yields
+// -(k+1) iff u mod 2^shift >= 2^(shift-1), else -k, with k = u >> shift. The magnitude
+// (|t| + half) >> shift is also |fold|, which the row maximum wants. Other columns take fold().
+SSLM_HD bool fold_is_plain(int32_t identity, int32_t mult, int32_t shift) {
+	return identity == 0 && shift >= 0 && shift <= 31 && mult != (int32_t)(-2147483647 - 1);
+}
+SSLM_HD int32_t fold_plain(int32_t acc, int32_t mult, int32_t shift, uint32_t half, uint32_t* magnitude) {
+	const int64_t p = (int64_t)acc * (int64_t)mult + ((int64_t)1 << 30);
+	const int32_t t = (int32_t)(p >> 31);
+	const uint32_t u = t < 0 ? 0u - (uint32_t)t : (uint32_t)t;
+	const uint32_t a = (u + half) >> shift;
+	*magnitude = a;
+	return t < 0 ? (int32_t)(0u - a) : (int32_t)a;
+}
 // ApplyAmplifyingWeightScaleFold (src/forward/forward_sites.cpp:472-481) with
 // SaturatingLeftShift32 (src/intmath.cpp:270-276)
 SSLM_HD int32_t amp_fold(int32_t acc, int32_t identity, int32_t mult, int32_t exponent) {
@@ -183,20 +210,7 @@ SSLM_HD void normalize_scale(int64_t d_prime, int64_t* dn, int* s) {
 // DynamicScaleReciprocal (src/intmath.cpp:303-333): seed, 3 Newton steps, 2
 // corrections, on the exact word sequence of the reference (it is also called on
 // non-canonical mantissas, where only the operation sequence defines the result).
-SSLM_HD int64_t dyn_recip(int64_t dn) {
-	// On a normalised divisor (2^30 <= dn < 2^31, every funnel's case) the seed, the three
-	// Newton steps and the two corrections land on round(2^62 / dn) = floor((2^62 + dn/2) / dn):
-	// checked exhaustively, once, over all 2^30 such divisors against the word sequence
-	// below. One division (a double estimate repaired with integers) replaces ~40 wide
-	// multiplies; every other operand still takes the reference's operation sequence.
-	if ((uint64_t)(dn - ((int64_t)1 << 30)) < ((uint64_t)1 << 30)) {
-		const uint64_t num = ((uint64_t)1 << 62) + ((uint64_t)dn >> 1);
-		uint64_t q = (uint64_t)((double)num * rcp_estimate((double)dn));
-		int64_t r = (int64_t)(num - q * (uint64_t)dn);
-		while (r < 0) { --q; r += dn; }
-		while (r >= dn) { ++q; r -= dn; }
-		return (int64_t)q;
-	}
+SSLM_HD_OUTLINE int64_t dyn_recip_sequence(int64_t dn) {
 	const int64_t c48 = (2 * ((int64_t)48 << 31) + 17) / 34;
 	const int64_t c32 = (2 * ((int64_t)32 << 31) + 17) / 34;
 	int64_t y = c48 - ((int64_t)((uint64_t)c32 * (uint64_t)dn) >> 31);
@@ -216,7 +230,33 @@ SSLM_HD int64_t dyn_recip(int64_t dn) {
 	}
 	return y;
 }
-// RequantTokenCodeWide (src/intmath.cpp:476-490)
+SSLM_HD int64_t dyn_recip(int64_t dn) {
+	// On a normalised divisor (2^30 <= dn < 2^31, every funnel's case) the seed, the three
+	// Newton steps and the two corrections land on round(2^62 / dn) = floor((2^62 + dn/2) / dn):
+	// checked exhaustively, once, over all 2^30 such divisors against the word sequence
+	// below. One division (a double estimate repaired with integers) replaces ~40 wide
+	// multiplies; every other operand still takes the reference's operation sequence.
+	if ((uint64_t)(dn - ((int64_t)1 << 30)) < ((uint64_t)1 << 30)) {
+		const uint64_t num = ((uint64_t)1 << 62) + ((uint64_t)dn >> 1);
+		uint64_t q = (uint64_t)((double)num * rcp_estimate((double)dn));
+		int64_t r = (int64_t)(num - q * (uint64_t)dn);
+		while (r < 0) { --q; r += dn; }
+		while (r >= dn) { ++q; r -= dn; }
+		return (int64_t)q;
+	}
+	return dyn_recip_sequence(dn);
+}
+// RequantTokenCodeWide (src/intmath.cpp:476-490): the 128-bit composite for any operands
+SSLM_HD_OUTLINE int8_t requant_code_general(int64_t x, int64_t r, int s) {
+	int exponent = 62 - s;  // [32,63]
+	uint64_t ax = x < 0 ? (~(uint64_t)x + 1u) : (uint64_t)x;
+	U128 prod = umul128x64(umul64(ax, (uint64_t)r), 127u);
+	U128 num = uadd(U128{prod.lo << 1, (prod.hi << 1) | (prod.lo >> 63)}, U128{(uint64_t)1 << exponent, 0});
+	U128 sh = ushr(num, exponent + 1);
+	uint64_t mag = sh.lo > 127u ? 127u : sh.lo;
+	int32_t q = (int32_t)mag;
+	return (int8_t)(x < 0 ? -q : q);
+}
 SSLM_HD int8_t requant_code(int64_t x, int64_t r, int s) {
 	int exponent = 62 - s;  // [32,63]
 	uint64_t ax = x < 0 ? (~(uint64_t)x + 1u) : (uint64_t)x;
@@ -233,12 +273,7 @@ SSLM_HD int8_t requant_code(int64_t x, int64_t r, int s) {
 		const int32_t qf = (int32_t)mag;
 		return (int8_t)(x < 0 ? -qf : qf);
 	}
-	U128 prod = umul128x64(umul64(ax, (uint64_t)r), 127u);
-	U128 num = uadd(U128{prod.lo << 1, (prod.hi << 1) | (prod.lo >> 63)}, U128{(uint64_t)1 << exponent, 0});
-	U128 sh = ushr(num, exponent + 1);
-	uint64_t mag = sh.lo > 127u ? 127u : sh.lo;
-	int32_t q = (int32_t)mag;
-	return (int8_t)(x < 0 ? -q : q);
+	return requant_code_general(x, r, s);
 }
 // The same code with 32-bit words, for the operands a funnel hands over once its domain
 // check passed: |x| <= 2^31, 2^31 < R < 2^32 and an exponent E >= 33. With p = |x| * R =
@@ -279,12 +314,12 @@ SSLM_HD int32_t code_narrow(uint32_t ax, bool neg, const Coder& c) {
 }
 SSLM_HD int8_t code_of(int32_t x, const Coder& c) {
 	if (c.narrow) return (int8_t)code_narrow(x < 0 ? 0u - (uint32_t)x : (uint32_t)x, x < 0, c);
-	return requant_code((int64_t)x, c.r, c.s);
+	return requant_code_general((int64_t)x, c.r, c.s);
 }
 SSLM_HD int8_t code_of(int64_t x, const Coder& c) {
 	const uint64_t ax = x < 0 ? (~(uint64_t)x + 1u) : (uint64_t)x;
 	if (c.narrow && ax <= ((uint64_t)1 << 31)) return (int8_t)code_narrow((uint32_t)ax, x < 0, c);
-	return requant_code(x, c.r, c.s);
+	return requant_code_general(x, c.r, c.s);
 }
 SSLM_HD int64_t sat_add64(int64_t a, int64_t b) {
 	int64_t out = (int64_t)((uint64_t)a + (uint64_t)b);
@@ -318,17 +353,43 @@ struct FunnelParams {
 	Scale out;
 	int32_t status;
 };
-SSLM_HD FunnelParams funnel_params(uint64_t max_abs, const Scale* incoming, int n_incoming,
-                                   Scale site_constant) {
+//
+// The fold of the incoming scales and the site constant does not depend on the row maximum, so
+// it is split off (funnel_prefold): a kernel derives it while the data it will reduce is still
+// on its way, and only normalise + reciprocal + one combine (funnel_finish) follow the maximum.
+struct FunnelFold {
+	Scale run;            // incoming[0] (x) incoming[1] ... (x) site constant
+	int32_t pre_status;   // a mantissa outside int32 before anything is folded
+	int32_t fold_status;  // a folded mantissa outside int32
+};
+SSLM_HD FunnelFold funnel_prefold(const Scale* incoming, int n_incoming, Scale site_constant) {
+	FunnelFold f;
+	f.run = Scale{0, 0};
+	f.pre_status = kOk;
+	f.fold_status = kOk;
+	for (int i = 0; i < n_incoming; ++i) {
+		if (!fits_i32(incoming[i].m)) f.pre_status = kCarriedScaleMantissaOutOfDomain;
+	}
+	if (!fits_i32(site_constant.m)) f.pre_status = kCarriedScaleMantissaOutOfDomain;
+	if (f.pre_status != kOk) return f;
+	Scale run = n_incoming > 0 ? incoming[0] : site_constant;
+	for (int i = 1; i < n_incoming; ++i) {
+		run = combine(run, incoming[i]);
+		if (!fits_i32(run.m)) f.fold_status = kCarriedScaleMantissaOutOfDomain;
+	}
+	if (n_incoming > 0) {
+		run = combine(run, site_constant);
+		if (!fits_i32(run.m)) f.fold_status = kCarriedScaleMantissaOutOfDomain;
+	}
+	f.run = run;
+	return f;
+}
+SSLM_HD FunnelParams funnel_finish(uint64_t max_abs, const FunnelFold& f) {
 	FunnelParams fp;
 	fp.r = 0;
 	fp.s = 0;
 	fp.out = Scale{0, 0};
-	fp.status = kOk;
-	for (int i = 0; i < n_incoming; ++i) {
-		if (!fits_i32(incoming[i].m)) fp.status = kCarriedScaleMantissaOutOfDomain;
-	}
-	if (!fits_i32(site_constant.m)) fp.status = kCarriedScaleMantissaOutOfDomain;
+	fp.status = f.pre_status;
 	if (fp.status != kOk) return fp;
 	uint64_t d = max_abs < 1 ? 1 : max_abs;
 	if (d > ((uint64_t)1 << 31)) {
@@ -338,19 +399,15 @@ SSLM_HD FunnelParams funnel_params(uint64_t max_abs, const Scale* incoming, int 
 	int64_t dn;
 	normalize_scale((int64_t)d, &dn, &fp.s);
 	fp.r = dyn_recip(dn);
-	Scale run = n_incoming > 0 ? incoming[0] : site_constant;
-	for (int i = 1; i < n_incoming; ++i) {
-		run = combine(run, incoming[i]);
-		if (!fits_i32(run.m)) fp.status = kCarriedScaleMantissaOutOfDomain;
-	}
-	if (n_incoming > 0) {
-		run = combine(run, site_constant);
-		if (!fits_i32(run.m)) fp.status = kCarriedScaleMantissaOutOfDomain;
-	}
-	run = combine(run, Scale{dn, -(int64_t)fp.s});
+	fp.status = f.fold_status;
+	const Scale run = combine(f.run, Scale{dn, -(int64_t)fp.s});
 	if (!fits_i32(run.m)) fp.status = kCarriedScaleMantissaOutOfDomain;
 	fp.out = run;
 	return fp;
+}
+SSLM_HD FunnelParams funnel_params(uint64_t max_abs, const Scale* incoming, int n_incoming,
+                                   Scale site_constant) {
+	return funnel_finish(max_abs, funnel_prefold(incoming, n_incoming, site_constant));
 }
 
 // ----------------------------------------------------------- exact divisions
@@ -418,7 +475,7 @@ SSLM_HD bool bias_exponent_in_domain(int64_t e_a, int* exponent) {
 	return true;
 }
 // false when the rounded term does not fit int64 (the reference refuses the row)
-SSLM_HD bool bias_reconcile(int64_t b, int64_t r_a, int exponent, int64_t* term) {
+SSLM_HD_OUTLINE bool bias_reconcile(int64_t b, int64_t r_a, int exponent, int64_t* term) {
 	const U128 w = smul64(b, r_a);
 	const uint64_t mask = ((uint64_t)1 << exponent) - 1u;     // exponent <= 63
 	const bool neg = (int64_t)w.hi < 0;
@@ -451,28 +508,12 @@ SSLM_HD bool bias_accumulate(int64_t acc, int64_t term, int64_t* out) {
 // round_half_away((code * m_a * r_t) / 2^(62-(e_a-e_t))), exact left shift when the
 // composed exponent is negative; reports "outside +-127 or lost" (the saturation
 // counter's predicate) and "does not fit int64".
-SSLM_HD int64_t landing_rescale(int64_t code, int64_t m_a, int64_t r_t, int64_t e_a, int64_t e_t,
-                                bool* saturated, bool* exceeded_int64) {
+SSLM_HD_OUTLINE int64_t landing_rescale_general(int64_t code, int64_t m_a, int64_t r_t, int64_t k,
+                                                bool* saturated, bool* exceeded_int64) {
 	const bool neg = (code < 0) != (m_a < 0);
 	uint64_t ac = code < 0 ? (~(uint64_t)code + 1u) : (uint64_t)code;
 	uint64_t am = m_a < 0 ? (~(uint64_t)m_a + 1u) : (uint64_t)m_a;
 	U128 mag = umul128x64(umul64(ac, am), (uint64_t)r_t);
-	int64_t k = sat_sub64(62, sat_sub64(e_a, e_t));
-	if (k > 4096) k = 4096;
-	if (k < -4096) k = -4096;
-	// The operands every in-domain call site produces (|code| <= 2^31, |m_a| < 2^31,
-	// 0 < r_t <= 2^32, 33 <= k <= 94) keep the composite inside 64-bit words: with
-	// P = |code|*|m_a|*r_t = A*2^32 + b the rounded quotient floor((P + 2^(k-1)) / 2^k) is
-	// floor((A + 2^(k-33)) / 2^(k-32)). Anything else takes the general 128-bit route.
-	if (k >= 33 && k <= 94 && ac <= ((uint64_t)1 << 31) && am < ((uint64_t)1 << 31) && r_t > 0 &&
-	    (uint64_t)r_t <= ((uint64_t)1 << 32)) {
-		const uint64_t p = am * (uint64_t)r_t;                                        // < 2^63
-		const uint64_t a = ac * (p >> 32) + ((ac * (p & 0xFFFFFFFFull)) >> 32);       // floor(P / 2^32)
-		const uint64_t qm = (a + ((uint64_t)1 << (k - 33))) >> (k - 32);
-		if (saturated) *saturated = qm > 127;
-		if (exceeded_int64) *exceeded_int64 = false;
-		return neg ? -(int64_t)qm : (int64_t)qm;
-	}
 	bool over_clamp, over_i64;
 	int64_t raw;
 	if (k >= 0) {
@@ -498,6 +539,29 @@ SSLM_HD int64_t landing_rescale(int64_t code, int64_t m_a, int64_t r_t, int64_t 
 	if (saturated) *saturated = over_clamp || raw < -127 || raw > 127;
 	if (exceeded_int64) *exceeded_int64 = over_i64;
 	return raw;
+}
+SSLM_HD int64_t landing_rescale(int64_t code, int64_t m_a, int64_t r_t, int64_t e_a, int64_t e_t,
+                                bool* saturated, bool* exceeded_int64) {
+	const bool neg = (code < 0) != (m_a < 0);
+	uint64_t ac = code < 0 ? (~(uint64_t)code + 1u) : (uint64_t)code;
+	uint64_t am = m_a < 0 ? (~(uint64_t)m_a + 1u) : (uint64_t)m_a;
+	int64_t k = sat_sub64(62, sat_sub64(e_a, e_t));
+	if (k > 4096) k = 4096;
+	if (k < -4096) k = -4096;
+	// The operands every in-domain call site produces (|code| <= 2^31, |m_a| < 2^31,
+	// 0 < r_t <= 2^32, 33 <= k <= 94) keep the composite inside 64-bit words: with
+	// P = |code|*|m_a|*r_t = A*2^32 + b the rounded quotient floor((P + 2^(k-1)) / 2^k) is
+	// floor((A + 2^(k-33)) / 2^(k-32)). Anything else takes the general 128-bit route.
+	if (k >= 33 && k <= 94 && ac <= ((uint64_t)1 << 31) && am < ((uint64_t)1 << 31) && r_t > 0 &&
+	    (uint64_t)r_t <= ((uint64_t)1 << 32)) {
+		const uint64_t p = am * (uint64_t)r_t;                                        // < 2^63
+		const uint64_t a = ac * (p >> 32) + ((ac * (p & 0xFFFFFFFFull)) >> 32);       // floor(P / 2^32)
+		const uint64_t qm = (a + ((uint64_t)1 << (k - 33))) >> (k - 32);
+		if (saturated) *saturated = qm > 127;
+		if (exceeded_int64) *exceeded_int64 = false;
+		return neg ? -(int64_t)qm : (int64_t)qm;
+	}
+	return landing_rescale_general(code, m_a, r_t, k, saturated, exceeded_int64);
 }
 // RopeApplyPair + ClampRopeCode (src/intmath.cpp:782-792, forward_sites.cpp:655-661, :750-758)
 SSLM_HD void rope_pair_clamped(int32_t x, int32_t y, int32_t c, int32_t s, int8_t* ox, int8_t* oy) {
@@ -535,7 +599,7 @@ SSLM_HD bool silu_scale_in_domain(Scale g) {
 struct IExpConsts { int64_t q_ln2, q_b, q_c; };
 // IExpScaleConstants with the production coefficients, all formats 30
 // (src/intmath.cpp:702-778). 0 ok, else out of domain.
-SSLM_HD int iexp_scale_constants(int64_t m, int64_t e, IExpConsts* out) {
+SSLM_HD_OUTLINE int iexp_scale_constants(int64_t m, int64_t e, IExpConsts* out) {
 	int64_t sh_l = sat_add64(92, e);
 	int64_t sh_c = sat_add64(154, sat_add64(e, e));
 	int64_t mn = sh_l < sh_c ? sh_l : sh_c;
@@ -558,7 +622,7 @@ SSLM_HD int iexp_scale_constants(int64_t m, int64_t e, IExpConsts* out) {
 // largest row peak the Q15 normalisation can carry (checked_chain_funnel.h:563)
 #define SSLM_SOFTMAX_MAX_SAFE (((int64_t)1 << 62) >> 15)
 // CheckSoftmaxRowWidthDomain (src/forward/checked_chain_funnel.cpp:520-583)
-SSLM_HD bool softmax_width_in_domain(int64_t q_b, int64_t q_c, uint64_t width, int64_t* peak) {
+SSLM_HD_OUTLINE bool softmax_width_in_domain(int64_t q_b, int64_t q_c, uint64_t width, int64_t* peak) {
 	if (q_c < 0 || width == 0) return false;
 	U128 m = uadd(smul64(q_b, q_b), U128{(uint64_t)q_c, 0});
 	if (m.hi != 0 || m.lo > (uint64_t)SSLM_SOFTMAX_MAX_SAFE) return false;

@@ -87,6 +87,7 @@ __device__ __forceinline__ int64_t load_wide(const RowBatch& b, int row, int col
 __device__ __forceinline__ void stage16(void* dst, const void* src, int bytes) {
 	const char* s = (const char*)src;
 	const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+#pragma unroll 1
 	for (int i = threadIdx.x * 16; i < bytes; i += blockDim.x * 16)
 		asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + i), "l"(s + i) : "memory");
 }
@@ -130,10 +131,12 @@ __device__ __forceinline__ bool row_refused(const Red& red) { return red.w[kRedM
 //
 // block_code is the part after the row maximum is known to every thread (the caller's
 // reduction barrier must also have made w[] visible); block_funnel takes the maximum itself.
-template <typename WT>
-__device__ int32_t block_code(const WT* w, int n, unsigned long long mx, const Scale* incoming, int n_incoming,
-                              Scale site, int8_t* out_g, int8_t* out_s, Scale* out_scale) {
-	const FunnelParams fp = funnel_params(mx, incoming, n_incoming, site);
+// `fold` is the scale fold of the site, derived ahead of the maximum (funnel_prefold).
+// These building blocks are out of line on purpose: the residual and norm kernels share one
+// copy of each, so the second kernel of a layer finds them in the instruction cache.
+__device__ int32_t block_code(const int64_t* w, int n, unsigned long long mx, const FunnelFold& fold,
+                                           int8_t* out_g, int8_t* out_s, Scale* out_scale) {
+	const FunnelParams fp = funnel_finish(mx, fold);
 	if (fp.status != kOk) return fp.status;
 	const Coder cd = make_coder(fp.r, fp.s);
 	if ((n & 3) == 0) {
@@ -146,6 +149,7 @@ __device__ int32_t block_code(const WT* w, int n, unsigned long long mx, const S
 			if (out_s) ((uint32_t*)out_s)[i] = pk;
 		}
 	} else {
+#pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) {
 			const int8_t c = code_of(w[i], cd);
 			if (out_g) out_g[i] = c;
@@ -155,16 +159,17 @@ __device__ int32_t block_code(const WT* w, int n, unsigned long long mx, const S
 	if (threadIdx.x == 0 && out_scale) *out_scale = fp.out;
 	return kOk;
 }
-template <typename WT>
-__device__ int32_t block_funnel(const WT* w, int n, const Scale* incoming, int n_incoming, Scale site,
+__device__ int32_t block_funnel(const int64_t* w, int n, const Scale* incoming, int n_incoming, Scale site,
                                 int8_t* out_g, int8_t* out_s, Scale* out_scale, Red& red) {
+	const FunnelFold fold = funnel_prefold(incoming, n_incoming, site);
 	unsigned long long mx = 0;
+#pragma unroll 1
 	for (int i = threadIdx.x; i < n; i += blockDim.x) {
-		unsigned long long a = abs_u64((int64_t)w[i]);
+		unsigned long long a = abs_u64(w[i]);
 		mx = a > mx ? a : mx;
 	}
 	mx = block_max_u64(mx, red);
-	return block_code<WT>(w, n, mx, incoming, n_incoming, site, out_g, out_s, out_scale);
+	return block_code(w, n, mx, fold, out_g, out_s, out_scale);
 }
 
 // RmsNormSite (src/forward/forward_sites.cpp:410-459) on codes h[n] (global or shared):
@@ -184,6 +189,7 @@ __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Sca
 			ss += v0 * v0 + v1 * v1 + v2 * v2 + v3 * v3;
 		}
 	} else {
+#pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) {
 			const int v = h[i];
 			ss += v * v;
@@ -212,6 +218,7 @@ __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Sca
 			*(longlong2*)&wide[4 * i + 2] = make_longlong2(v[2], v[3]);
 		}
 	} else {
+#pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) {
 			const int64_t v = lut[(int)h[i] + 127] * (int64_t)gain[i];
 			wide[i] = v;
@@ -220,7 +227,7 @@ __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Sca
 		}
 	}
 	mx = block_max_u64(mx, red);   // its barrier also publishes wide[]
-	return block_code<int64_t>(wide, n, mx, nullptr, 0, site, out_g, nullptr, out_scale);
+	return block_code(wide, n, mx, funnel_prefold(nullptr, 0, site), out_g, nullptr, out_scale);
 }
 
 __device__ __forceinline__ void set_status(const RowBatch& b, int row, int32_t st) {
@@ -249,13 +256,15 @@ k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource*
 	int32_t st = kOk;
 	const RowSource s = src[r];
 	if (s.hidden != nullptr) {
+#pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = s.hidden[i];
 		if (threadIdx.x == 0) b.xs[r] = *s.scale;
 	} else {
 		const int8_t* e = embed + (size_t)b.rows[r].token * n;
+#pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) wide[i] = e[i];
 		__syncthreads();
-		st = block_funnel<int64_t>(wide, n, nullptr, 0, c_embed, x, nullptr, &b.xs[r], red);
+		st = block_funnel(wide, n, nullptr, 0, c_embed, x, nullptr, &b.xs[r], red);
 	}
 	__syncthreads();
 	if (st == kOk && layer != nullptr) {
@@ -313,6 +322,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	const int32_t* sin_row = vec ? s_sin : rope_sin + (size_t)pos * half;
 	const int page = b.rows[r].pages[pos / kPageTokens];
 	const int slot = pos % kPageTokens;
+	const FunnelFold fold_q = funnel_prefold(&ns, 1, c_q);
 	pdl_wait();
 	pdl_release();
 	if (vec) stage16(sw, wide_row32(b, r), d.qkv_rows * 4);
@@ -351,6 +361,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		// the row maximum the GEMM reduced does not include the bias: take it here
 		unsigned long long lmx = 0;
 		int bad = 0;
+#pragma unroll 1
 		for (int i = threadIdx.x; i < H; i += blockDim.x) {
 			bool ok;
 			const unsigned long long a = abs_u64(biased(wv(i), lw.b_q, i, &ok));
@@ -364,7 +375,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		}
 		mxq = block_max_u64(lmx, red);
 	}
-	const FunnelParams fp = funnel_params(mxq, &ns, 1, c_q);
+	const FunnelParams fp = funnel_finish(mxq, fold_q);
 	if (fp.status != kOk) {
 		set_status(b, r, fp.status);
 		return;
@@ -404,6 +415,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	if ((int)threadIdx.x < q_threads) {
 		const Coder cd = make_coder(fp.r, fp.s);
 		if (lw.b_q != nullptr) {
+#pragma unroll 1
 			for (int i = threadIdx.x; i < H; i += q_threads) {
 				bool ok;
 				sq[i] = code_of(biased(wv(i), lw.b_q, i, &ok), cd);
@@ -418,6 +430,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 				((uint32_t*)sq)[i] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
 			}
 		} else {
+#pragma unroll 1
 			for (int i = threadIdx.x; i < H; i += q_threads) sq[i] = code_of(wv(i), cd);
 		}
 	}
@@ -429,6 +442,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	// K/V landing
 	long long sat = 0;
 	int kv_bad = 0;
+#pragma unroll 1
 	for (int i = threadIdx.x; i < d.kv_hidden; i += blockDim.x) {
 		const int h = i / hd, dd = i - h * hd;
 		bool s1, s2;
@@ -486,6 +500,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 			*(uint32_t*)kdst = rope_word(((const uint32_t*)sk)[w], dd / 2);
 		}
 	} else {
+#pragma unroll 1
 	for (int p = threadIdx.x; p < H / 2; p += blockDim.x) {
 		const int pi = p % half;
 		const int32_t c = cos_row[pi], s = sin_row[pi];
@@ -494,6 +509,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		qrot[2 * p] = ox;
 		qrot[2 * p + 1] = oy;
 	}
+#pragma unroll 1
 	for (int p = threadIdx.x; p < d.kv_hidden / 2; p += blockDim.x) {
 		const int h = (2 * p) / hd, dd = 2 * p - h * hd, pi = dd / 2;
 		const int32_t c = cos_row[pi], s = sin_row[pi];
@@ -526,7 +542,7 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 	int32_t* sw = (int32_t*)(smem + kRedBytes);
 	const int r = blockIdx.x, n = d.hidden;
 	const bool vec = (n & 3) == 0;
-	const Scale c_ctx = layer->c_ctx;
+	const FunnelFold fold_ctx = funnel_prefold(nullptr, 0, layer->c_ctx);
 	pdl_wait();
 	pdl_release();
 	if (vec) stage16(sw, b.ctxw + (size_t)r * n, n * 4);
@@ -535,7 +551,7 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 	__syncthreads();
 	const unsigned long long mx = red.w[kRedMisc];
 	if (row_refused(red)) return;
-	const FunnelParams fp = funnel_params(mx, nullptr, 0, c_ctx);
+	const FunnelParams fp = funnel_finish(mx, fold_ctx);
 	if (fp.status != kOk) {
 		set_status(b, r, fp.status);
 		return;
@@ -553,6 +569,7 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 		}
 	} else {
 		const int32_t* w = b.ctxw + (size_t)r * n;
+#pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = code_of(w[i], cd);
 	}
 	if (threadIdx.x == 0) b.cs[r] = fp.out;
@@ -560,11 +577,12 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 
 // Residual reconciliation (ResidualReconcileSite, forward_sites.cpp:871-989) staged in
 // shared memory: wide_i = LandingRescale(branch_i, S[branch], Recip(S[stream].m), ...) + stream_i.
+// `fold` = funnel_prefold(&ss, 1, site constant), which the caller derives ahead of its data.
 __device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t* stream, Scale ss, int n,
-                                  Scale site, int64_t* wide, int8_t* out_g, int8_t* out_s,
-                                  Scale* out_scale, int64_t* lut, Red& red) {
+                                               int64_t r_h, const FunnelFold& fold, int64_t* wide, int8_t* out_g,
+                                               int8_t* out_s, Scale* out_scale, int64_t* lut, Red& red) {
+	// r_h = Recip(S[stream].m), also derived by the caller ahead of its data
 	if (!fits_i32(ss.m)) return kCarriedScaleMantissaOutOfDomain;
-	const int64_t r_h = dyn_recip(ss.m);
 	// the rescaled branch value depends only on the branch code: one LandingRescale per code value.
 	// lex marks the codes whose rescaled magnitude left int64 (the site refuses a row that uses one).
 	uint8_t* lex = (uint8_t*)(lut + 256);
@@ -593,6 +611,7 @@ __device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t
 			*(longlong2*)&wide[4 * i + 2] = make_longlong2(v[2], v[3]);
 		}
 	} else {
+#pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) {
 			const int c = (int)branch_s[i] + 127;
 			if (lex[c]) {
@@ -608,7 +627,7 @@ __device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t
 	}
 	mx = block_max_u64(mx, red);   // its barrier also publishes wide[]
 	if (mx == ~0ull) return kResidualMagnitudeOutOfDomain;
-	return block_code<int64_t>(wide, n, mx, &ss, 1, site, out_g, out_s, out_scale);
+	return block_code(wide, n, mx, fold, out_g, out_s, out_scale);
 }
 
 // o-projection funnel -> attention residual -> MLP RMSNorm (forward_sites.cpp:1906-1937)
@@ -634,6 +653,11 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	}
 	const Scale cs = b.cs[r], xs = b.xs[r];
 	const Scale c_o = lw.c_o, c_res = lw.c_attn_res, c_norm = lw.c_mlp_norm;
+	// ... and every scalar that needs only those: the scale folds of both funnels and the
+	// stream scale's reciprocal
+	const FunnelFold fold_o = funnel_prefold(&cs, 1, c_o);
+	const FunnelFold fold_res = funnel_prefold(&xs, 1, c_res);
+	const int64_t r_h = dyn_recip(xs.m);
 	pdl_wait();
 	pdl_release();
 	if (vec) stage16(wraw, wide_row32(b, r), n * 4);
@@ -642,17 +666,18 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	__syncthreads();
 	const unsigned long long mx = red.w[kRedMisc];
 	if (row_refused(red)) return;
-	const FunnelParams fp = funnel_params(mx, &cs, 1, c_o);
+	const FunnelParams fp = funnel_finish(mx, fold_o);
 	int32_t st = fp.status;
 	if (st == kOk) {
 		const Coder cd = make_coder(fp.r, fp.s);
 		if (vec) {
 			code_words(wraw, n >> 2, cd, so);
 		} else {
+#pragma unroll 1
 			for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = code_of(load_wide(b, r, i), cd);
 		}
 		__syncthreads();
-		st = block_residual(so, fp.out, vec ? sx : b.x + (size_t)r * n, xs, n, c_res, wide,
+		st = block_residual(so, fp.out, vec ? sx : b.x + (size_t)r * n, xs, n, r_h, fold_res, wide,
 		                    b.a + (size_t)r * n, sa, &b.as[r], lut, red);
 	}
 	if (st == kOk) {
@@ -688,6 +713,9 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	const Scale c_down = lw.c_down, c_res = lw.c_mlp_res;
 	Scale c_norm = Scale{0, 0};
 	if (next_layer != nullptr) c_norm = next_layer->c_attn_norm;
+	const FunnelFold fold_down = funnel_prefold(&as, 1, c_down);
+	const FunnelFold fold_res = funnel_prefold(&rs, 1, c_res);
+	const int64_t r_h = dyn_recip(rs.m);
 	pdl_wait();
 	pdl_release();
 	if (vec) stage16(wraw, wide_row32(b, r), n * 4);
@@ -696,17 +724,18 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	__syncthreads();
 	const unsigned long long mx = red.w[kRedMisc];
 	if (row_refused(red)) return;
-	const FunnelParams fp = funnel_params(mx, &as, 1, c_down);
+	const FunnelParams fp = funnel_finish(mx, fold_down);
 	int32_t st = fp.status;
 	if (st == kOk) {
 		const Coder cd = make_coder(fp.r, fp.s);
 		if (vec) {
 			code_words(wraw, n >> 2, cd, sd);
 		} else {
+#pragma unroll 1
 			for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = code_of(load_wide(b, r, i), cd);
 		}
 		__syncthreads();
-		st = block_residual(sd, fp.out, vec ? sa : b.a + (size_t)r * n, rs, n, c_res, wide,
+		st = block_residual(sd, fp.out, vec ? sa : b.a + (size_t)r * n, rs, n, r_h, fold_res, wide,
 		                    b.x + (size_t)r * n, sx, &b.xs[r], lut, red);
 	}
 	if (st == kOk && next_layer != nullptr) {
@@ -723,7 +752,7 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 template <bool NARROW>
 __device__ __forceinline__ int code_sel(int32_t x, const Coder& c) {
 	if (NARROW) return code_narrow(x < 0 ? 0u - (uint32_t)x : (uint32_t)x, x < 0, c);
-	return (int)requant_code((int64_t)x, c.r, c.s);
+	return (int)requant_code_general((int64_t)x, c.r, c.s);
 }
 // wide[] holds the gate row on entry and g * sigmoid(g) * u on exit; returns this thread's
 // largest product magnitude
@@ -776,6 +805,7 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	const LayerDev& lw = *layer;
 	const Scale ns = b.ns[r];
 	const Scale c_gate = lw.c_gate, c_up = lw.c_up, c_act = lw.c_act;
+	const FunnelFold fold_g = funnel_prefold(&ns, 1, c_gate), fold_u = funnel_prefold(&ns, 1, c_up);
 	pdl_wait();
 	pdl_release();
 	if (vec) {
@@ -791,8 +821,8 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 		stage_wait();
 		return;
 	}
-	const FunnelParams fg = funnel_params(mxg, &ns, 1, c_gate);
-	const FunnelParams fu = funnel_params(mxu, &ns, 1, c_up);
+	const FunnelParams fg = funnel_finish(mxg, fold_g);
+	const FunnelParams fu = funnel_finish(mxu, fold_u);
 	int32_t st = fg.status != kOk ? fg.status : fu.status;
 	if (st == kOk && !silu_scale_in_domain(fg.out)) st = kSiluScaleOutOfDomain;
 	if (st != kOk) {
@@ -811,12 +841,15 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	__syncthreads();
 	// products g * sigmoid(g) * u, |.| <= 127 * 2^15 * 127 < 2^29, left in shared memory
 	// with their running maximum so that the funnel below needs no second pass for it
+	const Scale inc[2] = {fg.out, fu.out};
+	const FunnelFold fold_act = funnel_prefold(inc, 2, c_act);   // ahead of the maximum it will meet
 	uint32_t lmax = 0;
 	if (vec) {
 		const Coder cg = make_coder(fg.r, fg.s), cu = make_coder(fu.r, fu.s);
 		lmax = (cg.narrow && cu.narrow) ? act_products<true>(wide, urow, gsil, n >> 2, cg, cu)
 		                                : act_products<false>(wide, urow, gsil, n >> 2, cg, cu);
 	} else {
+#pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) {
 			const int g = requant_code(load_wide(b, r, i), fg.r, fg.s);
 			const int u = requant_code(load_wide(b, r, n + i), fu.r, fu.s);
@@ -827,8 +860,7 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 		}
 	}
 	const unsigned long long mx = block_max_u64((unsigned long long)lmax, red);
-	const Scale inc[2] = {fg.out, fu.out};
-	const FunnelParams fp = funnel_params(mx, inc, 2, c_act);
+	const FunnelParams fp = funnel_finish(mx, fold_act);
 	if (fp.status != kOk) {
 		set_status(b, r, fp.status);
 		return;
@@ -839,6 +871,7 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 		if (ca.narrow) code_row4<true>(wide, n >> 2, ca, out);
 		else code_row4<false>(wide, n >> 2, ca, out);
 	} else {
+#pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = requant_code((int64_t)wide[i], fp.r, fp.s);
 	}
 	if (threadIdx.x == 0) b.acts[r] = fp.out;
@@ -853,6 +886,7 @@ k_scatter(RowBatch b, Dims d, const RowSink* sink) {
 	const RowSink s = sink[r];
 	if (s.hidden == nullptr || b.status[r] != 0) return;
 	const int8_t* x = b.x + (size_t)r * n;
+#pragma unroll 1
 	for (int i = threadIdx.x; i < n; i += blockDim.x) s.hidden[i] = x[i];
 	if (threadIdx.x == 0) *s.scale = b.xs[r];
 }

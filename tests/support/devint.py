@@ -21,6 +21,7 @@ def lib():
     sig = {
         "dev_srdhm": (i32, [i32, i32]), "dev_rdivpot32": (i32, [i32, C.c_int]), "dev_rdivpot64": (i64, [i64, C.c_int]),
         "dev_fold": (i32, [i32] * 4), "dev_amp_fold": (i32, [i32] * 4),
+        "dev_fold_epilogue": (i32, [i32] * 4 + [PI, C.POINTER(C.c_uint32)]),
         "dev_normalize_scale": (None, [i64, P64, PI]), "dev_dyn_recip": (i64, [i64]),
         "dev_requant_code": (C.c_int8, [i64, i64, C.c_int]),
         "dev_code_of64": (C.c_int8, [i64, i64, C.c_int]), "dev_code_of32": (C.c_int8, [i32, i64, C.c_int]),

@@ -12,6 +12,13 @@ int32_t dev_amp_fold(int32_t a, int32_t id, int32_t m, int32_t s) { return amp_f
 void dev_normalize_scale(int64_t d, int64_t* dn, int* s) { normalize_scale(d, dn, s); }
 int64_t dev_dyn_recip(int64_t dn) { return dyn_recip(dn); }
 int8_t dev_requant_code(int64_t x, int64_t r, int s) { return requant_code(x, r, s); }
+// the epilogue's fold: the plain form where it applies, fold() elsewhere; -1 in *plain when not plain
+int32_t dev_fold_epilogue(int32_t acc, int32_t identity, int32_t mult, int32_t shift, int* plain, uint32_t* mag) {
+	*plain = fold_is_plain(identity, mult, shift) ? 1 : 0;
+	*mag = 0;
+	if (!*plain) return fold(acc, identity, mult, shift);
+	return fold_plain(acc, mult, shift, shift ? (uint32_t)1 << (shift - 1) : 0u, mag);
+}
 int8_t dev_code_of64(int64_t x, int64_t r, int s) { return code_of(x, make_coder(r, s)); }
 int8_t dev_code_of32(int32_t x, int64_t r, int s) { return code_of(x, make_coder(r, s)); }
 void dev_combine(int64_t am, int64_t ae, int64_t bm, int64_t be, int64_t* om, int64_t* oe) {

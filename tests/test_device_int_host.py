@@ -113,6 +113,38 @@ def test_folds_and_scale_algebra(port):
         assert (om.value, oe.value) == (c.m, c.e)
 
 
+def test_epilogue_fold_equals_the_two_step_fold(port):
+    # the GEMM epilogue's one-rounding form against ApplyWeightScaleFold: ties at every shift,
+    # both signs, the int32 edges, and the operands that must stay on the two-step form
+    d = devint.lib()
+    rnd = random.Random(12)
+    lo, hi = -(1 << 31), (1 << 31) - 1
+    plain_seen = other_seen = 0
+    for i in range(200000):
+        sh = rnd.randrange(0, 32)
+        mult = rnd.choice([rnd.randrange(1 << 30, 1 << 31), ri(rnd, 31), lo, hi, 1 << 30, -(1 << 30), 0, 1, -1])
+        mult = max(lo, min(hi, mult))
+        acc = rnd.choice([ri(rnd, 31), ri(rnd, 20), ri(rnd, 8), lo, hi, lo + 1, 0])
+        acc = max(lo, min(hi, acc))
+        if i % 3 == 0 and mult not in (0,):
+            # an accumulator whose doubled high product lands next to a rounding tie of the shift
+            k = rnd.randrange(-(1 << 20), 1 << 20)
+            t = (2 * k + 1) << sh >> 1
+            acc = max(lo, min(hi, (t << 31) // mult + rnd.choice([-1, 0, 1])))
+        idn = int(i % 17 == 0)
+        plain, mag = C.c_int(), C.c_uint32()
+        got = d.dev_fold_epilogue(acc, idn, mult, sh, C.byref(plain), C.byref(mag))
+        want = port.osc_fold(acc, idn, mult, sh)
+        assert got == want, (acc, idn, mult, sh)
+        if plain.value:
+            plain_seen += 1
+            assert mag.value == abs(want)
+        else:
+            other_seen += 1
+            assert idn or mult == lo
+    assert plain_seen > 100000 and other_seen > 1000
+
+
 def test_bias_reconcile(port):
     d = devint.lib()
     rnd = random.Random(6)

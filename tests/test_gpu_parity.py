@@ -280,6 +280,33 @@ def test_linear_layer_sweep(gpu_lib, K, N, M, use_tc):
     assert (got[2] == want[2]).all()
 
 
+@pytest.mark.parametrize("K,N,M", [(1536, 512, 256), (256, 384, 40), (1536, 300, 130)])
+def test_linear_fold_forms(gpu_lib, K, N, M):
+    """Tiles whose columns all take the epilogue's one-rounding fold (every shift 0..31, multipliers of
+    both signs and small magnitude), and tiles where a single identity / INT32_MIN-multiplier column
+    sends the whole tile to the two-step fold."""
+    rng = np.random.default_rng(K + N + M)
+    x = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    w = rng.integers(-127, 128, (N, K)).astype(np.int8)
+    fold = np.zeros((N, 3), dtype=np.int32)
+    fold[:, 1] = rng.integers(1 << 30, 1 << 31, N)
+    fold[1::3, 1] = -fold[1::3, 1]
+    fold[2::11, 1] = rng.integers(-(1 << 16), 1 << 16, fold[2::11, 1].size)
+    fold[:, 2] = np.arange(N) % 32
+    if N > 300:                      # the second half of the columns: one odd column per 64
+        fold[N // 2 + 5::128, 0] = 1
+        fold[N // 2 + 70::128, 1] = -(1 << 31)
+    in_scales = np.stack([rng.integers(1 << 30, 1 << 31, M), np.full(M, -37)], axis=1).astype(np.int64)
+    site = (1090717716, -44)
+    want = oracle_linear(x, w, fold, in_scales, site)
+    for use_tc in (0, 1):
+        got = gpu_linear(gpu_lib, x, w, fold, in_scales, site, use_tc)
+        assert (got[3] == want[3]).all()
+        assert (got[0].astype(np.int64) == want[0]).all()
+        assert (got[1] == want[1]).all()
+        assert (got[2] == want[2]).all()
+
+
 def test_linear_layer_extremes(gpu_lib):
     """All-(-127) x all-(-128) rows at the largest K; all-zero rows; identity fold overflow to the funnel's reject."""
     K, N, M = 8960, 40, 3
