@@ -91,6 +91,13 @@ __device__ __forceinline__ void load_row_words(const int8_t* row, int c, uint32_
 	if constexpr (HD == 32) {
 		const int2 x = *(const int2*)(row + c * 8);
 		w[0] = (uint32_t)x.x; w[1] = (uint32_t)x.y;
+	} else if constexpr (HD == 128) {
+		// one 32-byte load per lane: the four lanes of a position cover its 128-byte row, and a
+		// warp's load covers eight whole lines (rows are 128-byte aligned in the pages and in q)
+		asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+		             : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+		             : "l"(row + c * 32)
+		             : "memory");
 	} else {
 		const int4 x = *(const int4*)(row + c * 16);
 		w[0] = (uint32_t)x.x; w[1] = (uint32_t)x.y; w[2] = (uint32_t)x.z; w[3] = (uint32_t)x.w;

@@ -124,6 +124,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 32-byte store (dst 32-byte aligned)
+__device__ __forceinline__ void st_global_v8(int32_t* dst, const int (&v)[8]) {
+	asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+	             "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+	             : "memory");
+}
+
 // One 32-column chunk of one output row: fold, LoRA delta, store, row max / argmax key.
 // sfold: this tile's fold words in shared memory, {multiplier, shift, rounding half, identity}
 // per column (or nullptr: no fold), indexed by column offset inside the tile.
@@ -307,6 +314,7 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 		const bool vec_ok = !a.out64 && (a.out_ld & 3) == 0 && (((uintptr_t)a.out) & 15) == 0;
 		// straight-line path: int32 rows, fold present, no adapters, not the head
 		const bool fast_ok = vec_ok && a.fold != nullptr && a.rows == nullptr && a.best == nullptr;
+		const bool wide_ok = (a.out_ld & 7) == 0 && (((uintptr_t)a.out) & 31) == 0;   // 32-byte stores line up
 		uint32_t tc = 0;
 		for (int w = blockIdx.x; w < items; w += gridDim.x, ++tc) {
 			const uint32_t as = tc & 1u;
@@ -465,16 +473,23 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 							uint32_t mx = 0;
 							int32_t* dst = (int32_t*)a.out + (size_t)row * a.out_ld + nb;
 #pragma unroll
-							for (int j4 = 0; j4 < 32; j4 += 4) {
-								int v[4];
+							for (int j8 = 0; j8 < 32; j8 += 8) {
+								int v[8];
 #pragma unroll
-								for (int jj = 0; jj < 4; ++jj) {
-									const int4 f = sf[c0 + j4 + jj];
+								for (int jj = 0; jj < 8; ++jj) {
+									const int4 f = sf[c0 + j8 + jj];
 									uint32_t mag;
-									v[jj] = fold_plain((int32_t)r[j4 + jj], f.x, f.y, (uint32_t)f.z, &mag);
+									v[jj] = fold_plain((int32_t)r[j8 + jj], f.x, f.y, (uint32_t)f.z, &mag);
 									mx = mag > mx ? mag : mx;
 								}
-								*(int4*)(dst + j4) = make_int4(v[0], v[1], v[2], v[3]);
+								// a thread owns a row, so a warp's store touches 32 different lines: the
+								// 32-byte form halves the number of requests the row's 128 bytes take
+								if (wide_ok) {
+									st_global_v8(dst + j8, v);
+								} else {
+									*(int4*)(dst + j8) = make_int4(v[0], v[1], v[2], v[3]);
+									*(int4*)(dst + j8 + 4) = make_int4(v[4], v[5], v[6], v[7]);
+								}
 							}
 							if (seg == 0) lmax[0] = mx > lmax[0] ? mx : lmax[0];
 							else if (seg == 1) lmax[1] = mx > lmax[1] ? mx : lmax[1];
