@@ -46,7 +46,9 @@ __device__ __forceinline__ IExpFast iexp_fast_prepare(const SoftmaxConsts& k) {
 	f.inv_ln2 = 1.0f / (float)f.ln2;
 	return f;
 }
-__device__ __forceinline__ bool iexp_fast(uint32_t dq, const IExpFast& f, int64_t* value) {
+// *parts = (z << 24) | rem with x = z * q_ln2 + rem (rem < q_ln2 < 2^24, z <= 30): the second
+// softmax pass rebuilds the element from it (iexp_from_parts) instead of dividing again.
+__device__ __forceinline__ bool iexp_fast(uint32_t dq, const IExpFast& f, int64_t* value, uint32_t* parts) {
 	const uint32_t x = dq < f.clip ? dq : f.clip;
 	int32_t z = (int32_t)((float)x * f.inv_ln2);
 	int32_t rem = (int32_t)(x - (uint32_t)z * f.ln2);
@@ -55,7 +57,12 @@ __device__ __forceinline__ bool iexp_fast(uint32_t dq, const IExpFast& f, int64_
 	const int32_t base = f.qb - rem;
 	const int64_t v = ((int64_t)base * (int64_t)base + f.qc) >> z;
 	*value = v;
+	*parts = ((uint32_t)z << 24) | (uint32_t)rem;
 	return f.peak >= 1 && v >= 0 && v <= f.peak;
+}
+__device__ __forceinline__ int64_t iexp_from_parts(uint32_t parts, const IExpFast& f) {
+	const int32_t base = f.qb - (int32_t)(parts & 0xFFFFFFu);
+	return ((int64_t)base * (int64_t)base + f.qc) >> (parts >> 24);
 }
 // floor((e << 15) / tot) for 0 <= e <= tot, tot >= 1: float estimate (within 1), exact repair
 __device__ __forceinline__ uint32_t prob_q15(int64_t e, unsigned long long tot, float rinv) {
@@ -114,9 +121,10 @@ struct AttnSmem {
 	uint8_t* pl;          // [G][wp] low byte of the Q15 probability
 	uint8_t* ph;          // [G][wp] high byte
 	unsigned long long* red;   // [8 heads][warps] partials
+	int* flag;            // [4] single values handed to the whole block
 };
 __host__ __device__ inline size_t attn_smem_bytes(int group, int wp) {
-	return (size_t)wp / 16 * 8 + (size_t)group * wp * 6 + 8 * kAttnMaxWarps * 8;
+	return (size_t)wp / 16 * 8 + (size_t)group * wp * 6 + 8 * kAttnMaxWarps * 8 + 16;
 }
 __device__ __forceinline__ AttnSmem carve(unsigned char* smem, int group, int wp) {
 	AttnSmem s;
@@ -125,8 +133,11 @@ __device__ __forceinline__ AttnSmem carve(unsigned char* smem, int group, int wp
 	s.pl = (uint8_t*)(s.sc + (size_t)group * wp);
 	s.ph = s.pl + (size_t)group * wp;
 	s.red = (unsigned long long*)(s.ph + (size_t)group * wp);
+	s.flag = (int*)(s.red + 8 * kAttnMaxWarps);
 	return s;
 }
+// ask for the line at p to be brought into L2; nothing waits for it
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 // HD = head_dim (32, 64 or 128); wp = padded width, a multiple of 64
 template <int HD>
@@ -134,25 +145,41 @@ __global__ void __launch_bounds__(2 * HD, HD == 128 ? 4 : 8)
 k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int wp) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	const int r = blockIdx.y, kvh = blockIdx.x;
-	pdl_wait();
-	pdl_release();
-	if (b.status[r] != 0) return;
 	constexpr int kAttnThreads = 2 * HD, kAttnWarps = kAttnThreads / 32;
 	const int G = d.heads / d.kv_heads;
 	const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
 	const int g = lane >> 2, c = lane & 3;
+	const AttnSmem s = carve(smem, G, wp);
+	// Ahead of the kernel that lands this step's K / V rows (it may still be running): the row
+	// descriptor and the page table were uploaded before the step's first launch, and every K / V
+	// row but the newest was written by earlier steps. So the page offsets are staged now, and
+	// the old K rows are asked into L2 while that kernel, which moves little data, finishes.
 	const int width = b.rows[r].pos + 1;
 	const int w64 = (width + 63) & ~63;
-	const AttnSmem s = carve(smem, G, wp);
-
 	const int8_t* kplane = pool.base + kv_plane_offset(d, pool, layer_index, kvh, 0);
 	const int8_t* vplane = pool.base + kv_plane_offset(d, pool, layer_index, kvh, 1);
+	const int npages = (width + kPageTokens - 1) / kPageTokens;
 	{
 		const int32_t* pages = b.rows[r].pages;
-		const int npages = (width + kPageTokens - 1) / kPageTokens;
 		for (int j = t; j < npages; j += kAttnThreads) s.pbase[j] = (int64_t)pages[j] * (kPageTokens * HD);
 	}
+	int32_t fi = 1, fm = 0, fs = 0;                // this lane's head: the context fold (weights)
+	if (g < G) {
+		const int32_t* f = layer->f_ctx + 3 * (kvh * G + g);
+		fi = f[0]; fm = f[1]; fs = f[2];
+	}
 	__syncthreads();
+	constexpr int kRowsPerLine = 128 / HD;
+	for (int pos = t * kRowsPerLine; pos < width - 1; pos += kAttnThreads * kRowsPerLine)
+		prefetch_l2(kplane + s.pbase[pos >> 4] + (pos & 15) * HD);
+	pdl_wait();
+	pdl_release();
+	// one thread reads the row's status for everybody: the block of the row's other kv head may
+	// refuse the row at any moment, and the threads here must agree on leaving
+	if (t == 0) *s.flag = __ldcg(&b.status[r]);
+	const SoftmaxConsts smc = b.smc[(size_t)r * d.kv_heads + kvh];   // wanted after the scores; asked for now
+	__syncthreads();
+	if (*s.flag != 0) return;
 
 	// ---- stage 1: scores, 8 positions per MMA group, groups dealt round-robin to the warps
 	{
@@ -185,8 +212,12 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	}
 	__syncthreads();
 
+	// the softmax below moves no data: ask for this row's V pages (16 lines each) meanwhile
+	for (int ln = t; ln < npages * (kPageTokens * HD / 128); ln += kAttnThreads)
+		prefetch_l2(vplane + s.pbase[ln / (kPageTokens * HD / 128)] + (ln % (kPageTokens * HD / 128)) * 128);
+
 	// ---- stage 2: softmax. Each thread takes 4 consecutive positions of every head.
-	const IExpFast fx = iexp_fast_prepare(b.smc[(size_t)r * d.kv_heads + kvh]);
+	const IExpFast fx = iexp_fast_prepare(smc);
 	int mx[8];
 #pragma unroll
 	for (int h = 0; h < 8; ++h) mx[h] = INT32_MIN;
@@ -206,9 +237,10 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	int* redi = (int*)s.red;
 #pragma unroll
 	for (int h = 0; h < 8; ++h) {
-#pragma unroll
-		for (int o = 16; o > 0; o >>= 1) mx[h] = max(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
-		if (lane == 0) redi[h * kAttnWarps + warp] = mx[h];
+		if (h < G) {
+			mx[h] = __reduce_max_sync(0xffffffffu, mx[h]);
+			if (lane == 0) redi[h * kAttnWarps + warp] = mx[h];
+		}
 	}
 	__syncthreads();
 #pragma unroll
@@ -230,23 +262,33 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 			if (h < G) {
 				const int4 v = *(const int4*)&s.sc[(size_t)h * wp + k4];
 				const int sv[4] = {v.x, v.y, v.z, v.w};
+				uint32_t parts[4];
 #pragma unroll
 				for (int j = 0; j < 4; ++j) {
 					int64_t e;
-					const bool ok = iexp_fast((uint32_t)mx[h] - (uint32_t)sv[j], fx, &e);
+					const bool ok = iexp_fast((uint32_t)mx[h] - (uint32_t)sv[j], fx, &e, &parts[j]);
 					if (k4 + j < width) {
 						tot[h] += ok ? (unsigned long long)e : 0ull;
 						bad |= !ok;
 					}
 				}
+				// the score has done its work: its place now holds the element's (shift, remainder),
+				// which this same thread reads back in the probability pass
+				*(int4*)&s.sc[(size_t)h * wp + k4] = make_int4((int)parts[0], (int)parts[1], (int)parts[2], (int)parts[3]);
 			}
 		}
 	}
 #pragma unroll
 	for (int h = 0; h < 8; ++h) {
-#pragma unroll
-		for (int o = 16; o > 0; o >>= 1) tot[h] += __shfl_xor_sync(0xffffffffu, tot[h], o);
-		if (lane == 0) s.red[h * kAttnWarps + warp] = tot[h];
+		if (h < G) {
+			// a thread's partial is below 2^62; three 24-bit limbs (the top one 16 bits) add up
+			// across the warp without leaving 32 bits, one warp-reduce instruction each
+			const uint32_t l0 = __reduce_add_sync(0xffffffffu, (uint32_t)tot[h] & 0xFFFFFFu);
+			const uint32_t l1 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot[h] >> 24) & 0xFFFFFFu);
+			const uint32_t l2 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot[h] >> 48));
+			if (lane == 0)
+				s.red[h * kAttnWarps + warp] = (unsigned long long)l0 + ((unsigned long long)l1 << 24) + ((unsigned long long)l2 << 48);
+		}
 	}
 	if (__syncthreads_or(bad ? 1 : 0)) {
 		// the reference refuses the row (SoftmaxKernelRefusedAfterGateAccepted)
@@ -273,8 +315,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 #pragma unroll
 				for (int j = 0; j < 4; ++j) {
 					if (k4 + j < width) {
-						int64_t e;
-						iexp_fast((uint32_t)mx[h] - (uint32_t)sv[j], fx, &e);
+						const int64_t e = iexp_from_parts((uint32_t)sv[j], fx);
 						const uint32_t p = prob_q15(e, tot[h], inv[h]);
 						lo |= (p & 0xffu) << (8 * j);
 						hi |= (p >> 8) << (8 * j);
@@ -334,7 +375,6 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	uint32_t lmax = 0;
 	if (g < G) {
 		const int head = kvh * G + g;
-		const int32_t fi = layer->f_ctx[3 * head], fm = layer->f_ctx[3 * head + 1], fs = layer->f_ctx[3 * head + 2];
 #pragma unroll
 		for (int i = 0; i < NDB; ++i) {
 			int2 o;

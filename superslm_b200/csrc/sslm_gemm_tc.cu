@@ -91,6 +91,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 	    "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
 	    ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
+// the same tile asked into L2 only: no shared memory, no barrier, nothing waits for it
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+	asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
+}
 // K-major, 128-byte-swizzled operand tile: 8-row groups are 1024 bytes apart
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 	uint64_t d = 0;
@@ -249,8 +253,19 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 	__syncthreads();
 	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 	const uint32_t tmem_base = *tmem_slot;
-	// everything above touched only this block's shared and tensor memory; from here on the
-	// kernel reads what earlier kernels wrote
+	// everything above touched only this block's shared and tensor memory. The weights are not
+	// written by any kernel either: while the previous kernel (a row kernel that moves little
+	// data) finishes, the producer warp asks for the weight tiles of this block's work items
+	// into L2, so the main loop's first loads do not start a cold trip to HBM. Only the block's
+	// first work item: that is the whole weight matrix for the layer projections, and a bounded
+	// part of the vocabulary head, which is larger than L2.
+	if (warp == 0 && (int)blockIdx.x < items) {
+		const int t = (int)blockIdx.x % tiles, ks = (int)blockIdx.x / tiles;
+		const int n0 = (t / m_groups) * BN;
+		const int kb0 = (int)((long long)ks * kblocks / splits), kb1 = (int)((long long)(ks + 1) * kblocks / splits);
+		for (int kb = kb0 + lane; kb < kb1; kb += 32) tma_prefetch_2d(&map_b, kb * BK, n0);
+	}
+	// from here on the kernel reads what earlier kernels wrote
 	pdl_wait();
 	pdl_release();
 
