@@ -120,6 +120,23 @@ def _chk(verb, st):
         raise SslmError(verb, st)
 
 
+class DecodeBatch:
+    """See Engine.batch."""
+
+    def __init__(self, eng: "Engine", seqs, layer_budget: int):
+        self.eng = eng
+        self.n = len(seqs)
+        self.arr = (_H * self.n)(*[s.handle for s in seqs])
+        self.params = SslmDecodeParams(layer_budget=layer_budget)
+        self.out = (C.c_int32 * self.n)()
+        self.tokens = np.ctypeslib.as_array(self.out)
+        self._call = eng.lib.sslm_decode_step
+        self._params_ref = C.byref(self.params)
+
+    def step(self) -> int:
+        return self._call(self.eng.model, self.arr, self.n, self._params_ref, self.eng.ws, self.out)
+
+
 class Engine:
     """model + kv pool + workspace over one library."""
 
@@ -166,6 +183,11 @@ class Engine:
         out = (C.c_int32 * n)()
         st = self.lib.sslm_decode_step(self.model, arr, n, C.byref(params), self.ws, out)
         return st, list(out)
+
+    def batch(self, seqs, layer_budget: int):
+        """A fixed batch prepared once, the way a C caller holds its handle array: step() is then
+        just the sslm_decode_step call, and `tokens` is a numpy view of the output buffer."""
+        return DecodeBatch(self, seqs, layer_budget)
 
     def close(self):
         for s in list(self.seqs):

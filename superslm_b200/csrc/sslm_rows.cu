@@ -578,9 +578,13 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 // Residual reconciliation (ResidualReconcileSite, forward_sites.cpp:871-989) staged in
 // shared memory: wide_i = LandingRescale(branch_i, S[branch], Recip(S[stream].m), ...) + stream_i.
 // `fold` = funnel_prefold(&ss, 1, site constant), which the caller derives ahead of its data.
-__device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t* stream, Scale ss, int n,
-                                               int64_t r_h, const FunnelFold& fold, int64_t* wide, int8_t* out_g,
-                                               int8_t* out_s, Scale* out_scale, int64_t* lut, Red& red) {
+// The branch is given either as codes (branch_s) or, with raw != nullptr, as the staged int32
+// projection row together with its coder: the codes are then taken on the fly, which saves the
+// separate coding pass and its barrier.
+__device__ int32_t block_residual(const int8_t* branch_s, const int32_t* raw, const Coder& raw_coder, Scale bs,
+                                  const int8_t* stream, Scale ss, int n, int64_t r_h, const FunnelFold& fold,
+                                  int64_t* wide, int8_t* out_g, int8_t* out_s, Scale* out_scale, int64_t* lut,
+                                  Red& red) {
 	// r_h = Recip(S[stream].m), also derived by the caller ahead of its data
 	if (!fits_i32(ss.m)) return kCarriedScaleMantissaOutOfDomain;
 	// the rescaled branch value depends only on the branch code: one LandingRescale per code value.
@@ -595,7 +599,26 @@ __device__ int32_t block_residual(const int8_t* branch_s, Scale bs, const int8_t
 	// one reduction carries both the row maximum and "some code's rescaled magnitude left
 	// int64": no in-range sum has magnitude 2^64 - 1, which stands for the latter
 	unsigned long long mx = 0;
-	if ((n & 3) == 0 && ((((uintptr_t)branch_s) | ((uintptr_t)stream)) & 3) == 0) {
+	if (raw != nullptr) {
+		// (the caller guarantees n % 4 == 0, raw 16-byte and stream 4-byte aligned)
+		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+			const int4 p = ((const int4*)raw)[i];
+			const uint32_t sw = ((const uint32_t*)stream)[i];
+			const int cs4[4] = {code_of(p.x, raw_coder), code_of(p.y, raw_coder), code_of(p.z, raw_coder),
+			                    code_of(p.w, raw_coder)};
+			int64_t v[4];
+#pragma unroll
+			for (int j = 0; j < 4; ++j) {
+				const int c = cs4[j] + 127;
+				const bool ex = lex[c] != 0;
+				v[j] = ex ? 0 : lut[c] + (int64_t)(int8_t)(sw >> (8 * j));
+				const unsigned long long a = ex ? ~0ull : abs_u64(v[j]);
+				mx = a > mx ? a : mx;
+			}
+			*(longlong2*)&wide[4 * i] = make_longlong2(v[0], v[1]);
+			*(longlong2*)&wide[4 * i + 2] = make_longlong2(v[2], v[3]);
+		}
+	} else if ((n & 3) == 0 && ((((uintptr_t)branch_s) | ((uintptr_t)stream)) & 3) == 0) {
 		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
 			const uint32_t bw = ((const uint32_t*)branch_s)[i], sw = ((const uint32_t*)stream)[i];
 			int64_t v[4];
@@ -670,15 +693,13 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	int32_t st = fp.status;
 	if (st == kOk) {
 		const Coder cd = make_coder(fp.r, fp.s);
-		if (vec) {
-			code_words(wraw, n >> 2, cd, so);
-		} else {
+		if (!vec) {
 #pragma unroll 1
 			for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = code_of(load_wide(b, r, i), cd);
+			__syncthreads();
 		}
-		__syncthreads();
-		st = block_residual(so, fp.out, vec ? sx : b.x + (size_t)r * n, xs, n, r_h, fold_res, wide,
-		                    b.a + (size_t)r * n, sa, &b.as[r], lut, red);
+		st = block_residual(so, vec ? wraw : nullptr, cd, fp.out, vec ? sx : b.x + (size_t)r * n, xs, n, r_h,
+		                    fold_res, wide, b.a + (size_t)r * n, sa, &b.as[r], lut, red);
 	}
 	if (st == kOk) {
 		__syncthreads();
@@ -728,15 +749,13 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	int32_t st = fp.status;
 	if (st == kOk) {
 		const Coder cd = make_coder(fp.r, fp.s);
-		if (vec) {
-			code_words(wraw, n >> 2, cd, sd);
-		} else {
+		if (!vec) {
 #pragma unroll 1
 			for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = code_of(load_wide(b, r, i), cd);
+			__syncthreads();
 		}
-		__syncthreads();
-		st = block_residual(sd, fp.out, vec ? sa : b.a + (size_t)r * n, rs, n, r_h, fold_res, wide,
-		                    b.x + (size_t)r * n, sx, &b.xs[r], lut, red);
+		st = block_residual(sd, vec ? wraw : nullptr, cd, fp.out, vec ? sa : b.a + (size_t)r * n, rs, n, r_h,
+		                    fold_res, wide, b.x + (size_t)r * n, sx, &b.xs[r], lut, red);
 	}
 	if (st == kOk && next_layer != nullptr) {
 		__syncthreads();
