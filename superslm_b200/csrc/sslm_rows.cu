@@ -132,29 +132,38 @@ __device__ __forceinline__ bool row_refused(const Red& red) { return red.w[kRedM
 // block_code is the part after the row maximum is known to every thread (the caller's
 // reduction barrier must also have made w[] visible); block_funnel takes the maximum itself.
 // `fold` is the scale fold of the site, derived ahead of the maximum (funnel_prefold).
-// These building blocks are out of line on purpose: the residual and norm kernels share one
-// copy of each, so the second kernel of a layer finds them in the instruction cache.
+// sumsq (optional): this thread's sum of squares of the codes it wrote, for the RMSNorm that
+// follows a residual site in the same kernel.
 __device__ int32_t block_code(const int64_t* w, int n, unsigned long long mx, const FunnelFold& fold,
-                                           int8_t* out_g, int8_t* out_s, Scale* out_scale) {
+                              int8_t* out_g, int8_t* out_s, Scale* out_scale, long long* sumsq = nullptr) {
 	const FunnelParams fp = funnel_finish(mx, fold);
 	if (fp.status != kOk) return fp.status;
 	const Coder cd = make_coder(fp.r, fp.s);
 	if ((n & 3) == 0) {
 		// four codes per thread and pass: word stores to global and shared memory
+		int sq = 0;
 		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
 			uint32_t pk = 0;
 #pragma unroll
-			for (int j = 0; j < 4; ++j) pk |= (uint32_t)(uint8_t)code_of(w[4 * i + j], cd) << (8 * j);
+			for (int j = 0; j < 4; ++j) {
+				const int c = code_of(w[4 * i + j], cd);
+				sq += c * c;
+				pk |= (uint32_t)(uint8_t)c << (8 * j);
+			}
 			if (out_g) ((uint32_t*)out_g)[i] = pk;
 			if (out_s) ((uint32_t*)out_s)[i] = pk;
 		}
+		if (sumsq) *sumsq = sq;
 	} else {
+		long long sq = 0;
 #pragma unroll 1
 		for (int i = threadIdx.x; i < n; i += blockDim.x) {
 			const int8_t c = code_of(w[i], cd);
+			sq += (int)c * (int)c;
 			if (out_g) out_g[i] = c;
 			if (out_s) out_s[i] = c;
 		}
+		if (sumsq) *sumsq = sq;
 	}
 	if (threadIdx.x == 0 && out_scale) *out_scale = fp.out;
 	return kOk;
@@ -175,14 +184,18 @@ __device__ int32_t block_funnel(const int64_t* w, int n, const Scale* incoming, 
 // RmsNormSite (src/forward/forward_sites.cpp:410-459) on codes h[n] (global or shared):
 // root = max(isqrt(floor((sum h^2) << 32 / n)), 1); wide_i = floor((h_i << 32) / root) * g_i;
 // funnel with no incoming scale. wide: shared int64[n].
+// ss_partial (optional): this thread's share of sum h^2, already taken by whoever wrote h.
 __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Scale site, int64_t* wide,
-                                 int8_t* out_g, Scale* out_scale, int64_t* lut, Red& red) {
+                                 int8_t* out_g, Scale* out_scale, int64_t* lut, Red& red,
+                                 const long long* ss_partial = nullptr) {
 	// four codes per word where the rows allow it: these passes are short dependent chains,
 	// and a quarter of the iterations is a quarter of the latency
 	const bool vec = (n & 3) == 0 && ((((uintptr_t)h) | ((uintptr_t)gain)) & 3) == 0;
 	const double inv_n = rcp_estimate((double)n);
 	long long ss = 0;
-	if (vec) {
+	if (ss_partial != nullptr) {
+		ss = *ss_partial;
+	} else if (vec) {
 		for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
 			const uint32_t w = ((const uint32_t*)h)[i];
 			const int v0 = (int8_t)w, v1 = (int8_t)(w >> 8), v2 = (int8_t)(w >> 16), v3 = (int8_t)(w >> 24);
@@ -584,7 +597,7 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 __device__ int32_t block_residual(const int8_t* branch_s, const int32_t* raw, const Coder& raw_coder, Scale bs,
                                   const int8_t* stream, Scale ss, int n, int64_t r_h, const FunnelFold& fold,
                                   int64_t* wide, int8_t* out_g, int8_t* out_s, Scale* out_scale, int64_t* lut,
-                                  Red& red) {
+                                  Red& red, long long* sumsq = nullptr) {
 	// r_h = Recip(S[stream].m), also derived by the caller ahead of its data
 	if (!fits_i32(ss.m)) return kCarriedScaleMantissaOutOfDomain;
 	// the rescaled branch value depends only on the branch code: one LandingRescale per code value.
@@ -650,7 +663,7 @@ __device__ int32_t block_residual(const int8_t* branch_s, const int32_t* raw, co
 	}
 	mx = block_max_u64(mx, red);   // its barrier also publishes wide[]
 	if (mx == ~0ull) return kResidualMagnitudeOutOfDomain;
-	return block_code(wide, n, mx, fold, out_g, out_s, out_scale);
+	return block_code(wide, n, mx, fold, out_g, out_s, out_scale, sumsq);
 }
 
 // o-projection funnel -> attention residual -> MLP RMSNorm (forward_sites.cpp:1906-1937)
@@ -691,6 +704,7 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	if (row_refused(red)) return;
 	const FunnelParams fp = funnel_finish(mx, fold_o);
 	int32_t st = fp.status;
+	long long ssq = 0;
 	if (st == kOk) {
 		const Coder cd = make_coder(fp.r, fp.s);
 		if (!vec) {
@@ -699,11 +713,11 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 			__syncthreads();
 		}
 		st = block_residual(so, vec ? wraw : nullptr, cd, fp.out, vec ? sx : b.x + (size_t)r * n, xs, n, r_h,
-		                    fold_res, wide, b.a + (size_t)r * n, sa, &b.as[r], lut, red);
+		                    fold_res, wide, b.a + (size_t)r * n, sa, &b.as[r], lut, red, &ssq);
 	}
 	if (st == kOk) {
-		__syncthreads();
-		st = block_rmsnorm(sa, vec ? sg : lw.g_mlp, n, c_norm, wide, b.nrm + (size_t)r * n, &b.ns[r], lut, red);
+		// (the norm's first barrier, in its sum, also separates the passes above from its own)
+		st = block_rmsnorm(sa, vec ? sg : lw.g_mlp, n, c_norm, wide, b.nrm + (size_t)r * n, &b.ns[r], lut, red, &ssq);
 	}
 	set_status(b, r, st);
 }
@@ -747,6 +761,7 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	if (row_refused(red)) return;
 	const FunnelParams fp = funnel_finish(mx, fold_down);
 	int32_t st = fp.status;
+	long long ssq = 0;
 	if (st == kOk) {
 		const Coder cd = make_coder(fp.r, fp.s);
 		if (!vec) {
@@ -755,12 +770,11 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 			__syncthreads();
 		}
 		st = block_residual(sd, vec ? wraw : nullptr, cd, fp.out, vec ? sa : b.a + (size_t)r * n, rs, n, r_h,
-		                    fold_res, wide, b.x + (size_t)r * n, sx, &b.xs[r], lut, red);
+		                    fold_res, wide, b.x + (size_t)r * n, sx, &b.xs[r], lut, red, &ssq);
 	}
 	if (st == kOk && next_layer != nullptr) {
-		__syncthreads();
 		st = block_rmsnorm(sx, vec ? sg : next_layer->g_attn, n, c_norm, wide,
-		                   b.nrm + (size_t)r * n, &b.ns[r], lut, red);
+		                   b.nrm + (size_t)r * n, &b.ns[r], lut, red, &ssq);
 	}
 	set_status(b, r, st);
 }
