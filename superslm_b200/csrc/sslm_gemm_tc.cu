@@ -668,12 +668,19 @@ bool launch_linear_tc(const LinearArgs& a, cudaStream_t st) {
 	// two accumulators per weight tile once there is more than one 128-row group -- unless the
 	// output is so small that even 128-row tiles leave SMs idle: then the smaller tile doubles
 	// the blocks and halves each block's main loop bytes and epilogue (the second read of a
-	// weight tile hits L2). Narrower weight tiles when there would otherwise be fewer tiles
-	// than SMs.
+	// weight tile hits L2). Narrower weight tiles when there would otherwise be clearly fewer tiles
+	// than SMs (below 90 % of them; SSLM_B200_TC_NARROW_PCT moves that): every tile re-reads the
+	// activation rows from L2, so halving the tile width doubles that traffic, and at 140 tiles
+	// on 148 SMs (the gate/up projection of the 1.5B shape) one wide tile per block is faster
+	// than two narrow ones even though the narrow ones overlap their epilogues.
 	const int n128 = (a.N + 127) / 128;
 	const bool two = a.M > BM && n128 * ((a.M + 127) / 128) >= sm_count();
 	const int tiles128 = ((a.N + 127) / 128) * ((a.M + (two ? 255 : 127)) / (two ? 256 : 128));
-	const bool narrow = tiles128 < sm_count();
+	static const int narrow_pct = [] {
+		const char* e = getenv("SSLM_B200_TC_NARROW_PCT");
+		return e ? atoi(e) : 90;
+	}();
+	const bool narrow = tiles128 * 100 < sm_count() * narrow_pct;
 	bool ok;
 	if (two) ok = narrow ? launch_cfg<2, 64>(a, st) : launch_cfg<2, 128>(a, st);
 	else ok = narrow ? launch_cfg<1, 64>(a, st) : launch_cfg<1, 128>(a, st);
