@@ -142,9 +142,10 @@ __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefe
 // HD = head_dim (32, 64 or 128); wp = padded width, a multiple of 64
 template <int HD>
 __global__ void __launch_bounds__(2 * HD, HD == 128 ? 4 : 8)
-k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int wp) {
+k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int wp, int reverse_rows) {
 	extern __shared__ __align__(16) unsigned char smem[];
-	const int r = blockIdx.y, kvh = blockIdx.x;
+	// blocks start in index order: with reverse_rows the last (widest) rows of a prefill chunk go first
+	const int r = reverse_rows ? (int)gridDim.y - 1 - (int)blockIdx.y : (int)blockIdx.y, kvh = blockIdx.x;
 	constexpr int kAttnThreads = 2 * HD, kAttnWarps = kAttnThreads / 32;
 	const int G = d.heads / d.kv_heads;
 	const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -395,8 +396,8 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 static int pad_width(int w) { return (w + 63) / 64 * 64; }
 template <int HD>
 static void launch_attn(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index, KvPoolDev pool,
-                        int wp, size_t sm, cudaStream_t st) {
-	launch_pdl(k_attention<HD>, dim3(d.kv_heads, b.m), dim3(2 * HD), sm, st, b, d, layer, layer_index, pool, wp);
+                        int wp, size_t sm, int reverse_rows, cudaStream_t st) {
+	launch_pdl(k_attention<HD>, dim3(d.kv_heads, b.m), dim3(2 * HD), sm, st, b, d, layer, layer_index, pool, wp, reverse_rows);
 }
 
 cudaError_t attn_configure(const Dims& d) {
@@ -417,12 +418,12 @@ cudaError_t attn_configure(const Dims& d) {
 }
 
 void launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
-                      KvPoolDev pool, int max_width, cudaStream_t st) {
+                      KvPoolDev pool, int max_width, int reverse_rows, cudaStream_t st) {
 	const int wp = pad_width(max_width);
 	const size_t sm = attn_smem_bytes(d.heads / d.kv_heads, wp);
-	if (d.head_dim == 128) launch_attn<128>(b, d, layer, layer_index, pool, wp, sm, st);
-	else if (d.head_dim == 64) launch_attn<64>(b, d, layer, layer_index, pool, wp, sm, st);
-	else launch_attn<32>(b, d, layer, layer_index, pool, wp, sm, st);
+	if (d.head_dim == 128) launch_attn<128>(b, d, layer, layer_index, pool, wp, sm, reverse_rows, st);
+	else if (d.head_dim == 64) launch_attn<64>(b, d, layer, layer_index, pool, wp, sm, reverse_rows, st);
+	else launch_attn<32>(b, d, layer, layer_index, pool, wp, sm, reverse_rows, st);
 }
 
 // ------------------------------------------------------------ canonical KV export

@@ -680,7 +680,9 @@ bool launch_linear_tc(const LinearArgs& a, cudaStream_t st) {
 		const char* e = getenv("SSLM_B200_TC_NARROW_PCT");
 		return e ? atoi(e) : 90;
 	}();
-	const bool narrow = tiles128 * 100 < sm_count() * narrow_pct;
+	// (a prefill chunk of several hundred rows has enough work per tile that the wide tile wins
+	// until the tiles are fewer than a quarter of the SMs: measured on the 1.5B projections)
+	const bool narrow = tiles128 * 100 < sm_count() * (a.M <= 2 * BM ? narrow_pct : (narrow_pct < 25 ? narrow_pct : 25));
 	bool ok;
 	if (two) ok = narrow ? launch_cfg<2, 64>(a, st) : launch_cfg<2, 128>(a, st);
 	else ok = narrow ? launch_cfg<1, 64>(a, st) : launch_cfg<1, 128>(a, st);

@@ -336,6 +336,13 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	const int page = b.rows[r].pages[pos / kPageTokens];
 	const int slot = pos % kPageTokens;
 	const FunnelFold fold_q = funnel_prefold(&ns, 1, c_q);
+	// the landing constants (weights) of the kv head this thread's first K / V element belongs to
+	int64_t k_rt0 = 0, k_et0 = 0, v_rt0 = 0, v_et0 = 0;
+	if ((int)threadIdx.x < d.kv_hidden) {
+		const int h0 = (int)threadIdx.x / hd;
+		k_rt0 = lw.k_recip[3 * h0 + 2]; k_et0 = lw.k_recip[3 * h0 + 1];
+		v_rt0 = lw.v_recip[3 * h0 + 2]; v_et0 = lw.v_recip[3 * h0 + 1];
+	}
 	pdl_wait();
 	pdl_release();
 	if (vec) stage16(sw, wide_row32(b, r), d.qkv_rows * 4);
@@ -470,10 +477,12 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 			vacc = biased(vacc, lw.b_v, i, &ok);
 			if (!ok) kv_bad = 1;
 		}
-		const int64_t kraw = landing_rescale(kacc, ns.m, lw.k_recip[3 * h + 2], ns.e,
-		                                     lw.k_recip[3 * h + 1], &s1, nullptr);
-		const int64_t vraw = landing_rescale(vacc, ns.m,
-		                                     lw.v_recip[3 * h + 2], ns.e, lw.v_recip[3 * h + 1], &s2, nullptr);
+		// this thread's first element uses the head constants it fetched ahead of the wait
+		const bool first = i == (int)threadIdx.x;
+		const int64_t k_rt = first ? k_rt0 : lw.k_recip[3 * h + 2], k_et = first ? k_et0 : lw.k_recip[3 * h + 1];
+		const int64_t v_rt = first ? v_rt0 : lw.v_recip[3 * h + 2], v_et = first ? v_et0 : lw.v_recip[3 * h + 1];
+		const int64_t kraw = landing_rescale(kacc, ns.m, k_rt, ns.e, k_et, &s1, nullptr);
+		const int64_t vraw = landing_rescale(vacc, ns.m, v_rt, ns.e, v_et, &s2, nullptr);
 		sat += (s1 ? 1 : 0) + (s2 ? 1 : 0);
 		sk[i] = (int8_t)clamp127(kraw);
 		// V pages are stored transposed ([head_dim][16 positions]) so that the attention
