@@ -8,7 +8,7 @@ tests/golden/reference_fixtures.json so that the oracle and the CUDA kernels can
 checked against them on machines where the reference tree is absent.
 
 Run where the reference is mounted:
-    python tests/golden/transcribe_reference_fixtures.py [/root/reference]
+    python tests/golden/transcribe_reference_fixtures.py [<reference root>]
 """
 from __future__ import annotations
 
