@@ -6,7 +6,7 @@
 // operand form tcgen05.mma wants, so nothing is repacked: TMA (cp.async.bulk.tensor.2d,
 // 128-byte swizzle, no multicast) streams 128-byte-wide tiles of both into a shared-memory
 // ring, one thread issues tcgen05.mma.kind::i8 (s8 x s8 -> s32, M=128, N=BN, K=32 per
-// instruction) into TMEM accumulators, and four epilogue warps read the accumulators back
+// instruction) into TMEM accumulators, and eight epilogue warps read the accumulators back
 // with tcgen05.ld, apply the per-channel fixed-point fold (ApplyWeightScaleFold,
 // src/forward/forward_sites.cpp:461-470), add the runtime LoRA delta (:1082-1102), store the
 // wide row and reduce the row maximum the requant funnel needs (integer max: order-free).
