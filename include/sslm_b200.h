@@ -241,6 +241,17 @@ SSLM_API sslm_status sslm_b200_last_call_ms(sslm_workspace ws, float* ms, uint64
 /* Process-wide counters of the tensor-core linear kernel: launches, times it declined a shape
  * (the streaming kernel ran instead) and the reason code of the last refusal. */
 SSLM_API sslm_status sslm_b200_tc_stats(uint64_t* launches, uint64_t* refusals, int32_t* last_reason);
+/* Launches of the tensor-core linear kernel per tile shape (rows x weight columns), first n of:
+ * 128 x 64, 128 x 128, 256 x 64, 256 x 128. Lets a test assert which variant served a shape. */
+SSLM_API sslm_status sslm_b200_tc_variant_counts(uint64_t* counts, int32_t n);
+
+/* The vocabulary head on host buffers: logits[m, n] = sum_k x[m,k] w[n,k] (int32, no fold), and per
+ * row the greedy token = the lowest index of the row's maximum (LogitsSite + NarrowRowChecked +
+ * ArgmaxLowestIndexTieBreak, src/forward/forward_sites.cpp:2412-2437). out_logits ([M,N], may be
+ * NULL: the kernels then keep only the running maximum, as in a decode step) and out_tokens [M].
+ * use_tensor_cores as for sslm_b200_linear. For the parity sweep of the logits form. */
+SSLM_API sslm_status sslm_b200_logits(const int8_t* x, const int8_t* w, int32_t M, int32_t N, int32_t K,
+                             int32_t use_tensor_cores, int32_t* out_logits, int32_t* out_tokens);
 
 /* Per-kernel-class device timing of later calls on `ws` (CUDA events around every launch;
  * slows the call slightly). Classes, in order: begin, linear q/k/v, q/k/v post, attention,

@@ -22,13 +22,16 @@ from superslm_b200 import artifact as A
 HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_SO = os.path.join(HERE, "liboracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libsslm_ref.so")
-REF_ROOT = os.environ.get("SSLM_REF_ROOT", "/root/reference")
+# Where the reference's sources are mounted, if anywhere: SSLM_REF_ROOT, else a directory named
+# "reference" beside this repository's checkout.
+_SIBLING = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+REF_ROOT = os.environ.get("SSLM_REF_ROOT") or (_SIBLING if os.path.isdir(os.path.join(_SIBLING, "src")) else "")
 
 
 def build(verbose: bool = False) -> None:
     """Compile the restatement, and the reference library when its sources exist."""
     targets = ["oracle"]
-    if os.path.isdir(os.path.join(REF_ROOT, "src")):
+    if REF_ROOT and os.path.isdir(os.path.join(REF_ROOT, "src")):
         targets.append("ref")
     out = subprocess.run(["make", "-C", HERE, "-j8", "REF_ROOT=" + REF_ROOT] + targets,
                          capture_output=True, text=True)
@@ -93,6 +96,7 @@ def port():
             "osc_isqrt": (i64, [i64]), "osc_floor_div": (i64, [i64, i64]),
             "osc_rope_pair": (None, [i32, i32, i32, i32, C.POINTER(i64), C.POINTER(i64)]),
             "osc_fold": (i64, [i64, i32, i32, i32]), "osc_amp_fold": (i64, [i64, i32, i32, i32]),
+            "osc_fold_matrix": (None, [p, C.c_size_t, C.c_size_t, p, p]),
             "osc_combine": (Scale, [Scale, Scale]),
             "osc_landing_rescale": (i64, [i64, i64, i64, i64, i64, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
             "osc_silu_sigmoid_q15": (i32, [p, C.c_int8, i64, C.c_int]),

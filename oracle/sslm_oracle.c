@@ -121,6 +121,13 @@ int64_t osc_fold(int64_t acc, int32_t identity, int32_t mult, int32_t shift) {
 	return (int64_t)osc_mbqm((int32_t)acc, mult, shift);
 }
 
+/* the same fold over a whole [m, n] accumulator matrix (fold triples per column), for the linear sweeps */
+void osc_fold_matrix(const int64_t* acc, size_t m, size_t n, const int32_t* fold, int64_t* out) {
+	for (size_t t = 0; t < m; ++t)
+		for (size_t j = 0; j < n; ++j)
+			out[t * n + j] = osc_fold(acc[t * n + j], fold[3 * j], fold[3 * j + 1], fold[3 * j + 2]);
+}
+
 int64_t osc_amp_fold(int64_t acc, int32_t identity, int32_t mult, int32_t exponent) {
 	if (identity != 0) return acc;
 	int32_t hi = osc_srdhm((int32_t)acc, mult);

@@ -59,6 +59,7 @@ int64_t osc_isqrt(int64_t n);                               /* src/intmath.cpp:5
 int64_t osc_floor_div(int64_t a, int64_t b);                /* src/forward/forward_sites.cpp:399-408 */
 void osc_rope_pair(int32_t x, int32_t y, int32_t c, int32_t s, int64_t* ox, int64_t* oy); /* src/intmath.cpp:782-792 */
 int64_t osc_fold(int64_t acc, int32_t identity, int32_t mult, int32_t shift);      /* forward_sites.cpp:461-470 */
+void osc_fold_matrix(const int64_t* acc, size_t m, size_t n, const int32_t* fold, int64_t* out);
 /* BiasReconcileWide with q_B = 30 (src/intmath.cpp:397-418): 1 and *out = round_half_away(b * r_a / 2^(92 + e_a))
  * when the exponent is in [0,63] and the result fits int64, else 0 */
 int osc_bias_reconcile(int64_t b, int64_t r_a, int64_t e_a, int64_t* out);

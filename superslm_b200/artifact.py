@@ -269,6 +269,12 @@ SHAPES = {
     "tiny": Shape("tiny", 128, 2, 4, 2, 32, 256, 512),
     "small": Shape("small", 256, 3, 4, 2, 64, 768, 1024),
     "mini1.5b": Shape("mini1.5b", 1536, 2, 12, 2, 128, 8960, 4096),
+    # two layers at the 0.5B and 3B widths (GQA 7:1 with head_dim 64; GQA 8:1), and four layers at
+    # the 3B widths for the adapter-swap workload: long rows at real widths that a CPU still
+    # finishes in minutes
+    "mini0.5b": Shape("mini0.5b", 896, 2, 14, 2, 64, 4864, 4096),
+    "mini3b": Shape("mini3b", 2048, 2, 16, 2, 128, 11008, 4096),
+    "3b4l": Shape("3b4l", 2048, 4, 16, 2, 128, 11008, 8192),
 }
 
 _W_RMS = 73.3  # rms of a uniform integer in [-127,127]
@@ -353,11 +359,13 @@ def synthetic_schemas(seed: int, vocab: int, count: int, states: int = 6, fanout
 
 def build_synthetic_model(shape: Shape | str, seed: int, context_cap: int,
                           shift_lo: int = 8, shift_hi: int = 20, bias_bits: int = 0,
-                          flags: int = 0, schemas: int = 0) -> bytes:
+                          flags: int = 0, schemas: int = 0, const_overrides: dict | None = None) -> bytes:
     """A loadable base artifact of the given architecture (header flags 0). bias_bits > 0 adds a
     BIA1 section: int64 q/k/v bias codes (Q30 against the projection's input scale, as the
     converter writes them for Qwen2.5's q/k/v biases), uniform in +-2^bias_bits. schemas > 0 adds
-    an SCM1 section with that many seeded decode schemas (synthetic_schemas)."""
+    an SCM1 section with that many seeded decode schemas (synthetic_schemas). const_overrides
+    replaces composition constants by name ("layer0.mlp_norm" -> (m, e)): the way tests build
+    artifacts that leave an integer-domain gate of the forward pass on purpose."""
     sh = SHAPES[shape] if isinstance(shape, str) else shape
     H, L, I, KV = sh.hidden, sh.layers, sh.inter, sh.kv_hidden
     weights: list[tuple[str, np.ndarray]] = []
@@ -415,6 +423,10 @@ def build_synthetic_model(shape: Shape | str, seed: int, context_cap: int,
                 kv_scales.append(("%s.%s_head%d" % (p, kv, h), canonical_scale(s_kh)))
                 kv_recips.append(("%s.%s_head%d" % (p, kv, h), (m_t, e_t, r_t)))
 
+    if const_overrides:
+        left = dict(const_overrides)
+        consts = [(k, tuple(left.pop(k))) if k in left else (k, v) for k, v in consts]
+        assert not left, "unknown constants: %s" % sorted(left)
     cos, sin = rope_tables(context_cap, sh.head_dim, 1e6)
     sections = [
         (SEC_CONFIG, cfg1(H, L, sh.heads, sh.kv_heads, sh.head_dim, I, sh.vocab, context_cap)),
@@ -435,9 +447,12 @@ def build_synthetic_model(shape: Shape | str, seed: int, context_cap: int,
 
 def build_synthetic_adapter(base: bytes, seed: int, rank: int = 16,
                             projections=("q_proj", "k_proj", "v_proj", "o_proj"),
-                            u_exp=(8, 9), d_exp=(8, 10), name: str = "synthetic") -> bytes:
+                            u_exp=(8, 9), d_exp=(8, 10), name: str = "synthetic",
+                            layer_d_exp: dict | None = None) -> bytes:
     """A rank-`rank` runtime-additive LoRA adapter bound to `base` (ADP1 + lora_A/B +
-    DFS1/UFS1). Layout: include/superslm/adapter_marshal.h:38-53, :266-307."""
+    DFS1/UFS1). Layout: include/superslm/adapter_marshal.h:38-53, :266-307. layer_d_exp gives
+    single layers their own delta-fold exponent range (tests use it to make one layer's delta
+    leave the funnel's domain)."""
     view = parse_artifact(base)
     cfg = view.config
     H, I, KV, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["kv_hidden"], cfg["num_hidden_layers"]
@@ -456,7 +471,8 @@ def build_synthetic_adapter(base: bytes, seed: int, rank: int = 16,
             weights.append((nm + ".lora_A", stream_int8(seed, nm + ".A", rank * k_in).reshape(rank, k_in)))
             weights.append((nm + ".lora_B", stream_int8(seed, nm + ".B", n_out * rank).reshape(n_out, rank)))
             ufs.append((nm, _fold_rows(seed, nm + ".ufs", rank, u_exp[0], u_exp[1])))
-            dfs.append((nm, _fold_rows(seed, nm + ".dfs", n_out, d_exp[0], d_exp[1])))
+            de = (layer_d_exp or {}).get(l, d_exp)
+            dfs.append((nm, _fold_rows(seed, nm + ".dfs", n_out, de[0], de[1])))
     cfg_bytes = view.sections[SEC_CONFIG]
     sections = [
         (SEC_CONFIG, bytes(cfg_bytes)),

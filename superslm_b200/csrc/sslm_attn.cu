@@ -293,7 +293,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	}
 	if (__syncthreads_or(bad ? 1 : 0)) {
 		// the reference refuses the row (SoftmaxKernelRefusedAfterGateAccepted)
-		if (t == 0) atomicCAS(&b.status[r], 0, kSoftmaxKernelRefused);
+		if (t == 0) atomicCAS(&b.status[r], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
 		return;
 	}
 	float inv[8];

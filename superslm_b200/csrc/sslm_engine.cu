@@ -34,6 +34,7 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 sslm_status map_forward_status(int32_t st) {
 	// MapForwardStatus, src/sslm_abi.cpp:1352-1370
+	st = status_code(st);      // (the device packs the failing site and layer beside the code)
 	if (st == kOk) return SSLM_OK;
 	if (st == kSoftmaxKernelRefused) return SSLM_NUMERIC_STEP_REFUSED;
 	// not a reference status: a bounded device-side wait of this implementation ran out
@@ -131,6 +132,7 @@ extern "C" sslm_status sslm_model_map(const void* data, size_t size, sslm_model*
 
 	auto fail = [&](sslm_status st) {
 		cudaFree(m->arena.base);
+		cudaFree(m->d_schema_pages);
 		delete m;
 		return st;
 	};
@@ -273,7 +275,6 @@ extern "C" sslm_status sslm_model_map(const void* data, size_t size, sslm_model*
 		for (const SchemaEntry& e : m->schemas.entries) {
 			if (!cuda_ok(cudaMemcpy(m->d_schema_pages + e.device_page0 * pb, m->schemas.pages(e), (size_t)e.states * pb,
 			                        cudaMemcpyHostToDevice))) {
-				cudaFree(m->d_schema_pages);
 				return fail(SSLM_ALLOCATION_FAILED);
 			}
 		}
@@ -390,6 +391,7 @@ size_t carve(const Dims& d, int rows, uint8_t* basep, RowBatch* b, size_t* wide_
 	b->rowmax = (unsigned long long*)take(R * 4 * 8);
 	b->smc = (SoftmaxConsts*)take(R * d.kv_heads * sizeof(SoftmaxConsts));
 	b->status = (int32_t*)take(R * 4);
+	b->done = (int32_t*)take(R * 4);
 	b->sat = (unsigned long long*)take(R * 8);
 	b->lora_u = (int8_t*)take(R * 3 * kMaxLoraRank);
 	b->best = (unsigned long long*)take(R * 8);
@@ -417,6 +419,7 @@ sslm_workspace_s* create_workspace(sslm_model_s* model, const sslm_config& cfg, 
 	ok = ok && cuda_ok(cudaMallocHost((void**)&w->h_src, rows * sizeof(RowSource)));
 	ok = ok && cuda_ok(cudaMallocHost((void**)&w->h_sink, rows * sizeof(RowSink)));
 	ok = ok && cuda_ok(cudaMallocHost((void**)&w->h_status, rows * 4));
+	ok = ok && cuda_ok(cudaMallocHost((void**)&w->h_done, rows * 4));
 	ok = ok && cuda_ok(cudaMallocHost((void**)&w->h_sat, rows * 8));
 	ok = ok && cuda_ok(cudaMallocHost((void**)&w->h_best, rows * 8));
 	ok = ok && cuda_ok(cudaMalloc((void**)&w->d_rows, rows * sizeof(RowDesc)));
@@ -460,6 +463,7 @@ static void destroy_workspace(sslm_workspace_s* w) {
 	cudaFreeHost(w->h_src);
 	cudaFreeHost(w->h_sink);
 	cudaFreeHost(w->h_status);
+	cudaFreeHost(w->h_done);
 	cudaFreeHost(w->h_sat);
 	cudaFreeHost(w->h_best);
 	if (w->ev0) cudaEventDestroy(w->ev0);
@@ -520,6 +524,14 @@ extern "C" sslm_status sslm_b200_tc_stats(uint64_t* launches, uint64_t* refusals
 	if (launches) *launches = l;
 	if (refusals) *refusals = r;
 	if (last_reason) *last_reason = why;
+	return SSLM_OK;
+}
+
+extern "C" sslm_status sslm_b200_tc_variant_counts(uint64_t* counts, int32_t n) {
+	if (!counts || n < 1) return SSLM_INVALID_ARGUMENT;
+	unsigned long long c[8] = {0};
+	tc_variant_counts(c, 8);
+	for (int i = 0; i < n; ++i) counts[i] = i < 8 ? c[i] : 0;
 	return SSLM_OK;
 }
 

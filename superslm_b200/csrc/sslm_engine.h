@@ -40,6 +40,7 @@ struct sslm_workspace_s {
 	sslm::RowSource* h_src = nullptr;
 	sslm::RowSink* h_sink = nullptr;
 	int32_t* h_status = nullptr;
+	int32_t* h_done = nullptr;
 	unsigned long long* h_sat = nullptr;
 	unsigned long long* h_best = nullptr;
 	// device mirrors
@@ -62,6 +63,7 @@ struct sslm_workspace_s {
 	cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 	float last_ms = 0.f;
 	uint64_t launches = 0;
+	bool launch_failed = false;   // a kernel launch of the current call was refused by the runtime
 	// optional per-kernel-class timing (sslm_b200_profile): an event before every launch
 	bool profile = false;
 	std::vector<cudaEvent_t> prof_events;

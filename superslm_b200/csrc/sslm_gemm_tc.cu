@@ -35,9 +35,12 @@
 namespace sslm {
 
 // how often the tensor-core path ran / declined, and why it last declined
-// (1 alignment, 2 shared-memory opt-in, 3 no cuTensorMapEncodeTiled, 4 tensor-map encode failed)
+// (1 alignment, 2 shared-memory opt-in, 3 no cuTensorMapEncodeTiled, 4 tensor-map encode failed,
+// 5 the launch itself was refused)
 static std::atomic<unsigned long long> g_tc_launches{0}, g_tc_refusals{0};
 static std::atomic<int> g_tc_last_reason{0};
+// launches per kernel variant: 0 = 128 x 64 tiles, 1 = 128 x 128, 2 = 256 x 64, 3 = 256 x 128
+static std::atomic<unsigned long long> g_tc_variant[8];
 
 namespace {
 
@@ -594,16 +597,6 @@ bool tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out
 	return true;
 }
 
-int sm_count() {
-	static int n = [] {
-		int dev = 0, v = 148;
-		cudaGetDevice(&dev);
-		if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) v = 148;
-		return v;
-	}();
-	return n;
-}
-
 // K slices per output tile: only when the tiles alone would leave SMs idle, never fewer than
 // eight 128-wide k-blocks per slice (a shorter main loop is cheaper than the exchange), and
 // only as many as the scratch can hold.
@@ -629,13 +622,12 @@ template <int MT, int BN>
 bool launch_cfg(const LinearArgs& a_in, cudaStream_t st) {
 	using Cfg = TcCfg<MT, BN>;
 	LinearArgs a = a_in;
-	static bool configured = false;
-	if (!configured) {
-		if (cudaFuncSetAttribute(k_linear_tc<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes) != cudaSuccess) {
-			g_tc_last_reason.store(2);
-			return false;
-		}
-		configured = true;
+	static PerDeviceOnce configured;
+	if (once_per_device(configured, [] {
+		    return cudaFuncSetAttribute(k_linear_tc<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
+	    }) != cudaSuccess) {
+		g_tc_last_reason.store(2);
+		return false;
 	}
 	CUtensorMap ma, mb;
 	if (!tensor_map(a.x, a.M, a.K, BM, &ma) || !tensor_map(a.w, a.N, a.K, BN, &mb)) {
@@ -646,7 +638,10 @@ bool launch_cfg(const LinearArgs& a_in, cudaStream_t st) {
 	a.splits = pick_splits<MT, BN>(a, tiles);
 	const int items = tiles * a.splits;
 	const int grid = items < sm_count() ? items : sm_count();
-	launch_pdl(k_linear_tc<MT, BN>, dim3(grid), dim3(kTcThreads), Cfg::kSmemBytes, st, ma, mb, a);
+	if (launch_pdl(k_linear_tc<MT, BN>, dim3(grid), dim3(kTcThreads), Cfg::kSmemBytes, st, ma, mb, a) != cudaSuccess) {
+		g_tc_last_reason.store(5);
+		return false;
+	}
 	return true;
 }
 
@@ -656,6 +651,9 @@ void tc_stats(unsigned long long* launches, unsigned long long* refusals, int* l
 	*launches = g_tc_launches.load();
 	*refusals = g_tc_refusals.load();
 	*last_reason = g_tc_last_reason.load();
+}
+void tc_variant_counts(unsigned long long* counts, int n) {
+	for (int i = 0; i < n; ++i) counts[i] = i < 8 ? g_tc_variant[i].load() : 0ull;
 }
 static bool tc_refuse(int reason) {
 	g_tc_refusals.fetch_add(1);
@@ -688,6 +686,7 @@ bool launch_linear_tc(const LinearArgs& a, cudaStream_t st) {
 	else ok = narrow ? launch_cfg<1, 64>(a, st) : launch_cfg<1, 128>(a, st);
 	if (!ok) return tc_refuse(g_tc_last_reason.load() ? g_tc_last_reason.load() : 9);
 	g_tc_launches.fetch_add(1);
+	g_tc_variant[(two ? 2 : 0) + (narrow ? 0 : 1)].fetch_add(1);
 	return true;
 }
 

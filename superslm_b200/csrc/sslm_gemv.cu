@@ -1,19 +1,41 @@
 // Decode-path int8 linear layer: out[m,n] = fold_n(sum_k x[m,k] w[n,k]) for a handful of
-// rows m. HBM-bound: the weights are streamed exactly once with 16-byte coalesced loads,
-// multiplied with dp4a against the activation rows held in shared memory, and reduced
-// with warp shuffles. The epilogue applies the per-channel weight-scale fold, adds the
-// LoRA delta, stores the wide row and reduces the per-row max |x| the funnel needs.
+// rows m. HBM-bound: the kernel exists to keep the weight stream at the speed of the memory.
+//
+// A block owns a contiguous range of output channels, i.e. one contiguous byte range of the
+// row-major weight matrix. A producer thread streams that range into a shared-memory ring with
+// bulk asynchronous copies (cp.async.bulk, 16 KiB each, completion counted on an mbarrier), so
+// ~100 KiB per block are in flight without holding a register; eight consumer warps walk each
+// landed chunk as a flat array of 16-byte pieces, multiply with dp4a against the activation rows
+// held in shared memory, and add their partial sums into per-channel accumulators in shared
+// memory (a warp reduces with one warp-reduce instruction per row it touches). Chunks need not
+// line up with weight rows: a piece knows its (channel, k) from its flat index.
+//
+// The weights are written by no kernel, so the ring's first copies and the block's fold rows are
+// requested BEFORE the dependency wait: while the kernel in front (a row kernel that moves
+// little data) finishes, this kernel's weight stream is already running.
+//
+// The epilogue applies the per-channel weight-scale fold, adds the LoRA delta, stores the wide
+// row and reduces the per-row max |x| the funnel needs (or the argmax key for the head).
 // (GemmInt8AccumulateRow + ApplyWeightScaleFold + AddAmplifyingLoraDelta,
 //  src/matmul.cpp:455-464, src/forward/forward_sites.cpp:461-470, :1051-1103.)
-// int32 accumulation is exact: K * 127 * 128 < 2^31 for every K the loader accepts.
+// int32 accumulation is exact: K * 127 * 128 < 2^31 for every K the loader accepts, and integer
+// sums do not depend on the order in which pieces are added.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out marks the block's rows with an
+// internal status, the block stops issuing copies, waits (bounded again) for the copies it has
+// in flight, and returns.
 #include <cuda_runtime.h>
 
 #include "sslm_kernels.h"
 
 namespace sslm {
 
-constexpr int kGemvThreads = 256;
-constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kGemvConsumers = 256;                 // eight consumer warps
+constexpr int kGemvThreads = kGemvConsumers + 32;   // + the producer warp
+constexpr int kChunkBytes = 16 * 1024;
+constexpr int kChunkVec = kChunkBytes / 16;         // 16-byte pieces per chunk
+constexpr int kMaxStages = 6;
+constexpr uint32_t kGemvMaxPolls = 1u << 22;
 
 __device__ __forceinline__ int dot16(const int4& a, const int4& b, int acc) {
 	acc = __dp4a(a.x, b.x, acc);
@@ -23,158 +45,320 @@ __device__ __forceinline__ int dot16(const int4& a, const int4& b, int acc) {
 	return acc;
 }
 
-// MT rows per pass, RPW output channels per warp per step.
-template <int MT, int RPW>
+namespace {
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+	asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
+	asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bar_try_wait(uint32_t bar, uint32_t parity) {
+	uint32_t ok;
+	asm volatile(
+	    "{\n\t.reg .pred p;\n\t"
+	    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+	    "selp.u32 %0, 1, 0, p;\n\t}"
+	    : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+	return ok != 0;
+}
+// bounded wait: false when the limit ran out
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
+	for (uint32_t i = 0; i < kGemvMaxPolls; ++i) {
+		if (bar_try_wait(bar, parity)) return true;
+		if (i > 1024) __nanosleep(64);
+	}
+	return false;
+}
+// contiguous global -> shared copy (both 16-byte aligned, bytes a multiple of 16); completes on `bar`
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+	asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+	             ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+}  // namespace
+
+// What the host decides per launch.
+struct GemvPlan {
+	int rows_per_block;   // output channels per block
+	int stages;           // ring depth
+	int k16;              // K / 16
+	int step_row, step_kc;   // (256 / k16, 256 % k16): how a thread's piece moves from one pass to the next
+};
+
+// MT rows of x per pass (grid.y walks the row groups).
+template <int MT>
 __global__ void __launch_bounds__(kGemvThreads)
-k_gemv(LinearArgs a) {
-	extern __shared__ __align__(16) unsigned char smem[];
-	int8_t* sx = (int8_t*)smem;                                         // [MT][K]
-	unsigned long long* smax = (unsigned long long*)(smem + (size_t)MT * a.K);  // [3][MT] (+ [MT] best)
+k_gemv(LinearArgs a, GemvPlan p) {
+	extern __shared__ __align__(128) unsigned char smem[];
+	const int K = a.K, k16 = p.k16, S = p.stages;
+	const int n0 = blockIdx.x * p.rows_per_block;
+	const int nrows = min(p.rows_per_block, a.N - n0);
 	const int m0 = blockIdx.y * MT;
 	const int mcount = min(MT, a.M - m0);
-	const int K = a.K, kv = K / 16;
-	pdl_wait();
-	pdl_release();
-	for (int i = threadIdx.x; i < MT * kv; i += blockDim.x) {
-		const int m = i / kv, c = i - m * kv;
-		int4 v = make_int4(0, 0, 0, 0);
-		if (m < mcount) v = ((const int4*)(a.x + (size_t)(m0 + m) * K))[c];
-		((int4*)sx)[i] = v;
+	// carve: ring | x rows | accumulators | fold rows | maxima | barriers
+	unsigned char* ring = smem;
+	int8_t* sx = (int8_t*)(ring + (size_t)S * kChunkBytes);
+	int* sacc = (int*)(sx + (size_t)MT * K);                                   // [MT][rows_per_block]
+	int32_t* sfold = sacc + (size_t)MT * p.rows_per_block;                     // [rows_per_block][3]
+	unsigned long long* smax = (unsigned long long*)(((uintptr_t)(sfold + 3 * (size_t)p.rows_per_block) + 7) & ~(uintptr_t)7);   // [4][MT]
+	const uint32_t bars = smem_addr(smax + 4 * MT);
+	auto full_bar = [&](int s) { return bars + 8u * s; };
+	auto empty_bar = [&](int s) { return bars + 8u * (kMaxStages + s); };
+	__shared__ int s_timeout;
+
+	const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+	const size_t total_bytes = (size_t)nrows * K;
+	const int nchunks = (int)((total_bytes + kChunkBytes - 1) / kChunkBytes);
+	const int8_t* wsrc = a.w + (size_t)n0 * K;
+
+	if (t == 0) {
+		for (int s = 0; s < S; ++s) {
+			bar_init(full_bar(s), 1);
+			bar_init(empty_bar(s), kGemvConsumers / 32);
+		}
+		s_timeout = 0;
+		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
-	if (threadIdx.x < 4 * MT) smax[threadIdx.x] = 0ull;
 	__syncthreads();
 
-	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-	const int gwarp = blockIdx.x * kGemvWarps + warp, nwarps = gridDim.x * kGemvWarps;
-	// this lane's output duty after the reduction: channel c_me of the step, row m_me
-	const int c_me = lane / MT, m_me = lane % MT;
-	unsigned long long lmax[3] = {0ull, 0ull, 0ull};
-	unsigned long long lbest = 0ull;
-
-	for (int n0 = gwarp * RPW; n0 < a.N; n0 += nwarps * RPW) {
-		int acc[RPW][MT];
-#pragma unroll
-		for (int c = 0; c < RPW; ++c)
-#pragma unroll
-			for (int m = 0; m < MT; ++m) acc[c][m] = 0;
-		for (int kc = lane; kc < kv; kc += 32) {
-			int4 wv[RPW];
-#pragma unroll
-			for (int c = 0; c < RPW; ++c) {
-				const int n = min(n0 + c, a.N - 1);
-				wv[c] = __ldg((const int4*)(a.w + (size_t)n * K) + kc);
-			}
-#pragma unroll
-			for (int m = 0; m < MT; ++m) {
-				const int4 xv = ((const int4*)(sx + (size_t)m * K))[kc];
-#pragma unroll
-				for (int c = 0; c < RPW; ++c) acc[c][m] = dot16(wv[c], xv, acc[c][m]);
+	if (warp == kGemvConsumers / 32) {
+		// ---- producer: one thread keeps the ring full. Its first S copies go out ahead of the
+		// dependency wait (weights are not written by any kernel).
+		auto issue = [&](int c) {
+			const int s = c % S;
+			const size_t off = (size_t)c * kChunkBytes;
+			const uint32_t bytes = (uint32_t)min((size_t)kChunkBytes, total_bytes - off);
+			bar_expect_tx(full_bar(s), bytes);
+			bulk_load(smem_addr(ring + (size_t)s * kChunkBytes), wsrc + off, bytes, full_bar(s));
+		};
+		if (lane == 0)
+			for (int c = 0; c < nchunks && c < S; ++c) issue(c);
+		pdl_wait();
+		pdl_release();
+		if (lane == 0) {
+			for (int c = S; c < nchunks; ++c) {
+				if (!bar_wait(empty_bar(c % S), ((uint32_t)(c / S) & 1u) ^ 1u)) {
+					atomicExch(&s_timeout, 1);
+					break;
+				}
+				if (*(volatile int*)&s_timeout) break;
+				issue(c);
 			}
 		}
-		int mine = 0;
-#pragma unroll
-		for (int c = 0; c < RPW; ++c)
-#pragma unroll
-			for (int m = 0; m < MT; ++m) {
-				int v = acc[c][m];
-#pragma unroll
-				for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-				if (c == c_me && m == m_me) mine = v;
+	} else {
+		// ---- consumers. Ahead of the wait: the block's fold rows (weights), cleared accumulators.
+		for (int i = t; i < MT * p.rows_per_block; i += kGemvConsumers) sacc[i] = 0;
+		if (a.fold != nullptr) {
+			const int32_t* f = a.fold + (size_t)n0 * 3;
+			for (int i = t; i < nrows * 3; i += kGemvConsumers) sfold[i] = __ldg(f + i);
+		}
+		if (t < 4 * MT) smax[t] = 0ull;
+		pdl_wait();
+		pdl_release();
+		// the activation rows (written by the kernel in front: read past the L1)
+		for (int i = t; i < MT * k16; i += kGemvConsumers) {
+			const int m = i / k16, c = i - m * k16;
+			int4 v = make_int4(0, 0, 0, 0);
+			if (m < mcount) v = __ldcg((const int4*)(a.x + (size_t)(m0 + m) * K) + c);
+			((int4*)sx)[i] = v;
+		}
+		asm volatile("bar.sync 1, 256;" ::: "memory");
+
+		// this thread's piece in pass j of chunk c is flat index c * kChunkVec + j * 256 + t
+		int row = t / k16, kc = t - row * k16;
+		bool ok = true;
+		for (int c = 0; c < nchunks && ok; ++c) {
+			const int s = c % S;
+			// (the whole warp agrees on the outcome: the warp-wide instructions below need all lanes)
+			if (!__all_sync(0xffffffffu, bar_wait(full_bar(s), (uint32_t)(c / S) & 1u) ? 1 : 0)) {
+				atomicExch(&s_timeout, 1);
+				ok = false;
+				break;
 			}
-		const int n = n0 + c_me;
-		if (c_me < RPW && n < a.N && m_me < mcount) {
-			const int row = m0 + m_me;
-			int seg = 0;
-			while (seg + 1 < a.nseg && n >= a.seg_end[seg]) ++seg;
-			int32_t v32 = mine;
-			if (a.fold) v32 = fold(mine, a.fold[3 * n], a.fold[3 * n + 1], a.fold[3 * n + 2]);
-			int64_t v = v32;
-			if (a.rows != nullptr && a.seg_lora[seg] >= 0) {
-				const LoraLayerDev* ll = a.rows[row].lora;
-				if (ll != nullptr) {
-					const LoraLayerDev& L = ll[a.layer];
-					const LoraProjDev& p = L.p[a.seg_lora[seg]];
-					if (p.a != nullptr) {
-						const int nl = n - (seg ? a.seg_end[seg - 1] : 0);
-						const int8_t* brow = p.b + (size_t)nl * L.rank;
-						const int8_t* u = a.lora_u + ((size_t)row * 3 + seg) * kMaxLoraRank;
-						int dsum = 0;
-						for (uint32_t t = 0; t < L.rank; ++t) dsum += (int)brow[t] * (int)u[t];
-						v += (int64_t)amp_fold(dsum, p.df[3 * nl], p.df[3 * nl + 1], p.df[3 * nl + 2]);
+			const int4* wv = (const int4*)(ring + (size_t)s * kChunkBytes);
+			const int vec_left = (int)((total_bytes - (size_t)c * kChunkBytes) >> 4);   // pieces from this chunk's start to the end
+#pragma unroll
+			for (int j = 0; j < kChunkVec / kGemvConsumers; ++j) {
+				const int i = j * kGemvConsumers + t;
+				const bool live = i < vec_left;
+				int4 w4 = make_int4(0, 0, 0, 0);
+				if (live) w4 = wv[i];
+				// rows this warp's 32 consecutive pieces touch: one or two when a weight row holds
+				// at least 32 pieces, several otherwise
+				const int row_lo = __shfl_sync(0xffffffffu, row, 0);
+				const int row_hi = __shfl_sync(0xffffffffu, row, 31);
+				if (row_hi <= row_lo + 1) {
+#pragma unroll
+					for (int m = 0; m < MT; ++m) {
+						int v = 0;
+						if (live) v = dot16(w4, ((const int4*)(sx + (size_t)m * K))[kc], 0);
+						const int s0 = __reduce_add_sync(0xffffffffu, row == row_lo ? v : 0);
+						if (lane == 0 && row_lo < nrows) atomicAdd(&sacc[m * p.rows_per_block + row_lo], s0);
+						if (row_hi != row_lo) {
+							const int s1 = __reduce_add_sync(0xffffffffu, row == row_lo ? 0 : v);
+							if (lane == 0 && row_hi < nrows) atomicAdd(&sacc[m * p.rows_per_block + row_hi], s1);
+						}
+					}
+				} else if (live) {
+#pragma unroll
+					for (int m = 0; m < MT; ++m)
+						atomicAdd(&sacc[m * p.rows_per_block + row], dot16(w4, ((const int4*)(sx + (size_t)m * K))[kc], 0));
+				}
+				row += p.step_row;
+				kc += p.step_kc;
+				if (kc >= k16) { kc -= k16; ++row; }
+			}
+			__syncwarp();
+			if (lane == 0) bar_arrive(empty_bar(s));
+		}
+		asm volatile("bar.sync 1, 256;" ::: "memory");
+
+		if (*(volatile int*)&s_timeout) {
+			if (a.status != nullptr && t < mcount) atomicCAS(&a.status[m0 + t], 0, (int32_t)kInternalWaitTimeout);
+		} else {
+			// ---- epilogue: thread i takes output (m, n) = (i / nrows, i % nrows)
+			unsigned long long lmax[3] = {0ull, 0ull, 0ull};
+			unsigned long long lbest = 0ull;
+			int my_m = -1;
+			for (int i = t; i < mcount * nrows; i += kGemvConsumers) {
+				const int m = i / nrows, nl0 = i - m * nrows;
+				if (m != my_m) {
+					// (a thread's outputs belong to one row except when nrows < 256: flush per row)
+					if (my_m >= 0) {
+						if (a.best != nullptr) {
+							if (lbest) atomicMax(&smax[3 * MT + my_m], lbest);
+						} else {
+#pragma unroll
+							for (int sg = 0; sg < 3; ++sg)
+								if (lmax[sg]) atomicMax(&smax[sg * MT + my_m], lmax[sg]);
+						}
+						lmax[0] = lmax[1] = lmax[2] = 0ull;
+						lbest = 0ull;
+					}
+					my_m = m;
+				}
+				const int n = n0 + nl0, rowg = m0 + m;
+				const int mine = sacc[m * p.rows_per_block + nl0];
+				int seg = 0;
+				while (seg + 1 < a.nseg && n >= a.seg_end[seg]) ++seg;
+				int32_t v32 = mine;
+				if (a.fold) v32 = fold(mine, sfold[3 * nl0], sfold[3 * nl0 + 1], sfold[3 * nl0 + 2]);
+				int64_t v = v32;
+				if (a.rows != nullptr && a.seg_lora[seg] >= 0) {
+					const LoraLayerDev* ll = a.rows[rowg].lora;
+					if (ll != nullptr) {
+						const LoraLayerDev& L = ll[a.layer];
+						const LoraProjDev& pj = L.p[a.seg_lora[seg]];
+						if (pj.a != nullptr) {
+							const int nl = n - (seg ? a.seg_end[seg - 1] : 0);
+							const int8_t* brow = pj.b + (size_t)nl * L.rank;
+							const int8_t* u = a.lora_u + ((size_t)rowg * 3 + seg) * kMaxLoraRank;
+							int dsum = 0;
+							for (uint32_t r = 0; r < L.rank; ++r) dsum += (int)brow[r] * (int)u[r];
+							v += (int64_t)amp_fold(dsum, pj.df[3 * nl], pj.df[3 * nl + 1], pj.df[3 * nl + 2]);
+						}
+					}
+				}
+				if (a.best != nullptr) {
+					if (a.row_mask != nullptr) {
+						const uint8_t* page = a.row_mask[rowg];
+						if (page != nullptr && !((page[n >> 3] >> (n & 7)) & 1u)) v32 = INT32_MIN;
+					}
+					const unsigned long long key =
+					    ((unsigned long long)((uint32_t)v32 ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)n);
+					lbest = key > lbest ? key : lbest;
+					if (a.logits) a.logits[(size_t)rowg * a.N + n] = v32;
+				} else {
+					if (a.out64) ((int64_t*)a.out)[(size_t)rowg * a.out_ld + n] = v;
+					else ((int32_t*)a.out)[(size_t)rowg * a.out_ld + n] = (int32_t)v;
+					if (a.seg_slot[seg] >= 0) {
+						const unsigned long long ab = v < 0 ? (~(unsigned long long)v + 1ull) : (unsigned long long)v;
+						lmax[seg] = ab > lmax[seg] ? ab : lmax[seg];
 					}
 				}
 			}
-			if (a.best != nullptr) {
-				if (a.row_mask != nullptr) {
-					const uint8_t* page = a.row_mask[row];
-					if (page != nullptr && !((page[n >> 3] >> (n & 7)) & 1u)) v32 = INT32_MIN;
+			if (my_m >= 0) {
+				if (a.best != nullptr) {
+					if (lbest) atomicMax(&smax[3 * MT + my_m], lbest);
+				} else {
+#pragma unroll
+					for (int sg = 0; sg < 3; ++sg)
+						if (lmax[sg]) atomicMax(&smax[sg * MT + my_m], lmax[sg]);
 				}
-				const unsigned long long key =
-				    ((unsigned long long)((uint32_t)v32 ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)n);
-				lbest = key > lbest ? key : lbest;
-				if (a.logits) a.logits[(size_t)row * a.N + n] = v32;
-			} else {
-				if (a.out64) ((int64_t*)a.out)[(size_t)row * a.out_ld + n] = v;
-				else ((int32_t*)a.out)[(size_t)row * a.out_ld + n] = (int32_t)v;
-				if (a.seg_slot[seg] >= 0) {
-					const unsigned long long ab = v < 0 ? (~(unsigned long long)v + 1ull) : (unsigned long long)v;
-					lmax[seg] = ab > lmax[seg] ? ab : lmax[seg];
+			}
+			asm volatile("bar.sync 1, 256;" ::: "memory");
+			if (t < 4 * MT) {
+				const int sg = t / MT, m = t % MT;
+				const unsigned long long v = smax[t];
+				if (v != 0ull && m < mcount) {
+					if (sg == 3) atomicMax(&a.best[m0 + m], v);
+					else if (a.rowmax != nullptr && sg < a.nseg && a.seg_slot[sg] >= 0)
+						atomicMax(&a.rowmax[(size_t)(m0 + m) * 4 + a.seg_slot[sg]], v);
 				}
 			}
 		}
 	}
-	// block-level reduction of the row maxima / argmax keys, then one global atomic each
-	if (c_me < RPW && m_me < mcount) {
-		if (a.best != nullptr) {
-			if (lbest) atomicMax(&smax[3 * MT + m_me], lbest);
-		} else {
-#pragma unroll
-			for (int s = 0; s < 3; ++s)
-				if (lmax[s]) atomicMax(&smax[s * MT + m_me], lmax[s]);
-		}
-	}
+	// No copy may still be landing in this block's shared memory when the block ends. In the normal
+	// course every chunk was waited for by the consumers; after a timeout the producer's copies
+	// that did complete are drained here, bounded.
 	__syncthreads();
-	if (threadIdx.x < 4 * MT) {
-		const int s = threadIdx.x / MT, m = threadIdx.x % MT;
-		const unsigned long long v = smax[threadIdx.x];
-		if (v != 0ull && m < mcount) {
-			if (s == 3) atomicMax(&a.best[m0 + m], v);
-			else if (a.rowmax != nullptr && s < a.nseg && a.seg_slot[s] >= 0)
-				atomicMax(&a.rowmax[(size_t)(m0 + m) * 4 + a.seg_slot[s]], v);
-		}
+	if (t == 0 && *(volatile int*)&s_timeout) {
+		for (int c = max(0, nchunks - S); c < nchunks; ++c) bar_wait(full_bar(c % S), (uint32_t)(c / S) & 1u);
 	}
 }
 
-template <int MT, int RPW>
-static void launch_one(const LinearArgs& a, int grid_x, int grid_y, cudaStream_t st) {
-	const size_t smem = (size_t)MT * a.K + 4 * MT * 8 + 16;
-	static bool configured = false;
-	if (!configured) {
-		cudaFuncSetAttribute(k_gemv<MT, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-		configured = true;
-	}
-	launch_pdl(k_gemv<MT, RPW>, dim3(grid_x, grid_y), dim3(kGemvThreads), smem, st, a);
+// shared memory of one block: ring, activation rows, accumulators, fold rows, maxima, barriers
+static size_t gemv_smem_bytes(int mt, int K, int rows_per_block, int stages) {
+	return (size_t)stages * kChunkBytes + (size_t)mt * K + (size_t)mt * rows_per_block * 4 + (size_t)rows_per_block * 12 +
+	       8 + (size_t)4 * mt * 8 + (size_t)2 * kMaxStages * 8 + 16;
 }
 
 template <int MT>
-static void launch_mt(const LinearArgs& a, int grid_y, cudaStream_t st) {
-	// as many channels per warp step as keeps at least ~2 blocks per SM busy
-	const int want_blocks = 296;
-	int rpw = 4;
-	while (rpw > 1 && (a.N + kGemvWarps * rpw - 1) / (kGemvWarps * rpw) * grid_y < want_blocks) rpw >>= 1;
-	if (MT * rpw > 32) rpw = 32 / MT;   // one output per lane
-	int gx = (a.N + kGemvWarps * rpw - 1) / (kGemvWarps * rpw);
-	if (gx > 148 * 8) gx = 148 * 8;
-	if (rpw == 4) launch_one<MT, 4>(a, gx, grid_y, st);
-	else if (rpw == 2) launch_one<MT, 2>(a, gx, grid_y, st);
-	else launch_one<MT, 1>(a, gx, grid_y, st);
+static cudaError_t launch_mt(const LinearArgs& a, int grid_y, cudaStream_t st) {
+	static PerDeviceOnce configured;
+	cudaError_t e = once_per_device(configured, [] {
+		cudaError_t c = cudaFuncSetAttribute(k_gemv<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+		if (c != cudaSuccess) return c;
+		return cudaFuncSetAttribute(k_gemv<MT>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+	});
+	if (e != cudaSuccess) return e;
+	GemvPlan p;
+	// one block per multiprocessor when the matrix is large enough to keep them all streaming;
+	// never fewer than 8 channels per block
+	const int sms = sm_count();
+	int rpb = (a.N + sms - 1) / sms;
+	if (rpb < 8) rpb = 8;
+	if (rpb > a.N) rpb = a.N;
+	p.rows_per_block = rpb;
+	p.k16 = a.K / 16;
+	p.step_row = kGemvConsumers / p.k16;
+	p.step_kc = kGemvConsumers % p.k16;
+	// ring depth: as deep as lets two blocks share a multiprocessor (this kernel's blocks then
+	// start their weight stream while the kernel in front still runs), shallower when the
+	// activation rows are long, never more than the block's chunks
+	const size_t chunks = ((size_t)rpb * a.K + kChunkBytes - 1) / kChunkBytes;
+	int stages = kMaxStages;
+	const size_t budget = (size_t)MT * a.K > 40 * 1024 ? 200 * 1024 : 110 * 1024;
+	while (stages > 2 && gemv_smem_bytes(MT, a.K, rpb, stages) > budget) --stages;
+	if ((size_t)stages > chunks) stages = (int)chunks;
+	if (stages < 1) stages = 1;
+	p.stages = stages;
+	const size_t smem = gemv_smem_bytes(MT, a.K, rpb, stages);
+	if (smem > 220 * 1024) return cudaErrorInvalidConfiguration;
+	const int gx = (a.N + rpb - 1) / rpb;
+	return launch_pdl(k_gemv<MT>, dim3(gx, grid_y), dim3(kGemvThreads), smem, st, a, p);
 }
 
-void launch_linear_gemv(const LinearArgs& a, cudaStream_t st) {
-	if (a.M <= 1) launch_mt<1>(a, 1, st);
-	else if (a.M <= 2) launch_mt<2>(a, 1, st);
-	else if (a.M <= 4) launch_mt<4>(a, 1, st);
-	else launch_mt<8>(a, (a.M + 7) / 8, st);
+cudaError_t launch_linear_gemv(const LinearArgs& a, cudaStream_t st) {
+	if (a.M <= 1) return launch_mt<1>(a, 1, st);
+	if (a.M <= 2) return launch_mt<2>(a, 1, st);
+	if (a.M <= 4) return launch_mt<4>(a, 1, st);
+	return launch_mt<8>(a, (a.M + 7) / 8, st);
 }
 
 // ---------------------------------------------------------------- LoRA u = A x

@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <utility>
 
@@ -45,6 +46,39 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 	cfg.attrs = attr;
 	cfg.numAttrs = pdl_enabled() ? 1 : 0;
 	return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+// ---- per-device one-time set-up
+// cudaFuncSetAttribute and the device attributes apply to the CURRENT device only, and models may
+// be mapped on several devices of one process (sslm_b200_set_device): everything a launcher sets
+// up once is therefore kept per device ordinal. The set-up calls are idempotent, so two host
+// threads racing through the first launch on a device at worst both make them.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+	std::atomic<unsigned char> done[kMaxDevices];
+};
+inline int current_device_ordinal() {
+	int dev = 0;
+	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+	return dev;
+}
+template <typename F>
+cudaError_t once_per_device(PerDeviceOnce& o, F&& setup) {
+	const int dev = current_device_ordinal();
+	if (o.done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+	const cudaError_t e = setup();
+	if (e == cudaSuccess) o.done[dev].store(1, std::memory_order_release);
+	return e;
+}
+// multiprocessor count of the current device
+inline int sm_count() {
+	static std::atomic<int> cached[kMaxDevices];
+	const int dev = current_device_ordinal();
+	int v = cached[dev].load(std::memory_order_relaxed);
+	if (v > 0) return v;
+	if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v < 1) v = 148;
+	cached[dev].store(v, std::memory_order_relaxed);
+	return v;
 }
 
 struct RowSource { const int8_t* hidden; const Scale* scale; };  // nullptr hidden: embed rows[r].token
@@ -101,13 +135,15 @@ struct LinearArgs {
 	int n_tile_counters;
 	int splits;           // filled in by launch_linear_tc
 };
-// HBM-bound small-M path: vectorised weight streaming, dp4a, warp-shuffle reduction.
-void launch_linear_gemv(const LinearArgs& a, cudaStream_t st);
+// HBM-bound small-M path: bulk-copy weight streaming through a shared-memory ring, dp4a.
+cudaError_t launch_linear_gemv(const LinearArgs& a, cudaStream_t st);
 // tensor-core path for M > 8 rows (tcgen05 kind::i8, TMA-fed). Returns false when the
 // shape is not supported by that kernel (caller then uses the GEMV path).
 bool launch_linear_tc(const LinearArgs& a, cudaStream_t st);
 // process-wide counters of the tensor-core path: launches, refusals, reason of the last refusal
 void tc_stats(unsigned long long* launches, unsigned long long* refusals, int* last_reason);
+// launches per kernel variant (tile shape) of the tensor-core path
+void tc_variant_counts(unsigned long long* counts, int n);
 
 // u = clamp127(amp_fold(A x)) for up to three projections sharing the input x
 // (AddAmplifyingLoraDelta's first half, src/forward/forward_sites.cpp:1062-1080)

@@ -25,6 +25,8 @@
 //   * at most kResidentMaxRows rows per call; more is refused with SSLM_INVALID_ARGUMENT.
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "../../include/sslm_b200.h"
 #include "sslm_kernels.h"
 
@@ -38,7 +40,6 @@ namespace {
 
 constexpr int kResidentMaxRows = SSLM_B200_RESIDENT_MAX_ROWS;
 constexpr int kResidentMaxK = 16384;        // the streaming kernel stages 8 activation rows in shared memory
-constexpr int kMaxDevices = 64;
 
 // Funnel of the projected rows (FunnelProjectedRow's tail, src/forward/forward_sites.cpp:
 // 1114-1146): the same arithmetic as the funnel behind sslm_b200_linear, reading the row
@@ -64,7 +65,8 @@ k_resident_funnel(const int32_t* wide, int n, unsigned long long* row_peak, cons
 }
 
 // device address of g_row_peak, per device ordinal; resolved by the first call on a device
-unsigned long long* g_peak_addr[kMaxDevices] = {nullptr};
+// (host threads may race through that first call: they all store the same address)
+std::atomic<unsigned long long*> g_peak_addr[kMaxDevices];
 
 }  // namespace
 }  // namespace sslm
@@ -80,13 +82,19 @@ extern "C" sslm_status sslm_b200_linear_resident(const int8_t* d_x, const int8_t
 	if (M < 1 || N < 1 || K < 16 || K % 16 != 0) return SSLM_INVALID_ARGUMENT;
 	if (M > kResidentMaxRows || K > kResidentMaxK) return SSLM_INVALID_ARGUMENT;   // beyond the fixed scratch
 	if (((uintptr_t)d_x & 15) || ((uintptr_t)d_w & 15) || ((uintptr_t)d_out_folded & 15)) return SSLM_MISALIGNED_BUFFER;
+	// the remaining arrays are read and written as 4- and 8-byte words
+	if (((uintptr_t)d_fold & 3) || ((uintptr_t)d_row_status & 3) || ((uintptr_t)d_in_scales & 7) ||
+	    ((uintptr_t)d_out_scales & 7))
+		return SSLM_MISALIGNED_BUFFER;
 	int dev = -1;
 	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SSLM_ALLOCATION_FAILED;
-	if (g_peak_addr[dev] == nullptr) {
+	unsigned long long* peak = g_peak_addr[dev].load(std::memory_order_acquire);
+	if (peak == nullptr) {
 		// set-up, once per device: where this device keeps its copy of the array
 		void* p = nullptr;
 		if (cudaGetSymbolAddress(&p, g_row_peak) != cudaSuccess || p == nullptr) return SSLM_ALLOCATION_FAILED;
-		g_peak_addr[dev] = (unsigned long long*)p;
+		peak = (unsigned long long*)p;
+		g_peak_addr[dev].store(peak, std::memory_order_release);
 	}
 	cudaStream_t st = (cudaStream_t)stream;
 	if (d_row_status != nullptr && cudaMemsetAsync(d_row_status, 0, (size_t)M * 4, st) != cudaSuccess)
@@ -96,14 +104,22 @@ extern "C" sslm_status sslm_b200_linear_resident(const int8_t* d_x, const int8_t
 	a.x = d_x; a.w = d_w; a.fold = d_fold;
 	a.M = M; a.N = N; a.K = K;
 	a.out = d_out_folded; a.out_ld = N; a.out64 = 0;
-	a.rowmax = g_peak_addr[dev];
+	a.rowmax = peak;
 	a.nseg = 1;
 	a.seg_end[0] = a.seg_end[1] = a.seg_end[2] = N;
 	a.seg_slot[0] = 0; a.seg_slot[1] = a.seg_slot[2] = -1;
 	a.seg_lora[0] = a.seg_lora[1] = a.seg_lora[2] = -1;
 	a.status = d_row_status;
-	launch_linear_gemv(a, st);
-	k_resident_funnel<<<M, 256, 0, st>>>(d_out_folded, N, g_peak_addr[dev], (const Scale*)d_in_scales,
-	                                     Scale{site_m, site_e}, d_out_codes, (Scale*)d_out_scales, d_row_status);
-	return cudaGetLastError() == cudaSuccess ? SSLM_OK : SSLM_ALLOCATION_FAILED;
+	// nothing ran yet if the projection's launch is refused: the array still reads zero
+	if (launch_linear_gemv(a, st) != cudaSuccess) return SSLM_ALLOCATION_FAILED;
+	k_resident_funnel<<<M, 256, 0, st>>>(d_out_folded, N, peak, (const Scale*)d_in_scales, Scale{site_m, site_e},
+	                                     d_out_codes, (Scale*)d_out_scales, d_row_status);
+	if (cudaGetLastError() != cudaSuccess) {
+		// The projection is enqueued and will leave its row peaks in the array, but the kernel that
+		// consumes and clears them is not: clear the rows this call used, in stream order, so the
+		// next call on this device starts from zero all the same.
+		cudaMemsetAsync(peak, 0, (size_t)M * 4 * sizeof(unsigned long long), st);
+		return SSLM_ALLOCATION_FAILED;
+	}
+	return SSLM_OK;
 }

@@ -243,8 +243,8 @@ __device__ int32_t block_rmsnorm(const int8_t* h, const int8_t* gain, int n, Sca
 	return block_code(wide, n, mx, funnel_prefold(nullptr, 0, site), out_g, nullptr, out_scale);
 }
 
-__device__ __forceinline__ void set_status(const RowBatch& b, int row, int32_t st) {
-	if (threadIdx.x == 0 && st != kOk) atomicCAS(&b.status[row], 0, st);
+__device__ __forceinline__ void set_status(const RowBatch& b, int row, int32_t st, int site, int layer) {
+	if (threadIdx.x == 0 && st != kOk) atomicCAS(&b.status[row], 0, pack_status(st, site, layer));
 }
 
 // ------------------------------------------------------------------- kernels
@@ -265,8 +265,10 @@ k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource*
 	if (threadIdx.x == 0) {
 		b.status[r] = 0;
 		b.sat[r] = 0ull;
+		b.done[r] = 0;
 	}
 	int32_t st = kOk;
+	int site = kSiteEmbed;
 	const RowSource s = src[r];
 	if (s.hidden != nullptr) {
 #pragma unroll 1
@@ -281,10 +283,11 @@ k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource*
 	}
 	__syncthreads();
 	if (st == kOk && layer != nullptr) {
+		site = kSiteAttnNorm;
 		st = block_rmsnorm(x, layer->g_attn, n, layer->c_attn_norm, wide, b.nrm + (size_t)r * n,
 		                   &b.ns[r], lut, red);
 	}
-	set_status(b, r, st);
+	set_status(b, r, st, site, b.layer);
 }
 
 // RMSNorm of the stream with the given gain (used for the final norm before the head).
@@ -300,7 +303,7 @@ k_rmsnorm(RowBatch b, Dims d, const int8_t* gain, Scale site) {
 	if (b.status[r] != 0) return;
 	const int32_t st = block_rmsnorm(b.x + (size_t)r * n, gain, n, site, wide, b.nrm + (size_t)r * n,
 	                                 &b.ns[r], lut, red);
-	set_status(b, r, st);
+	set_status(b, r, st, kSiteFinalNorm, b.layer);
 }
 
 // After the fused q/k/v projection: q funnel (ProjectAndFunnel's tail,
@@ -375,7 +378,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 	unsigned long long mxq = mx;
 	if (lw.b_q != nullptr) {
 		if (!bias_gate) {
-			set_status(b, r, kRoundingDivideExponentOutOfDomain);
+			set_status(b, r, kRoundingDivideExponentOutOfDomain, kSiteQ, b.layer);
 			return;
 		}
 		// the row maximum the GEMM reduced does not include the bias: take it here
@@ -390,14 +393,14 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		}
 		bad = __syncthreads_or(bad);
 		if (bad != 0) {
-			set_status(b, r, kBiasReconcileProductOutOfDomain);
+			set_status(b, r, kBiasReconcileProductOutOfDomain, kSiteQ, b.layer);
 			return;
 		}
 		mxq = block_max_u64(lmx, red);
 	}
 	const FunnelParams fp = funnel_finish(mxq, fold_q);
 	if (fp.status != kOk) {
-		set_status(b, r, fp.status);
+		set_status(b, r, fp.status, kSiteQ, b.layer);
 		return;
 	}
 	// softmax constants per kv head: sm = Combine(S[q], softmax_khead) -> C30 constants -> width gate.
@@ -421,9 +424,14 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 				st = kIExpScaleDerivationOutOfDomain;
 			} else if (!softmax_width_in_domain(sc.c.q_b, sc.c.q_c, (uint64_t)pos + 1, &sc.peak)) {
 				st = kSoftmaxRowWidthOutOfDomain;
-			} else if (sc.c.q_ln2 < 1 || sc.c.q_ln2 > sc.c.q_b) {
+			} else if (sc.c.q_ln2 < 1) {
 				// q_ln2 == 0: every element's construction is refused by the reference
-				// (IExpConstruct's q_ln2 >= 1 check) -> SoftmaxKernelRefused
+				// (IExpConstruct's q_ln2 >= 1 check) -> SoftmaxKernelRefused.
+				// The attention kernel's 32-bit element form also needs q_ln2 <= q_b; that holds
+				// for every constant triple iexp_scale_constants returns and needs no test here:
+				// q_ln2 = floor(LN2_Q * r / 2^s) and q_b = floor(B_Q * r / 2^s) with the same
+				// unsigned reciprocal r and the same shift s, and LN2_Q < B_Q, so the floors are
+				// ordered the same way.
 				st = kSoftmaxKernelRefused;
 			}
 		}
@@ -455,7 +463,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		}
 	}
 	if ((lw.b_k != nullptr || lw.b_v != nullptr) && !bias_gate) {
-		set_status(b, r, kRoundingDivideExponentOutOfDomain);
+		set_status(b, r, kRoundingDivideExponentOutOfDomain, kSiteKv, b.layer);
 		return;
 	}
 
@@ -492,14 +500,16 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		*vdst = (int8_t)clamp127(vraw);
 	}
 	sat = block_sum_i64(sat, red, d.kv_hidden <= (1 << 20));   // also orders the sq / sk writes before the reads below
-	if (threadIdx.x == 0) b.sat[r] += (unsigned long long)sat;
 	if (lw.b_k != nullptr || lw.b_v != nullptr) {
+		// (a bias term outside int64 refuses the row before anything lands, so before anything
+		// could count as saturated: LandTokenKVRow, forward_sites.cpp:1281-1418)
 		kv_bad = __syncthreads_or(kv_bad);
 		if (kv_bad != 0) {
-			set_status(b, r, kBiasReconcileProductOutOfDomain);
+			set_status(b, r, kBiasReconcileProductOutOfDomain, kSiteKv, b.layer);
 			return;
 		}
 	}
+	if (threadIdx.x == 0) b.sat[r] += (unsigned long long)sat;
 
 	// RoPE: interleaved pairs (2i, 2i+1), table row = position
 	int8_t* qrot = b.qrot + (size_t)r * H;
@@ -549,7 +559,7 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 		if (b.xs != nullptr) { /* q scale is consumed only through smc */ }
 		for (int h = 0; h < d.kv_heads; ++h) {
 			if (st_kv[h] != kOk) {
-				atomicCAS(&b.status[r], 0, st_kv[h]);
+				atomicCAS(&b.status[r], 0, pack_status(st_kv[h], kSiteSoftmaxConsts, b.layer));
 				break;
 			}
 		}
@@ -575,7 +585,7 @@ k_ctx_funnel(RowBatch b, Dims d, const LayerDev* layer) {
 	if (row_refused(red)) return;
 	const FunnelParams fp = funnel_finish(mx, fold_ctx);
 	if (fp.status != kOk) {
-		set_status(b, r, fp.status);
+		set_status(b, r, fp.status, kSiteCtx, b.layer);
 		return;
 	}
 	int8_t* out = b.ctx + (size_t)r * n;
@@ -713,6 +723,7 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	if (row_refused(red)) return;
 	const FunnelParams fp = funnel_finish(mx, fold_o);
 	int32_t st = fp.status;
+	int site = kSiteO;
 	long long ssq = 0;
 	if (st == kOk) {
 		const Coder cd = make_coder(fp.r, fp.s);
@@ -721,14 +732,16 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 			for (int i = threadIdx.x; i < n; i += blockDim.x) so[i] = code_of(load_wide(b, r, i), cd);
 			__syncthreads();
 		}
+		site = kSiteAttnRes;
 		st = block_residual(so, vec ? wraw : nullptr, cd, fp.out, vec ? sx : b.x + (size_t)r * n, xs, n, r_h,
 		                    fold_res, wide, b.a + (size_t)r * n, sa, &b.as[r], lut, red, &ssq);
 	}
 	if (st == kOk) {
 		// (the norm's first barrier, in its sum, also separates the passes above from its own)
+		site = kSiteMlpNorm;
 		st = block_rmsnorm(sa, vec ? sg : lw.g_mlp, n, c_norm, wide, b.nrm + (size_t)r * n, &b.ns[r], lut, red, &ssq);
 	}
-	set_status(b, r, st);
+	set_status(b, r, st, site, b.layer);
 }
 
 // down-projection funnel -> MLP residual -> (next layer's attention RMSNorm)
@@ -770,6 +783,7 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	if (row_refused(red)) return;
 	const FunnelParams fp = funnel_finish(mx, fold_down);
 	int32_t st = fp.status;
+	int site = kSiteDown, site_layer = b.layer;
 	long long ssq = 0;
 	if (st == kOk) {
 		const Coder cd = make_coder(fp.r, fp.s);
@@ -778,14 +792,21 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 			for (int i = threadIdx.x; i < n; i += blockDim.x) sd[i] = code_of(load_wide(b, r, i), cd);
 			__syncthreads();
 		}
+		site = kSiteMlpRes;
 		st = block_residual(sd, vec ? wraw : nullptr, cd, fp.out, vec ? sa : b.a + (size_t)r * n, rs, n, r_h,
 		                    fold_res, wide, b.x + (size_t)r * n, sx, &b.xs[r], lut, red, &ssq);
 	}
-	if (st == kOk && next_layer != nullptr) {
-		st = block_rmsnorm(sx, vec ? sg : next_layer->g_attn, n, c_norm, wide,
-		                   b.nrm + (size_t)r * n, &b.ns[r], lut, red, &ssq);
+	if (st == kOk) {
+		// the layer is complete for this row: x / xs hold its stream, whatever the next layer does
+		if (threadIdx.x == 0) b.done[r] += 1;
+		if (next_layer != nullptr) {
+			site = kSiteAttnNorm;
+			site_layer = b.layer + 1;
+			st = block_rmsnorm(sx, vec ? sg : next_layer->g_attn, n, c_norm, wide,
+			                   b.nrm + (size_t)r * n, &b.ns[r], lut, red, &ssq);
+		}
 	}
-	set_status(b, r, st);
+	set_status(b, r, st, site, site_layer);
 }
 
 // The activation row is the longest a row kernel walks (intermediate width, three codes per
@@ -866,10 +887,14 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	const FunnelParams fg = funnel_finish(mxg, fold_g);
 	const FunnelParams fu = funnel_finish(mxu, fold_u);
 	int32_t st = fg.status != kOk ? fg.status : fu.status;
-	if (st == kOk && !silu_scale_in_domain(fg.out)) st = kSiluScaleOutOfDomain;
+	int site = fg.status != kOk ? kSiteGate : kSiteUp;
+	if (st == kOk && !silu_scale_in_domain(fg.out)) {
+		st = kSiluScaleOutOfDomain;
+		site = kSiteSilu;
+	}
 	if (st != kOk) {
 		stage_wait();
-		set_status(b, r, st);
+		set_status(b, r, st, site, b.layer);
 		return;
 	}
 	const int ge = (int)fg.out.e;
@@ -904,7 +929,7 @@ k_act(RowBatch b, Dims d, const LayerDev* layer, const int32_t* silu_table) {
 	const unsigned long long mx = block_max_u64((unsigned long long)lmax, red);
 	const FunnelParams fp = funnel_finish(mx, fold_act);
 	if (fp.status != kOk) {
-		set_status(b, r, fp.status);
+		set_status(b, r, fp.status, kSiteAct, b.layer);
 		return;
 	}
 	int8_t* out = b.act + (size_t)r * n;

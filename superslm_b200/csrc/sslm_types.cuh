@@ -77,6 +77,22 @@ struct RowDesc {
 	int32_t token;              // token id to embed when the row starts a token
 };
 
+// Where in the reference's program order a row was refused. A row's status word holds the
+// reference status in bits 0..7, the site in bits 8..15 and the layer index + 1 in bits 16..31;
+// any non-zero word means "refused". The host needs the place twice: a decode step that fails in
+// a later layer of its budget has committed the layers before it (the reference commits layer by
+// layer, src/forward/forward_sites.cpp:1989-2009), and when several rows of a prefill chunk fail,
+// the reference reports the failure that comes first in ITS loop order (layer, stage, token).
+enum Site : int32_t {
+	kSiteEmbed = 0, kSiteAttnNorm, kSiteQ, kSiteKv, kSiteRope, kSiteSoftmaxConsts, kSiteSoftmax, kSiteCtx, kSiteO,
+	kSiteAttnRes, kSiteMlpNorm, kSiteGate, kSiteUp, kSiteSilu, kSiteAct, kSiteDown, kSiteMlpRes, kSiteFinalNorm,
+	kSiteLogits
+};
+__host__ __device__ __forceinline__ int32_t pack_status(int32_t st, int site, int layer) {
+	return st == 0 ? 0 : (st & 0xFF) | (site << 8) | ((layer + 1) << 16);
+}
+__host__ __device__ __forceinline__ int32_t status_code(int32_t word) { return word & 0xFF; }
+
 struct SoftmaxConsts {
 	IExpConsts c;
 	int64_t peak;
@@ -98,7 +114,9 @@ struct RowBatch {
 	int8_t* act; Scale* acts;    // SwiGLU output codes                 [m, inter]
 	unsigned long long* rowmax;  // [m][4] max |x| slots: 0 q/o/down, 1 gate, 2 up, 3 ctx (self-clearing)
 	SoftmaxConsts* smc;          // [m][kv_heads]
-	int32_t* status;             // [m] first failing site's status, 0 = ok
+	int32_t* status;             // [m] first failing site's packed status word (pack_status), 0 = ok
+	int32_t* done;               // [m] layers this call completed for the row
+	int layer;                   // index of the layer the current launch works on
 	unsigned long long* sat;     // [m] K/V landing saturation events of this call
 	int8_t* lora_u;              // [m][3][kMaxLoraRank] clamped u = fold(A x) per projection slot of the current GEMM
 	unsigned long long* best;    // [m] packed (logit, index) argmax key

@@ -150,7 +150,8 @@ def transcribe(path: str) -> dict:
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    from oracle import harness
+    root = sys.argv[1] if len(sys.argv) > 1 else harness.REF_ROOT
     out = {}
     for h in HEADERS:
         out[os.path.basename(h)] = transcribe(os.path.join(root, h))

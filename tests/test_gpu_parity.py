@@ -202,16 +202,28 @@ def test_per_row_adapters_in_one_batch(gpu_lib):
 PROJ7 = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
 
 
+def cpu_gemm(x, w):
+    """int64 accumulators [M, N]: the reference's own GEMM where it travels with the tree (it is
+    vectorised), else the plain-C restatement."""
+    M, K = x.shape
+    N = w.shape[0]
+    acc = np.zeros((M, N), dtype=np.int64)
+    shim = H.ref_shim()
+    if shim is not None:
+        shim.refshim_gemm(x.ctypes.data, w.ctypes.data, M, K, N, acc.ctypes.data)
+    else:
+        H.port().osc_gemm(x.ctypes.data, w.ctypes.data, M, K, N, acc.ctypes.data)
+    return acc
+
+
 def oracle_linear(x, w, fold, in_scales, site):
     port = H.port()
     M, K = x.shape
     N = w.shape[0]
-    acc = np.zeros((M, N), dtype=np.int64)
-    port.osc_gemm(x.ctypes.data, w.ctypes.data, M, K, N, acc.ctypes.data)
+    acc = cpu_gemm(x, w)
     folded = np.empty_like(acc)
-    for j in range(N):
-        f = fold[j]
-        folded[:, j] = [port.osc_fold(int(a), int(f[0]), int(f[1]), int(f[2])) for a in acc[:, j]]
+    fold = np.ascontiguousarray(fold, dtype=np.int32)
+    port.osc_fold_matrix(acc.ctypes.data, M, N, fold.ctypes.data, folded.ctypes.data)
     codes = np.zeros((M, N), dtype=np.int8)
     scales = np.zeros((M, 2), dtype=np.int64)
     status = np.zeros(M, dtype=np.int32)
@@ -248,18 +260,30 @@ def tc_launches(lib):
     return n.value
 
 
+def tc_variants(lib):
+    """launches per tile shape of the tensor-core kernel: [128x64, 128x128, 256x64, 256x128]"""
+    f = lib.dll.sslm_b200_tc_variant_counts
+    f.argtypes = [C.POINTER(C.c_uint64), C.c_int32]
+    c = (C.c_uint64 * 4)()
+    assert f(c, 4) == 0
+    return list(c)
+
+
 LINEAR_CASES = [  # (K, N, M): every M class, ragged N, the real 1.5B K/V and hidden shapes
     (1536, 256, 1), (1536, 256, 16), (1536, 256, 128), (1536, 1536, 1), (1536, 1536, 5), (1536, 1536, 130),
     (8960, 1536, 1), (8960, 1536, 16), (1536, 8960, 2), (1536, 8960, 64), (128, 77, 3), (16, 1, 1), (256, 333, 257),
-    (1536, 4099, 9),
+    (1536, 4099, 9), (1536, 8960, 1), (896, 4864, 1), (4864, 896, 3), (2048, 11008, 1), (11008, 2048, 8), (48, 50, 7),
     # few output tiles and a long K: the tensor-core kernel splits K across blocks (3 to 16 slices)
     (8960, 1536, 256), (8960, 100, 200), (1536, 2048, 256), (4096, 64, 129),
+    # the shapes of the serving benchmark's step (256 rows) and of prefill chunks: the 256-row tiles
+    (1536, 17920, 256), (1536, 8960, 512), (256, 9600, 200), (1536, 1536, 512),
 ]
+# which tile shape each case must run on with tensor cores requested (index into tc_variants)
+LINEAR_VARIANT = {(1536, 17920, 256): 3, (1536, 8960, 512): 3, (256, 9600, 200): 2, (1536, 1536, 512): 1,
+                  (1536, 256, 16): 0, (1536, 1536, 130): 0}
 
 
-@pytest.mark.parametrize("K,N,M", LINEAR_CASES)
-@pytest.mark.parametrize("use_tc", [0, 1])
-def test_linear_layer_sweep(gpu_lib, K, N, M, use_tc):
+def linear_case_inputs(K, N, M):
     rng = np.random.default_rng(K * 131 + N * 17 + M)
     x = rng.integers(-127, 128, (M, K)).astype(np.int8)
     w = rng.integers(-127, 128, (N, K)).astype(np.int8)
@@ -268,16 +292,73 @@ def test_linear_layer_sweep(gpu_lib, K, N, M, use_tc):
     fold[:, 2] = rng.integers(8, 21, N)
     fold[::7, 0] = 1                                  # some identity channels
     in_scales = np.stack([rng.integers(1 << 30, 1 << 31, M), np.full(M, -37)], axis=1).astype(np.int64)
+    return x, w, fold, in_scales
+
+
+def check_linear(gpu_lib, K, N, M, use_tc):
+    x, w, fold, in_scales = linear_case_inputs(K, N, M)
     site = (1090717716, -44)
     want = oracle_linear(x, w, fold, in_scales, site)
-    before = tc_launches(gpu_lib)
+    before, vbefore = tc_launches(gpu_lib), tc_variants(gpu_lib)
     got = gpu_linear(gpu_lib, x, w, fold, in_scales, site, use_tc)
     # no silent substitution: M > 8 with tensor cores requested must run the tcgen05 kernel
     assert tc_launches(gpu_lib) - before == (1 if (use_tc and M > 8) else 0)
+    if use_tc and (K, N, M) in LINEAR_VARIANT:
+        delta = [a - b for a, b in zip(tc_variants(gpu_lib), vbefore)]
+        assert delta[LINEAR_VARIANT[(K, N, M)]] == 1 and sum(delta) == 1, delta
     assert (got[3] == want[3]).all()
     assert (got[0].astype(np.int64) == want[0]).all()
     assert (got[1] == want[1]).all()
     assert (got[2] == want[2]).all()
+
+
+@pytest.mark.parametrize("K,N,M", LINEAR_CASES)
+@pytest.mark.parametrize("use_tc", [0, 1])
+def test_linear_layer_sweep(gpu_lib, K, N, M, use_tc):
+    check_linear(gpu_lib, K, N, M, use_tc)
+
+
+@pytest.mark.parametrize("K,N,M", [(1536, 8960, 2048), (8960, 1536, 2048), (1536, 1536, 2048), (1536, 256, 2048),
+                                   (8960, 1536, 512), (1536, 256, 512)])
+def test_linear_layer_prefill_shapes(gpu_lib, K, N, M):
+    """The 2048- and 512-row cells of the standalone linear-layer grid (tensor-core kernel)."""
+    check_linear(gpu_lib, K, N, M, 1)
+
+
+@pytest.mark.parametrize("M,use_tc", [(1, 0), (4, 0), (16, 1), (128, 1), (300, 1)])
+@pytest.mark.parametrize("want_rows", [False, True])
+def test_vocabulary_head_form(gpu_lib, M, use_tc, want_rows):
+    """K 1536 x N 151936, the logits form: exact int32 rows, narrowing check and the greedy token with
+    the lowest-index rule on planted ties (two identical weight rows that hold the row maximum)."""
+    K, N = 1536, 151936
+    rng = np.random.default_rng(1000 + M)
+    x = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    w = rng.integers(-127, 128, (N, K)).astype(np.int8)
+    # the largest possible logit of row 0, twice: channel 90001 and channel 131 tie; plus an exact
+    # duplicate pair elsewhere for the other rows
+    peak = np.where(x[0] >= 0, 127, -127).astype(np.int8)
+    w[90001] = peak
+    w[131] = peak
+    w[N - 1] = w[70000]
+    f = gpu_lib.dll.sslm_b200_logits
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+    rows = np.zeros((M, N), dtype=np.int32) if want_rows else None
+    toks = np.zeros(M, dtype=np.int32)
+    assert f(x.ctypes.data, w.ctypes.data, M, N, K, use_tc, rows.ctypes.data if want_rows else None, toks.ctypes.data) == 0
+    acc = cpu_gemm(x, w)
+    shim = H.ref_shim()
+    for m in range(M):
+        if shim is not None:      # the reference's own narrowing and argmax
+            narrow = np.zeros(N, dtype=np.int32)
+            assert shim.refshim_narrow_row(acc[m].ctypes.data, N, narrow.ctypes.data) == 0
+            want_tok = shim.refshim_argmax(narrow.ctypes.data, N)
+        else:
+            narrow = acc[m].astype(np.int32)
+            want_tok = int(np.argmax(narrow))
+        assert toks[m] == want_tok, m
+        if want_rows:
+            assert (rows[m] == narrow).all(), m
+    assert toks[0] == 131
 
 
 @pytest.mark.parametrize("K,N,M", [(1536, 512, 256), (256, 384, 40), (1536, 300, 130)])
@@ -399,4 +480,52 @@ def test_option_g_flag_is_ignored_like_the_reference(gpu_lib):
     s.prefill(prompt, 16)
     assert s.decode(8, sh.layers) == ptoks
     assert abi.parse_save_blob(s.save(), sh.hidden)["kv"] == ps.kv.tobytes()
+    eng.close()
+
+
+def test_sequences_of_two_pools_in_one_decode_call(gpu_lib):
+    """One sslm_decode_step over sequences that live in different KV pools of the same model (the
+    reference takes them: every sequence carries its own block). Pools of different sizes, the
+    handles interleaved; every sequence must equal its own single-sequence run on the CPU."""
+    sh = A.SHAPES["small"]
+    art = A.build_synthetic_model("small", 2027, 96)
+    lens = [21, 5, 40, 33, 12]
+    prompts = [A.stream_uniform(300 + i, "p", n, 0, sh.vocab - 1) for i, n in enumerate(lens)]
+    want = []
+    for p in prompts:
+        toks, ps = run_port(art, p, 5)
+        want.append((toks, ps.kv.tobytes(), ps.s.kv_saturation_count))
+    eng = abi.Engine(gpu_lib, art, blocks=2, max_batch=8, max_chunk=64)
+    # a second, larger pool on the same model
+    need = eng.block_size * 5 + gpu_lib.sslm_kv_pool_overhead_size(eng.model, 5)
+    raw, ptr = abi._aligned_buffer(need)
+    pool2 = abi._H()
+    assert gpu_lib.sslm_kv_pool_create(eng.model, ptr, need, 5, C.byref(pool2)) == 0
+    seqs = []
+    for i in range(len(lens)):
+        if i % 2 == 0:
+            s = abi.Sequence.__new__(abi.Sequence)
+            s.eng, s.handle = eng, abi._H()
+            assert gpu_lib.sslm_seq_create(eng.model, C.byref(pool2), C.byref(s.handle)) == 0
+            eng.seqs.append(s)
+        else:
+            s = eng.new_seq()
+        seqs.append(s)
+    for s, p in zip(seqs, prompts):
+        s.prefill(p, 64)
+    got = [[] for _ in lens]
+    while len(got[0]) < 5:
+        st, toks = eng.decode_step(seqs, 2)
+        assert st == 0
+        for g, t in zip(got, toks):
+            if t >= 0:
+                g.append(t)
+    for i, s in enumerate(seqs):
+        blob = abi.parse_save_blob(s.save(), sh.hidden)
+        assert got[i] == want[i][0], i
+        assert blob["kv"] == want[i][1], i
+        assert blob["kv_saturation_count"] == want[i][2], i
+    for s in list(seqs):
+        s.release()
+    assert gpu_lib.sslm_kv_pool_destroy(pool2) == 0
     eng.close()

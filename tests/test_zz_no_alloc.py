@@ -72,6 +72,11 @@ def test_resident_linear_matches_the_allocating_entry_twice_in_a_row(gpu_lib):
         got = resident_entry(gpu_lib, torch, x, w, fold, in_scales)
         for a, b, what in zip(got, want, ("folded", "codes", "scales", "status")):
             assert (a == b).all(), (what, seed)
+        # both entry points run the same projection kernel, so the CPU oracle is asked as well
+        from tests.test_gpu_parity import oracle_linear
+        cpu = oracle_linear(x, w, fold, in_scales, SITE)
+        for a, b, what in zip(got, cpu, ("folded", "codes", "scales", "status")):
+            assert (np.asarray(a, dtype=np.int64) == np.asarray(b, dtype=np.int64)).all(), ("oracle", what, seed)
 
 
 def test_resident_linear_refuses_more_rows_than_its_scratch_holds(gpu_lib):
