@@ -245,6 +245,12 @@ SSLM_API sslm_status sslm_b200_tc_stats(uint64_t* launches, uint64_t* refusals, 
  * 128 x 64, 128 x 128, 256 x 64, 256 x 128. Lets a test assert which variant served a shape. */
 SSLM_API sslm_status sslm_b200_tc_variant_counts(uint64_t* counts, int32_t n);
 
+/* Attention cuts a row along its context width into slices that run as the blocks of one
+ * thread-block cluster. splits = 1, 2, 4, 8 or 16 fixes the slices per kv head of later calls
+ * (rounded down to a power of two, limited by the row's width); 0 restores the automatic choice.
+ * Results do not depend on it. For tuning and for tests that walk every cut. */
+SSLM_API sslm_status sslm_b200_set_attention_splits(int32_t splits);
+
 /* The vocabulary head on host buffers: logits[m, n] = sum_k x[m,k] w[n,k] (int32, no fold), and per
  * row the greedy token = the lowest index of the row's maximum (LogitsSite + NarrowRowChecked +
  * ArgmaxLowestIndexTieBreak, src/forward/forward_sites.cpp:2412-2437). out_logits ([M,N], may be

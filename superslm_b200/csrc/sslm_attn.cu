@@ -1,8 +1,10 @@
 // Integer i-exp softmax attention over the paged int8 KV pool, staged through shared
 // memory, with both contractions on the tensor cores (mma.sync m16n8k32, exact int32
-// accumulation). One block of head_dim/16 warps owns one (row, kv head) and serves every q head
-// of the GQA group from one pass over the K and V pages, so each K / V byte of the
-// sequence leaves HBM once per kv head.
+// accumulation). A row (one token's q heads over positions 0..pos) is cut by kv head and along
+// the context width; a block of head_dim/16 warps owns one slice of one kv head and serves every
+// q head of the GQA group from one pass over its K and V pages, so each K / V byte of the
+// sequence leaves HBM once per kv head. The blocks of a row form a thread-block cluster and
+// exchange maxima, sums and partial contexts through distributed shared memory (k_attention).
 //
 //   stage 1  scores[g][k] = q_rot[g] . K[k]      A = the group's q rows (heads in the M
 //            dimension), B = 8 K rows per MMA straight from the page (16-byte loads; the
@@ -18,6 +20,8 @@
 // (src/forward/forward_sites.cpp:1858-1897), SoftmaxRowQ15 (src/intmath.cpp:796-901) and
 // GemmProbQ15Accumulate (src/matmul.cpp:522-538).
 #include <cuda_runtime.h>
+
+#include <atomic>
 
 #include "sslm_kernels.h"
 
@@ -115,81 +119,148 @@ __device__ __forceinline__ void load_row_words(const int8_t* row, int c, uint32_
 	}
 }
 
-struct AttnSmem {
-	int64_t* pbase;       // [wp/16] byte offset of each page inside a plane
-	int32_t* sc;          // [G][wp] scores
-	uint8_t* pl;          // [G][wp] low byte of the Q15 probability
-	uint8_t* ph;          // [G][wp] high byte
-	unsigned long long* red;   // [8 heads][warps] partials
-	int* flag;            // [4] single values handed to the whole block
-};
-__host__ __device__ inline size_t attn_smem_bytes(int group, int wp) {
-	return (size_t)wp / 16 * 8 + (size_t)group * wp * 6 + 8 * kAttnMaxWarps * 8 + 16;
+// ---- thread-block cluster helpers (distributed shared memory)
+__device__ __forceinline__ uint32_t cluster_rank() {
+	uint32_t r;
+	asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+	return r;
 }
-__device__ __forceinline__ AttnSmem carve(unsigned char* smem, int group, int wp) {
+// the address, in the cluster's shared window, of `local` (a shared-memory address of this
+// block) inside the block of rank `rank`
+__device__ __forceinline__ uint32_t peer_addr(const void* local, uint32_t rank) {
+	uint32_t a = (uint32_t)__cvta_generic_to_shared(local), out;
+	asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(a), "r"(rank));
+	return out;
+}
+__device__ __forceinline__ uint32_t peer_ld32(uint32_t addr) {
+	uint32_t v;
+	asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+	return v;
+}
+__device__ __forceinline__ unsigned long long peer_ld64(uint32_t addr) {
+	unsigned long long v;
+	asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+	return v;
+}
+// Hardware barrier over all threads of all blocks of the cluster: everything written to shared
+// memory before it is visible to every block after it. Every block of a cluster executes every
+// barrier of the kernel (no early return), so nothing can wait for a block that left.
+__device__ __forceinline__ void cluster_sync_all() {
+	asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+	asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// What one block keeps in shared memory. `cp` = positions a block can hold (a multiple of 64).
+struct AttnSmem {
+	int64_t* pbase;       // [cp/16] byte offset of each of the block's pages inside a plane
+	int32_t* sc;          // [G][cp] scores, later (shift, remainder) of each element
+	uint8_t* pl;          // [G][cp] low byte of the Q15 probability
+	uint8_t* ph;          // [G][cp] high byte
+	unsigned long long* red;   // [8 heads][warps] partials inside the block
+	// what the other blocks of the cluster read (one block = one slice of one kv head's row):
+	int32_t* x_max;       // [8] largest score per head in this slice
+	unsigned long long* x_sum;   // [8] sum of the slice's exponentials per head
+	int32_t* x_ctx;       // [8][HD] this slice's share of P.V per head
+	uint32_t* x_flags;    // [0] the slice met an element the reference refuses, [1] largest folded |ctx| of the
+	                      //     channels this block reduced, [2] this block sits the row out
+};
+__host__ __device__ inline size_t attn_smem_bytes(int group, int cp, int hd) {
+	return (size_t)cp / 16 * 8 + (size_t)group * cp * 6 + 8 * kAttnMaxWarps * 8 + 8 * 4 + 8 * 8 + (size_t)8 * hd * 4 + 16;
+}
+__device__ __forceinline__ AttnSmem carve(unsigned char* smem, int group, int cp, int hd) {
 	AttnSmem s;
 	s.pbase = (int64_t*)smem;
-	s.sc = (int32_t*)(smem + (size_t)wp / 16 * 8);
-	s.pl = (uint8_t*)(s.sc + (size_t)group * wp);
-	s.ph = s.pl + (size_t)group * wp;
-	s.red = (unsigned long long*)(s.ph + (size_t)group * wp);
-	s.flag = (int*)(s.red + 8 * kAttnMaxWarps);
+	s.sc = (int32_t*)(smem + (size_t)cp / 16 * 8);
+	s.pl = (uint8_t*)(s.sc + (size_t)group * cp);
+	s.ph = s.pl + (size_t)group * cp;
+	s.red = (unsigned long long*)(s.ph + (size_t)group * cp);
+	s.x_sum = s.red + 8 * kAttnMaxWarps;
+	s.x_max = (int32_t*)(s.x_sum + 8);
+	s.x_ctx = s.x_max + 8;
+	s.x_flags = (uint32_t*)(s.x_ctx + 8 * hd);
 	return s;
 }
 // ask for the line at p to be brought into L2; nothing waits for it
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
-// HD = head_dim (32, 64 or 128); wp = padded width, a multiple of 64
+// One attention row = one token of one sequence, all its q heads over the positions 0..pos.
+// The row is cut two ways: by kv head (a block serves the q heads of one GQA group, so K and V
+// bytes are read once per kv head) and along the context width into `splits` slices of
+// `slice_len(width)` positions. The blocks of a row -- kv_heads x splits of them when
+// `whole_row`, else the `splits` of one kv head -- form one thread-block cluster and meet three
+// times through distributed shared memory, which is what the exact integer softmax needs
+// (SoftmaxRowQ15 is not mergeable online: an element's exponential depends on the row maximum
+// through floor divisions):
+//   1  scores of the slice (tensor cores), slice maximum per head      -> exchange: row maximum
+//   2  e_k per element, slice sum per head, refusal flag               -> exchange: row total
+//   3  p_k = (e_k << 15) / total, the slice's share of P.V (tensor cores) -> exchange: the shares
+//      are added per channel (integer adds: any order), then folded per head
+// and, when the cluster holds the whole row, a fourth time for the attention-context funnel
+// (forward_sites.cpp:1898-1903): largest folded magnitude of the row -> codes and carried scale,
+// so that no separate funnel kernel runs. HD = head_dim (32, 64 or 128); threads = 2 * HD.
 template <int HD>
-__global__ void __launch_bounds__(2 * HD, HD == 128 ? 4 : 8)
-k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int wp, int reverse_rows) {
+__global__ void __launch_bounds__(2 * HD)
+k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int cp, int splits, int whole_row,
+            int reverse_rows) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	// blocks start in index order: with reverse_rows the last (widest) rows of a prefill chunk go first
-	const int r = reverse_rows ? (int)gridDim.y - 1 - (int)blockIdx.y : (int)blockIdx.y, kvh = blockIdx.x;
+	const int r = reverse_rows ? (int)gridDim.y - 1 - (int)blockIdx.y : (int)blockIdx.y;
+	const int kvh = (int)blockIdx.x / splits, split = (int)blockIdx.x % splits;
 	constexpr int kAttnThreads = 2 * HD, kAttnWarps = kAttnThreads / 32;
 	const int G = d.heads / d.kv_heads;
 	const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
 	const int g = lane >> 2, c = lane & 3;
-	const AttnSmem s = carve(smem, G, wp);
+	const AttnSmem s = carve(smem, G, cp, HD);
+	const uint32_t my_rank = cluster_rank();
+	const uint32_t kv_rank0 = my_rank - (uint32_t)split;     // rank of this kv head's first slice
+	const uint32_t cluster_blocks = whole_row ? (uint32_t)(d.kv_heads * splits) : (uint32_t)splits;
 	// Ahead of the kernel that lands this step's K / V rows (it may still be running): the row
 	// descriptor and the page table were uploaded before the step's first launch, and every K / V
 	// row but the newest was written by earlier steps. So the page offsets are staged now, and
-	// the old K rows are asked into L2 while that kernel, which moves little data, finishes.
+	// the slice's old K rows are asked into L2 while that kernel, which moves little data, finishes.
 	const int width = b.rows[r].pos + 1;
-	const int w64 = (width + 63) & ~63;
+	// slice length: the row's width over the slices, rounded up to whole 64-position groups
+	const int slen = ((width + splits - 1) / splits + 63) & ~63;
+	const int p0 = split * slen;                                   // first position of this slice
+	const int n = max(0, min(slen, width - p0));                   // positions in it
+	const int n64 = (n + 63) & ~63;
 	const int8_t* kplane = pool.base + kv_plane_offset(d, pool, layer_index, kvh, 0);
 	const int8_t* vplane = pool.base + kv_plane_offset(d, pool, layer_index, kvh, 1);
-	const int npages = (width + kPageTokens - 1) / kPageTokens;
+	const int npages = (n + kPageTokens - 1) / kPageTokens;
 	{
-		const int32_t* pages = b.rows[r].pages;
+		const int32_t* pages = b.rows[r].pages + p0 / kPageTokens;
 		for (int j = t; j < npages; j += kAttnThreads) s.pbase[j] = (int64_t)pages[j] * (kPageTokens * HD);
 	}
-	int32_t fi = 1, fm = 0, fs = 0;                // this lane's head: the context fold (weights)
-	if (g < G) {
-		const int32_t* f = layer->f_ctx + 3 * (kvh * G + g);
-		fi = f[0]; fm = f[1]; fs = f[2];
-	}
+	const FunnelFold fold_ctx = funnel_prefold(nullptr, 0, layer->c_ctx);
 	__syncthreads();
 	constexpr int kRowsPerLine = 128 / HD;
-	for (int pos = t * kRowsPerLine; pos < width - 1; pos += kAttnThreads * kRowsPerLine)
+	for (int pos = t * kRowsPerLine; pos < n - (p0 + n == width ? 1 : 0); pos += kAttnThreads * kRowsPerLine)
 		prefetch_l2(kplane + s.pbase[pos >> 4] + (pos & 15) * HD);
 	pdl_wait();
 	pdl_release();
-	// one thread reads the row's status for everybody: the block of the row's other kv head may
-	// refuse the row at any moment, and the threads here must agree on leaving
-	if (t == 0) *s.flag = __ldcg(&b.status[r]);
+	// A row that an earlier site refused is sat out: no loads, zero contributions, but every
+	// barrier. One thread reads the word for the block; blocks of a cluster may see different
+	// words (another block can refuse the row while this one runs), which is harmless: a refused
+	// row's outputs are never used.
+	if (t == 0) s.x_flags[2] = __ldcg(&b.status[r]) != 0 ? 1u : 0u;
+	if (t < 8) {
+		s.x_max[t] = INT32_MIN;
+		s.x_sum[t] = 0ull;
+	}
+	if (t == 8) s.x_flags[0] = 0u;
+	if (t == 9) s.x_flags[1] = 0u;
 	const SoftmaxConsts smc = b.smc[(size_t)r * d.kv_heads + kvh];   // wanted after the scores; asked for now
 	__syncthreads();
-	if (*s.flag != 0) return;
+	const bool live = s.x_flags[2] == 0u;
 
 	// ---- stage 1: scores, 8 positions per MMA group, groups dealt round-robin to the warps
-	{
+	if (live) {
 		constexpr int NW = HD / 16;
 		uint32_t qw[NW];
 #pragma unroll
 		for (int j = 0; j < NW; ++j) qw[j] = 0;
 		if (g < G) load_row_words<HD>(b.qrot + (size_t)r * d.hidden + (size_t)(kvh * G + g) * HD, c, qw);
-		const int nblk = (width + 7) >> 3;
+		const int nblk = (n + 7) >> 3;
 		constexpr int U = 4;
 		for (int blk0 = warp * U; blk0 < nblk; blk0 += kAttnWarps * U) {
 			uint32_t kw[U][NW];
@@ -198,7 +269,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 				const int pos = (blk0 + u) * 8 + g;
 #pragma unroll
 				for (int j = 0; j < NW; ++j) kw[u][j] = 0;
-				if (pos < width)
+				if (pos < n)
 					load_row_words<HD>(kplane + s.pbase[pos >> 4] + (pos & 15) * HD, c, kw[u]);
 			}
 #pragma unroll
@@ -207,31 +278,34 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 #pragma unroll
 				for (int j = 0; j < NW / 2; ++j) mma_s8s8(acc, qw[2 * j], qw[2 * j + 1], kw[u][2 * j], kw[u][2 * j + 1]);
 				const int k = (blk0 + u) * 8 + c * 2;
-				if (g < G && blk0 + u < nblk) *(int2*)&s.sc[(size_t)g * wp + k] = make_int2(acc[0], acc[1]);
+				if (g < G && blk0 + u < nblk) *(int2*)&s.sc[(size_t)g * cp + k] = make_int2(acc[0], acc[1]);
 			}
 		}
 	}
 	__syncthreads();
 
-	// the softmax below moves no data: ask for this row's V pages (16 lines each) meanwhile
-	for (int ln = t; ln < npages * (kPageTokens * HD / 128); ln += kAttnThreads)
-		prefetch_l2(vplane + s.pbase[ln / (kPageTokens * HD / 128)] + (ln % (kPageTokens * HD / 128)) * 128);
+	// the softmax below moves no data: ask for this slice's V pages (16 lines each) meanwhile
+	if (live)
+		for (int ln = t; ln < npages * (kPageTokens * HD / 128); ln += kAttnThreads)
+			prefetch_l2(vplane + s.pbase[ln / (kPageTokens * HD / 128)] + (ln % (kPageTokens * HD / 128)) * 128);
 
 	// ---- stage 2: softmax. Each thread takes 4 consecutive positions of every head.
 	const IExpFast fx = iexp_fast_prepare(smc);
 	int mx[8];
 #pragma unroll
 	for (int h = 0; h < 8; ++h) mx[h] = INT32_MIN;
-	for (int k4 = t * 4; k4 < width; k4 += kAttnThreads * 4) {
+	if (live) {
+		for (int k4 = t * 4; k4 < n; k4 += kAttnThreads * 4) {
 #pragma unroll
-		for (int h = 0; h < 8; ++h) {
-			if (h < G) {
-				const int4 v = *(const int4*)&s.sc[(size_t)h * wp + k4];
-				int m = v.x;
-				if (k4 + 1 < width) m = max(m, v.y);
-				if (k4 + 2 < width) m = max(m, v.z);
-				if (k4 + 3 < width) m = max(m, v.w);
-				mx[h] = max(mx[h], m);
+			for (int h = 0; h < 8; ++h) {
+				if (h < G) {
+					const int4 v = *(const int4*)&s.sc[(size_t)h * cp + k4];
+					int m = v.x;
+					if (k4 + 1 < n) m = max(m, v.y);
+					if (k4 + 2 < n) m = max(m, v.z);
+					if (k4 + 3 < n) m = max(m, v.w);
+					mx[h] = max(mx[h], m);
+				}
 			}
 		}
 	}
@@ -244,38 +318,46 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		}
 	}
 	__syncthreads();
+	if (t < G) {
+		int m = redi[t * kAttnWarps];
+		for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[t * kAttnWarps + w]);
+		s.x_max[t] = m;
+	}
+	cluster_sync_all();      // ---- exchange 1: every slice's maxima are up
 #pragma unroll
 	for (int h = 0; h < 8; ++h) {
-		int m = redi[h * kAttnWarps];
-#pragma unroll
-		for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[h * kAttnWarps + w]);
-		mx[h] = m;
+		if (h < G) {
+			int m = INT32_MIN;
+			for (int j = 0; j < splits; ++j) m = max(m, (int)peer_ld32(peer_addr(&s.x_max[h], kv_rank0 + (uint32_t)j)));
+			mx[h] = m;
+		}
 	}
-	__syncthreads();
 
 	unsigned long long tot[8];
 #pragma unroll
 	for (int h = 0; h < 8; ++h) tot[h] = 0;
 	bool bad = false;
-	for (int k4 = t * 4; k4 < width; k4 += kAttnThreads * 4) {
+	if (live) {
+		for (int k4 = t * 4; k4 < n; k4 += kAttnThreads * 4) {
 #pragma unroll
-		for (int h = 0; h < 8; ++h) {
-			if (h < G) {
-				const int4 v = *(const int4*)&s.sc[(size_t)h * wp + k4];
-				const int sv[4] = {v.x, v.y, v.z, v.w};
-				uint32_t parts[4];
+			for (int h = 0; h < 8; ++h) {
+				if (h < G) {
+					const int4 v = *(const int4*)&s.sc[(size_t)h * cp + k4];
+					const int sv[4] = {v.x, v.y, v.z, v.w};
+					uint32_t parts[4];
 #pragma unroll
-				for (int j = 0; j < 4; ++j) {
-					int64_t e;
-					const bool ok = iexp_fast((uint32_t)mx[h] - (uint32_t)sv[j], fx, &e, &parts[j]);
-					if (k4 + j < width) {
-						tot[h] += ok ? (unsigned long long)e : 0ull;
-						bad |= !ok;
+					for (int j = 0; j < 4; ++j) {
+						int64_t e;
+						const bool ok = iexp_fast((uint32_t)mx[h] - (uint32_t)sv[j], fx, &e, &parts[j]);
+						if (k4 + j < n) {
+							tot[h] += ok ? (unsigned long long)e : 0ull;
+							bad |= !ok;
+						}
 					}
+					// the score has done its work: its place now holds the element's (shift, remainder),
+					// which this same thread reads back in the probability pass
+					*(int4*)&s.sc[(size_t)h * cp + k4] = make_int4((int)parts[0], (int)parts[1], (int)parts[2], (int)parts[3]);
 				}
-				// the score has done its work: its place now holds the element's (shift, remainder),
-				// which this same thread reads back in the probability pass
-				*(int4*)&s.sc[(size_t)h * wp + k4] = make_int4((int)parts[0], (int)parts[1], (int)parts[2], (int)parts[3]);
 			}
 		}
 	}
@@ -291,119 +373,238 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 				s.red[h * kAttnWarps + warp] = (unsigned long long)l0 + ((unsigned long long)l1 << 24) + ((unsigned long long)l2 << 48);
 		}
 	}
-	if (__syncthreads_or(bad ? 1 : 0)) {
-		// the reference refuses the row (SoftmaxKernelRefusedAfterGateAccepted)
-		if (t == 0) atomicCAS(&b.status[r], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
-		return;
+	const int any_bad = __syncthreads_or(bad ? 1 : 0);
+	if (t < G) {
+		unsigned long long x = 0;
+		for (int w = 0; w < kAttnWarps; ++w) x += s.red[t * kAttnWarps + w];
+		s.x_sum[t] = x;
 	}
+	if (t == 0 && any_bad) s.x_flags[0] = 1u;
+	cluster_sync_all();      // ---- exchange 2: every slice's sums and refusal flags are up
+	// the reference refuses the whole row when any element of any head is out of bounds
+	// (SoftmaxKernelRefusedAfterGateAccepted): every block of the cluster learns it here
+	bool refused = false;
+	for (uint32_t j = 0; j < cluster_blocks; ++j) refused |= peer_ld32(peer_addr(&s.x_flags[0], j)) != 0u;
+	if (refused && my_rank == 0 && t == 0) atomicCAS(&b.status[r], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
 	float inv[8];
 #pragma unroll
 	for (int h = 0; h < 8; ++h) {
 		unsigned long long x = 0;
-#pragma unroll
-		for (int w = 0; w < kAttnWarps; ++w) x += s.red[h * kAttnWarps + w];
+		if (h < G)
+			for (int j = 0; j < splits; ++j) x += peer_ld64(peer_addr(&s.x_sum[h], kv_rank0 + (uint32_t)j));
 		tot[h] = x > 1ull ? x : 1ull;
 		inv[h] = 32768.0f / (float)tot[h];
 	}
-	// probabilities, zero beyond the width up to the next multiple of 64 (stage 3 reads whole pages)
-	for (int k4 = t * 4; k4 < w64; k4 += kAttnThreads * 4) {
+	const bool work = live && !refused;
+	// probabilities, zero beyond the slice up to the next multiple of 64 (stage 3 reads whole pages)
+	if (work) {
+		for (int k4 = t * 4; k4 < n64; k4 += kAttnThreads * 4) {
 #pragma unroll
-		for (int h = 0; h < 8; ++h) {
-			if (h < G) {
-				const int4 v = *(const int4*)&s.sc[(size_t)h * wp + k4];
-				const int sv[4] = {v.x, v.y, v.z, v.w};
-				uint32_t lo = 0, hi = 0;
+			for (int h = 0; h < 8; ++h) {
+				if (h < G) {
+					const int4 v = *(const int4*)&s.sc[(size_t)h * cp + k4];
+					const int sv[4] = {v.x, v.y, v.z, v.w};
+					uint32_t lo = 0, hi = 0;
 #pragma unroll
-				for (int j = 0; j < 4; ++j) {
-					if (k4 + j < width) {
-						const int64_t e = iexp_from_parts((uint32_t)sv[j], fx);
-						const uint32_t p = prob_q15(e, tot[h], inv[h]);
-						lo |= (p & 0xffu) << (8 * j);
-						hi |= (p >> 8) << (8 * j);
+					for (int j = 0; j < 4; ++j) {
+						if (k4 + j < n) {
+							const int64_t e = iexp_from_parts((uint32_t)sv[j], fx);
+							const uint32_t p = prob_q15(e, tot[h], inv[h]);
+							lo |= (p & 0xffu) << (8 * j);
+							hi |= (p >> 8) << (8 * j);
+						}
 					}
+					*(uint32_t*)&s.pl[(size_t)h * cp + k4] = lo;
+					*(uint32_t*)&s.ph[(size_t)h * cp + k4] = hi;
 				}
-				*(uint32_t*)&s.pl[(size_t)h * wp + k4] = lo;
-				*(uint32_t*)&s.ph[(size_t)h * wp + k4] = hi;
 			}
 		}
 	}
 	__syncthreads();
 
-	// ---- stage 3: ctx = P V. Lane column c owns page 4*grp + c of each 64-position group;
-	// its 16-byte row of the transposed page feeds two MMAs (positions 0..7 and 8..15).
+	// ---- stage 3: the slice's share of ctx = P V. Lane column c owns page 4*grp + c of each
+	// 64-position group; its 16-byte row of the transposed page feeds two MMAs (positions 0..7 and 8..15).
 	constexpr int NDB = 2;            // 8-channel blocks per warp
 	int accl[NDB][4], acch[NDB][4];
 #pragma unroll
 	for (int i = 0; i < NDB; ++i)
 #pragma unroll
 		for (int j = 0; j < 4; ++j) accl[i][j] = acch[i][j] = 0;
-	const int ngrp = w64 >> 6;
-	constexpr int UG = 2;
-	for (int grp0 = 0; grp0 < ngrp; grp0 += UG) {
-		int4 vv[UG][NDB];
-		int4 al[UG], ah[UG];
+	if (work) {
+		const int ngrp = n64 >> 6;
+		constexpr int UG = 2;
+		for (int grp0 = 0; grp0 < ngrp; grp0 += UG) {
+			int4 vv[UG][NDB];
+			int4 al[UG], ah[UG];
 #pragma unroll
-		for (int u = 0; u < UG; ++u) {
-			const int page = (grp0 + u) * 4 + c;
-			const bool live = page * kPageTokens < width;
-			al[u] = ah[u] = make_int4(0, 0, 0, 0);
-			if (g < G && live) {
-				al[u] = *(const int4*)&s.pl[(size_t)g * wp + page * kPageTokens];
-				ah[u] = *(const int4*)&s.ph[(size_t)g * wp + page * kPageTokens];
+			for (int u = 0; u < UG; ++u) {
+				const int page = (grp0 + u) * 4 + c;
+				const bool in = page * kPageTokens < n;
+				al[u] = ah[u] = make_int4(0, 0, 0, 0);
+				if (g < G && in) {
+					al[u] = *(const int4*)&s.pl[(size_t)g * cp + page * kPageTokens];
+					ah[u] = *(const int4*)&s.ph[(size_t)g * cp + page * kPageTokens];
+				}
+#pragma unroll
+				for (int i = 0; i < NDB; ++i) {
+					vv[u][i] = make_int4(0, 0, 0, 0);
+					if (in) {
+						const int ch = (warp * NDB + i) * 8 + g;
+						vv[u][i] = *(const int4*)(vplane + s.pbase[page] + ch * kPageTokens);
+					}
+				}
 			}
 #pragma unroll
-			for (int i = 0; i < NDB; ++i) {
-				vv[u][i] = make_int4(0, 0, 0, 0);
-				if (live) {
-					const int ch = (warp * NDB + i) * 8 + g;
-					vv[u][i] = *(const int4*)(vplane + s.pbase[page] + ch * kPageTokens);
+			for (int u = 0; u < UG; ++u) {
+#pragma unroll
+				for (int i = 0; i < NDB; ++i) {
+					const int4 v = vv[u][i];
+					mma_u8s8(accl[i], (uint32_t)al[u].x, (uint32_t)al[u].y, (uint32_t)v.x, (uint32_t)v.y);
+					mma_u8s8(accl[i], (uint32_t)al[u].z, (uint32_t)al[u].w, (uint32_t)v.z, (uint32_t)v.w);
+					mma_u8s8(acch[i], (uint32_t)ah[u].x, (uint32_t)ah[u].y, (uint32_t)v.x, (uint32_t)v.y);
+					mma_u8s8(acch[i], (uint32_t)ah[u].z, (uint32_t)ah[u].w, (uint32_t)v.z, (uint32_t)v.w);
 				}
 			}
 		}
-#pragma unroll
-		for (int u = 0; u < UG; ++u) {
-#pragma unroll
-			for (int i = 0; i < NDB; ++i) {
-				const int4 v = vv[u][i];
-				mma_u8s8(accl[i], (uint32_t)al[u].x, (uint32_t)al[u].y, (uint32_t)v.x, (uint32_t)v.y);
-				mma_u8s8(accl[i], (uint32_t)al[u].z, (uint32_t)al[u].w, (uint32_t)v.z, (uint32_t)v.w);
-				mma_u8s8(acch[i], (uint32_t)ah[u].x, (uint32_t)ah[u].y, (uint32_t)v.x, (uint32_t)v.y);
-				mma_u8s8(acch[i], (uint32_t)ah[u].z, (uint32_t)ah[u].w, (uint32_t)v.z, (uint32_t)v.w);
-			}
-		}
 	}
-	// per-head context fold (forward_sites.cpp:1889-1896), store, row max for the funnel
-	uint32_t lmax = 0;
+	// the slice's share, [head][channel], for the block that reduces that channel
 	if (g < G) {
-		const int head = kvh * G + g;
 #pragma unroll
 		for (int i = 0; i < NDB; ++i) {
-			int2 o;
-			o.x = fold(accl[i][0] + 256 * acch[i][0], fi, fm, fs);
-			o.y = fold(accl[i][1] + 256 * acch[i][1], fi, fm, fs);
 			const int ch = (warp * NDB + i) * 8 + c * 2;
-			*(int2*)(b.ctxw + (size_t)r * d.hidden + (size_t)head * HD + ch) = o;
-			const uint32_t ax = o.x < 0 ? 0u - (uint32_t)o.x : (uint32_t)o.x;
-			const uint32_t ay = o.y < 0 ? 0u - (uint32_t)o.y : (uint32_t)o.y;
-			lmax = max(lmax, max(ax, ay));
+			*(int2*)&s.x_ctx[g * HD + ch] = make_int2(accl[i][0] + 256 * acch[i][0], accl[i][1] + 256 * acch[i][1]);
+		}
+	}
+	cluster_sync_all();      // ---- exchange 3: every slice's share of P.V is up
+
+	// Slice `split` of a kv head reduces channels [split * HD / splits, ...) of each of its heads:
+	// add the shares, per-head context fold (forward_sites.cpp:1889-1896), row maximum.
+	const int per = (HD + splits - 1) / splits;                    // channels per block
+	const int ch0 = split * per, nch = max(0, min(per, HD - ch0));
+	// element e of this block = (head e / nch, channel ch0 + e % nch); at most G * HD <= 2 * threads * ... per block
+	uint32_t lmax = 0;
+	constexpr int kMaxMine = 4;                                   // G * per <= 8 * HD = 4 * threads
+	int32_t mine[kMaxMine];
+#pragma unroll
+	for (int q = 0; q < kMaxMine; ++q) {
+		mine[q] = 0;
+		const int e = q * kAttnThreads + t;
+		if (e < G * nch) {
+			const int h = e / nch, ch = ch0 + e - h * nch;
+			int32_t sum = 0;
+			for (int j = 0; j < splits; ++j) sum += (int32_t)peer_ld32(peer_addr(&s.x_ctx[h * HD + ch], kv_rank0 + (uint32_t)j));
+			const int32_t* f = layer->f_ctx + 3 * (kvh * G + h);
+			const int32_t o = fold(sum, f[0], f[1], f[2]);
+			mine[q] = o;
+			lmax = max(lmax, o < 0 ? 0u - (uint32_t)o : (uint32_t)o);
+			if (!whole_row && work) b.ctxw[(size_t)r * d.hidden + (size_t)(kvh * G + h) * HD + ch] = o;
 		}
 	}
 #pragma unroll
 	for (int o = 16; o > 0; o >>= 1) lmax = max(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
-	if (lane == 0 && lmax) atomicMax(&b.rowmax[(size_t)r * 4 + 3], (unsigned long long)lmax);
+	if (!whole_row) {
+		if (lane == 0 && lmax && work) atomicMax(&b.rowmax[(size_t)r * 4 + 3], (unsigned long long)lmax);
+		cluster_sync_all();  // nobody leaves while its shared memory may still be read
+		return;
+	}
+	// ---- the cluster holds the whole row: its funnel runs here
+	if (lane == 0 && lmax) atomicMax(&s.x_flags[1], lmax);
+	cluster_sync_all();      // ---- exchange 4: every block's largest folded magnitude is up
+	uint32_t rowmx = 0;
+	for (uint32_t j = 0; j < cluster_blocks; ++j) rowmx = max(rowmx, peer_ld32(peer_addr(&s.x_flags[1], j)));
+	const FunnelParams fp = funnel_finish((unsigned long long)rowmx, fold_ctx);
+	if (work) {
+		if (fp.status != kOk) {
+			if (my_rank == 0 && t == 0) atomicCAS(&b.status[r], 0, pack_status(fp.status, kSiteCtx, b.layer));
+		} else {
+			const Coder cd = make_coder(fp.r, fp.s);
+#pragma unroll
+			for (int q = 0; q < kMaxMine; ++q) {
+				const int e = q * kAttnThreads + t;
+				if (e < G * nch) {
+					const int h = e / nch, ch = ch0 + e - h * nch;
+					b.ctx[(size_t)r * d.hidden + (size_t)(kvh * G + h) * HD + ch] = code_of(mine[q], cd);
+				}
+			}
+			if (my_rank == 0 && t == 0) b.cs[r] = fp.out;
+		}
+	}
+	cluster_sync_all();      // nobody leaves while its shared memory may still be read
 }
 
-static int pad_width(int w) { return (w + 63) / 64 * 64; }
+static int pad64(int w) { return (w + 63) / 64 * 64; }
+constexpr int kAttnMaxSlice = 2048;      // positions one block holds at most
+
+struct AttnPlan {
+	int splits;       // slices along the width
+	int whole_row;    // the cluster spans every kv head of the row (the funnel is fused)
+	int cp;           // positions per block (shared-memory capacity)
+};
+// How a launch over `m` rows of up to `max_width` positions is cut. A cluster has at most 8
+// blocks (the portable size), 16 only when a row is too wide for 8 slices; a row's funnel is
+// fused when all its kv heads fit into the cluster beside the slices.
+static std::atomic<int> g_forced_splits{-1};     // -1: not set yet (the environment decides), 0: automatic
+void attn_force_splits(int splits) { g_forced_splits.store(splits < 0 ? 0 : splits); }
+
+static AttnPlan attn_plan(const Dims& d, int m, int max_width) {
+	AttnPlan p;
+	int forced = g_forced_splits.load();
+	if (forced < 0) {      // SSLM_B200_ATTN_SPLITS=n fixes the slices per kv head (tuning, tests)
+		const char* e = getenv("SSLM_B200_ATTN_SPLITS");
+		forced = e ? atoi(e) : 0;
+		g_forced_splits.store(forced < 0 ? 0 : forced);
+	}
+	const int per_kv_max = d.kv_heads <= 8 ? 8 / d.kv_heads : 1;   // slices per kv head with the whole row in one cluster
+	int splits = 1;
+	if (forced > 0) {
+		while (splits * 2 <= forced && splits * 2 <= 16) splits *= 2;
+	} else {
+		// Slices of about 256 positions shorten each block's chain of dependent loads; when there
+		// are rows enough to fill the machine several times over (a prefill chunk) one slice per
+		// row has the least overhead; when there are few rows, more slices put more
+		// multiprocessors to work.
+		const int blocks = m * d.kv_heads;
+		int want = blocks >= 4 * sm_count() ? 1 : (max_width + 255) / 256;
+		while (want < 8 && blocks * want < sm_count()) want *= 2;
+		while (splits * 2 <= want && splits * 2 <= 8) splits *= 2;
+		if (splits > per_kv_max) splits = per_kv_max;              // prefer the fused funnel ...
+	}
+	while (splits > 1 && splits * 64 > pad64(max_width)) splits /= 2;
+	// ... unless the width does not fit the slices: then up to 16 slices of one kv head per cluster
+	while (splits < 16 && pad64((max_width + splits - 1) / splits) > kAttnMaxSlice) splits *= 2;
+	p.whole_row = splits <= per_kv_max ? 1 : 0;
+	p.splits = splits;
+	p.cp = pad64((max_width + splits - 1) / splits);
+	return p;
+}
+
 template <int HD>
-static void launch_attn(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index, KvPoolDev pool,
-                        int wp, size_t sm, int reverse_rows, cudaStream_t st) {
-	launch_pdl(k_attention<HD>, dim3(d.kv_heads, b.m), dim3(2 * HD), sm, st, b, d, layer, layer_index, pool, wp, reverse_rows);
+static cudaError_t launch_attn(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index, KvPoolDev pool,
+                               const AttnPlan& p, int reverse_rows, cudaStream_t st) {
+	const size_t sm = attn_smem_bytes(d.heads / d.kv_heads, p.cp, HD);
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = dim3(d.kv_heads * p.splits, b.m);
+	cfg.blockDim = dim3(2 * HD);
+	cfg.dynamicSmemBytes = sm;
+	cfg.stream = st;
+	cudaLaunchAttribute attr[2];
+	attr[0].id = cudaLaunchAttributeClusterDimension;
+	attr[0].val.clusterDim.x = (unsigned)(p.whole_row ? d.kv_heads * p.splits : p.splits);
+	attr[0].val.clusterDim.y = 1;
+	attr[0].val.clusterDim.z = 1;
+	attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+	attr[1].val.programmaticStreamSerializationAllowed = 1;
+	cfg.attrs = attr;
+	cfg.numAttrs = pdl_enabled() ? 2 : 1;
+	return cudaLaunchKernelEx(&cfg, k_attention<HD>, b, d, layer, layer_index, pool, p.cp, p.splits, p.whole_row, reverse_rows);
 }
 
 cudaError_t attn_configure(const Dims& d) {
 	const int group = d.heads / d.kv_heads;
 	if (group < 1 || group > 8 || d.heads % d.kv_heads != 0) return cudaErrorInvalidConfiguration;
-	const size_t need = attn_smem_bytes(group, pad_width(d.context_cap));
+	// widest row the plan can serve: 16 slices of kAttnMaxSlice positions
+	if (d.context_cap > 16 * kAttnMaxSlice) return cudaErrorInvalidConfiguration;
+	const size_t need = attn_smem_bytes(group, kAttnMaxSlice, d.head_dim);
 	if (need > 227 * 1024) return cudaErrorInvalidConfiguration;
 	const int n = (int)need;
 	const void* f = nullptr;
@@ -413,17 +614,22 @@ cudaError_t attn_configure(const Dims& d) {
 	else return cudaErrorInvalidConfiguration;
 	cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, n);
 	if (e != cudaSuccess) return e;
+	// clusters of 16 blocks (rows wider than 8 slices) are an opt-in size
+	e = cudaFuncSetAttribute(f, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+	if (e != cudaSuccess) return e;
 	// same carve-out as the kernels around it (see rows_configure)
 	return cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
-void launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
-                      KvPoolDev pool, int max_width, int reverse_rows, cudaStream_t st) {
-	const int wp = pad_width(max_width);
-	const size_t sm = attn_smem_bytes(d.heads / d.kv_heads, wp);
-	if (d.head_dim == 128) launch_attn<128>(b, d, layer, layer_index, pool, wp, sm, reverse_rows, st);
-	else if (d.head_dim == 64) launch_attn<64>(b, d, layer, layer_index, pool, wp, sm, reverse_rows, st);
-	else launch_attn<32>(b, d, layer, layer_index, pool, wp, sm, reverse_rows, st);
+bool launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
+                      KvPoolDev pool, int max_width, int reverse_rows, cudaStream_t st, cudaError_t* err) {
+	const AttnPlan p = attn_plan(d, b.m, max_width);
+	cudaError_t e;
+	if (d.head_dim == 128) e = launch_attn<128>(b, d, layer, layer_index, pool, p, reverse_rows, st);
+	else if (d.head_dim == 64) e = launch_attn<64>(b, d, layer, layer_index, pool, p, reverse_rows, st);
+	else e = launch_attn<32>(b, d, layer, layer_index, pool, p, reverse_rows, st);
+	if (err) *err = e;
+	return p.whole_row != 0;
 }
 
 // ------------------------------------------------------------ canonical KV export

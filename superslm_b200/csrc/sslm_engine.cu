@@ -535,6 +535,12 @@ extern "C" sslm_status sslm_b200_tc_variant_counts(uint64_t* counts, int32_t n) 
 	return SSLM_OK;
 }
 
+extern "C" sslm_status sslm_b200_set_attention_splits(int32_t splits) {
+	if (splits < 0 || splits > 16) return SSLM_INVALID_ARGUMENT;
+	attn_force_splits(splits);
+	return SSLM_OK;
+}
+
 extern "C" sslm_status sslm_b200_profile(sslm_workspace ws, int32_t enable) {
 	if (!ws) return SSLM_INVALID_ARGUMENT;
 	ws->profile = enable != 0;

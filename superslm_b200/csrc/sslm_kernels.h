@@ -152,8 +152,12 @@ void launch_lora_u(const RowBatch& b, const int8_t* x, int k_in, int layer, int 
 
 // ---- attention over the paged KV pool (sslm_attn.cu)
 cudaError_t attn_configure(const Dims& d);
-void launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
-                      KvPoolDev pool, int max_width, int reverse_rows, cudaStream_t st);
+// slices per kv head of later attention launches (0: chosen per launch); for tuning and tests
+void attn_force_splits(int splits);
+// Returns true when the launch also ran the attention-context funnel (codes in b.ctx, scale in
+// b.cs); otherwise b.ctxw / rowmax slot 3 are filled and launch_ctx_funnel must follow.
+bool launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
+                      KvPoolDev pool, int max_width, int reverse_rows, cudaStream_t st, cudaError_t* err);
 // gather a sequence's pages into the reference's canonical block layout
 // [layer][K|V][kv_head][position][head_dim]; positions beyond `valid(layer)` are zero
 void launch_kv_export(const Dims& d, KvPoolDev pool, const int32_t* pages, int context_length,

@@ -529,3 +529,32 @@ def test_sequences_of_two_pools_in_one_decode_call(gpu_lib):
         s.release()
     assert gpu_lib.sslm_kv_pool_destroy(pool2) == 0
     eng.close()
+
+
+@pytest.mark.parametrize("shape,plen", [("small", 530), ("tiny", 300)])
+def test_attention_row_cut_into_slices(gpu_lib, shape, plen):
+    """Attention splits a row along its width over the blocks of a cluster (1 to 16 slices per kv
+    head; with few slices the cluster also holds both kv heads and runs the context funnel itself,
+    with many it does not). Every cut must give the CPU oracle's tokens, K/V and scale, in prefill
+    (many rows, ascending widths) and in decode (one row)."""
+    sh = A.SHAPES[shape]
+    art = A.build_synthetic_model(shape, 0xA77E, 640)
+    prompt = A.stream_uniform(0xA77E, "prompt", plen, 0, sh.vocab - 1)
+    want_toks, ps = run_port(art, prompt, 6)
+    f = gpu_lib.dll.sslm_b200_set_attention_splits
+    f.argtypes = [C.c_int32]
+    try:
+        for splits in (1, 2, 4, 8, 16, 0):
+            assert f(splits) == 0
+            eng = abi.Engine(gpu_lib, art, blocks=1, max_chunk=256)
+            s = eng.new_seq()
+            s.prefill(prompt, 200)
+            toks = s.decode(6, 1 + splits % 2)
+            blob = abi.parse_save_blob(s.save(), sh.hidden)
+            eng.close()
+            assert toks == want_toks, splits
+            assert blob["kv"] == ps.kv.tobytes(), splits
+            assert blob["hidden_scale"] == (ps.s.hidden_scale.m, ps.s.hidden_scale.e), splits
+            assert blob["kv_saturation_count"] == ps.s.kv_saturation_count, splits
+    finally:
+        f(0)
