@@ -22,6 +22,7 @@ from superslm_b200 import artifact as A
 HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_SO = os.path.join(HERE, "liboracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libsslm_ref.so")
+ABI_PROBE = os.path.join(HERE, "_ref", "abi_probe")
 # Where the reference's sources are mounted, if anywhere: SSLM_REF_ROOT, else a directory named
 # "reference" beside this repository's checkout.
 _SIBLING = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
@@ -33,6 +34,8 @@ def build(verbose: bool = False) -> None:
     targets = ["oracle"]
     if REF_ROOT and os.path.isdir(os.path.join(REF_ROOT, "src")):
         targets.append("ref")
+        if os.path.exists(os.path.join(os.path.dirname(HERE), "superslm_b200", "libsslm_b200.so")):
+            targets.append("probe")     # the reference-header caller linked against the CUDA library
     out = subprocess.run(["make", "-C", HERE, "-j8", "REF_ROOT=" + REF_ROOT] + targets,
                          capture_output=True, text=True)
     if out.returncode != 0:

@@ -163,9 +163,15 @@ struct AttnSmem {
 	int32_t* x_ctx;       // [8][HD] this slice's share of P.V per head
 	uint32_t* x_flags;    // [0] the slice met an element the reference refuses, [1] largest folded |ctx| of the
 	                      //     channels this block reduced, [2] this block sits the row out
+	// local copies of what the exchanges fetched (a few threads read the peers, everybody reads these)
+	int32_t* l_max;       // [8] row maximum per head
+	unsigned long long* l_sum;   // [8] row total per head
+	uint32_t* l_misc;     // [0] some block refused the row, [1] largest folded |ctx| of the row
+	int32_t* l_fold;      // [8][3] context fold (identity, multiplier, shift) of this kv head's q heads
 };
 __host__ __device__ inline size_t attn_smem_bytes(int group, int cp, int hd) {
-	return (size_t)cp / 16 * 8 + (size_t)group * cp * 6 + 8 * kAttnMaxWarps * 8 + 8 * 4 + 8 * 8 + (size_t)8 * hd * 4 + 16;
+	return (size_t)cp / 16 * 8 + (size_t)group * cp * 6 + 8 * kAttnMaxWarps * 8 + 8 * 4 + 8 * 8 + (size_t)8 * hd * 4 + 16 +
+	       8 * 8 + 8 * 4 + 8 + 24 * 4;
 }
 __device__ __forceinline__ AttnSmem carve(unsigned char* smem, int group, int cp, int hd) {
 	AttnSmem s;
@@ -178,6 +184,10 @@ __device__ __forceinline__ AttnSmem carve(unsigned char* smem, int group, int cp
 	s.x_max = (int32_t*)(s.x_sum + 8);
 	s.x_ctx = s.x_max + 8;
 	s.x_flags = (uint32_t*)(s.x_ctx + 8 * hd);
+	s.l_sum = (unsigned long long*)(s.x_flags + 4);
+	s.l_max = (int32_t*)(s.l_sum + 8);
+	s.l_misc = (uint32_t*)(s.l_max + 8);
+	s.l_fold = (int32_t*)(s.l_misc + 2);
 	return s;
 }
 // ask for the line at p to be brought into L2; nothing waits for it
@@ -232,6 +242,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		for (int j = t; j < npages; j += kAttnThreads) s.pbase[j] = (int64_t)pages[j] * (kPageTokens * HD);
 	}
 	const FunnelFold fold_ctx = funnel_prefold(nullptr, 0, layer->c_ctx);
+	if (t < 3 * G) s.l_fold[t] = layer->f_ctx[3 * kvh * G + t];      // (weights: ahead of the wait)
 	__syncthreads();
 	constexpr int kRowsPerLine = 128 / HD;
 	for (int pos = t * kRowsPerLine; pos < n - (p0 + n == width ? 1 : 0); pos += kAttnThreads * kRowsPerLine)
@@ -324,14 +335,17 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		s.x_max[t] = m;
 	}
 	cluster_sync_all();      // ---- exchange 1: every slice's maxima are up
-#pragma unroll
-	for (int h = 0; h < 8; ++h) {
-		if (h < G) {
-			int m = INT32_MIN;
-			for (int j = 0; j < splits; ++j) m = max(m, (int)peer_ld32(peer_addr(&s.x_max[h], kv_rank0 + (uint32_t)j)));
-			mx[h] = m;
-		}
+	// (one thread per head fetches the peers' values; reading them from every thread would put
+	// thousands of remote loads on the cluster's shared-memory network)
+	if (t < G) {
+		int m = INT32_MIN;
+		for (int j = 0; j < splits; ++j) m = max(m, (int)peer_ld32(peer_addr(&s.x_max[t], kv_rank0 + (uint32_t)j)));
+		s.l_max[t] = m;
 	}
+	__syncthreads();
+#pragma unroll
+	for (int h = 0; h < 8; ++h)
+		if (h < G) mx[h] = s.l_max[h];
 
 	unsigned long long tot[8];
 #pragma unroll
@@ -383,15 +397,22 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	cluster_sync_all();      // ---- exchange 2: every slice's sums and refusal flags are up
 	// the reference refuses the whole row when any element of any head is out of bounds
 	// (SoftmaxKernelRefusedAfterGateAccepted): every block of the cluster learns it here
-	bool refused = false;
-	for (uint32_t j = 0; j < cluster_blocks; ++j) refused |= peer_ld32(peer_addr(&s.x_flags[0], j)) != 0u;
+	if (t < G) {
+		unsigned long long x = 0;
+		for (int j = 0; j < splits; ++j) x += peer_ld64(peer_addr(&s.x_sum[t], kv_rank0 + (uint32_t)j));
+		s.l_sum[t] = x;
+	} else if (t == 32) {
+		uint32_t any = 0;
+		for (uint32_t j = 0; j < cluster_blocks; ++j) any |= peer_ld32(peer_addr(&s.x_flags[0], j));
+		s.l_misc[0] = any;
+	}
+	__syncthreads();
+	const bool refused = s.l_misc[0] != 0u;
 	if (refused && my_rank == 0 && t == 0) atomicCAS(&b.status[r], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
 	float inv[8];
 #pragma unroll
 	for (int h = 0; h < 8; ++h) {
-		unsigned long long x = 0;
-		if (h < G)
-			for (int j = 0; j < splits; ++j) x += peer_ld64(peer_addr(&s.x_sum[h], kv_rank0 + (uint32_t)j));
+		const unsigned long long x = h < G ? s.l_sum[h] : 0ull;
 		tot[h] = x > 1ull ? x : 1ull;
 		inv[h] = 32768.0f / (float)tot[h];
 	}
@@ -493,8 +514,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 			const int h = e / nch, ch = ch0 + e - h * nch;
 			int32_t sum = 0;
 			for (int j = 0; j < splits; ++j) sum += (int32_t)peer_ld32(peer_addr(&s.x_ctx[h * HD + ch], kv_rank0 + (uint32_t)j));
-			const int32_t* f = layer->f_ctx + 3 * (kvh * G + h);
-			const int32_t o = fold(sum, f[0], f[1], f[2]);
+			const int32_t o = fold(sum, s.l_fold[3 * h], s.l_fold[3 * h + 1], s.l_fold[3 * h + 2]);
 			mine[q] = o;
 			lmax = max(lmax, o < 0 ? 0u - (uint32_t)o : (uint32_t)o);
 			if (!whole_row && work) b.ctxw[(size_t)r * d.hidden + (size_t)(kvh * G + h) * HD + ch] = o;
@@ -510,8 +530,13 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	// ---- the cluster holds the whole row: its funnel runs here
 	if (lane == 0 && lmax) atomicMax(&s.x_flags[1], lmax);
 	cluster_sync_all();      // ---- exchange 4: every block's largest folded magnitude is up
-	uint32_t rowmx = 0;
-	for (uint32_t j = 0; j < cluster_blocks; ++j) rowmx = max(rowmx, peer_ld32(peer_addr(&s.x_flags[1], j)));
+	if (t == 0) {
+		uint32_t v = 0;
+		for (uint32_t j = 0; j < cluster_blocks; ++j) v = max(v, peer_ld32(peer_addr(&s.x_flags[1], j)));
+		s.l_misc[1] = v;
+	}
+	__syncthreads();
+	const uint32_t rowmx = s.l_misc[1];
 	const FunnelParams fp = funnel_finish((unsigned long long)rowmx, fold_ctx);
 	if (work) {
 		if (fp.status != kOk) {

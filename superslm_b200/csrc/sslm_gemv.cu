@@ -1,17 +1,18 @@
 // Decode-path int8 linear layer: out[m,n] = fold_n(sum_k x[m,k] w[n,k]) for a handful of
 // rows m. HBM-bound: the kernel exists to keep the weight stream at the speed of the memory.
 //
-// A block owns a contiguous range of output channels, i.e. one contiguous byte range of the
-// row-major weight matrix. A producer thread streams that range into a shared-memory ring with
-// bulk asynchronous copies (cp.async.bulk, 16 KiB each, completion counted on an mbarrier), so
-// ~100 KiB per block are in flight without holding a register; eight consumer warps walk each
-// landed chunk as a flat array of 16-byte pieces, multiply with dp4a against the activation rows
-// held in shared memory, and add their partial sums into per-channel accumulators in shared
-// memory (a warp reduces with one warp-reduce instruction per row it touches). Chunks need not
-// line up with weight rows: a piece knows its (channel, k) from its flat index.
+// A block owns a contiguous range of output channels; its warps deal those channels among
+// themselves (warp w takes channels w, w + W, ...). Every warp streams ITS weight rows through
+// its own small ring in shared memory with bulk asynchronous copies (cp.async.bulk, one row or one
+// 4 KiB segment of a long row per copy, completion counted on an mbarrier of that ring slot): the
+// warp is producer and consumer of its ring, so the main loop has no block-wide synchronisation
+// at all, ~100 KiB per block are in flight without holding a register, and a lane's partial sums
+// of a channel stay in registers until the channel's last segment -- one warp reduction per
+// channel and row of x, whatever K is. The activations sit in shared memory; dp4a does the
+// arithmetic.
 //
-// The weights are written by no kernel, so the ring's first copies and the block's fold rows are
-// requested BEFORE the dependency wait: while the kernel in front (a row kernel that moves
+// The weights are written by no kernel, so every ring's first copies and the block's fold rows
+// are requested BEFORE the dependency wait: while the kernel in front (a row kernel that moves
 // little data) finishes, this kernel's weight stream is already running.
 //
 // The epilogue applies the per-channel weight-scale fold, adds the LoRA delta, stores the wide
@@ -22,19 +23,19 @@
 // sums do not depend on the order in which pieces are added.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out marks the block's rows with an
-// internal status, the block stops issuing copies, waits (bounded again) for the copies it has
-// in flight, and returns.
+// internal status, the warp stops issuing copies, waits (bounded again) for the copies it has
+// in flight, and the block returns.
 #include <cuda_runtime.h>
 
 #include "sslm_kernels.h"
 
 namespace sslm {
 
-constexpr int kGemvConsumers = 256;                 // eight consumer warps
-constexpr int kGemvThreads = kGemvConsumers + 32;   // + the producer warp
-constexpr int kChunkBytes = 16 * 1024;
-constexpr int kChunkVec = kChunkBytes / 16;         // 16-byte pieces per chunk
-constexpr int kMaxStages = 6;
+constexpr int kGemvWarps = 8;
+constexpr int kGemvThreads = kGemvWarps * 32;
+constexpr int kSegBytes = 4096;                     // longest single copy (a row, or a segment of a long row)
+constexpr int kRingBytesPerWarp = 12 * 1024;
+constexpr int kMaxSlots = 8;
 constexpr uint32_t kGemvMaxPolls = 1u << 22;
 
 __device__ __forceinline__ int dot16(const int4& a, const int4& b, int acc) {
@@ -53,9 +54,6 @@ __device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
 	asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bar_arrive(uint32_t bar) {
-	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool bar_try_wait(uint32_t bar, uint32_t parity) {
 	uint32_t ok;
@@ -85,9 +83,9 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 // What the host decides per launch.
 struct GemvPlan {
 	int rows_per_block;   // output channels per block
-	int stages;           // ring depth
-	int k16;              // K / 16
-	int step_row, step_kc;   // (256 / k16, 256 % k16): how a thread's piece moves from one pass to the next
+	int seg16;            // 16-byte pieces per copy (a whole row when K is short)
+	int nseg;             // copies per weight row
+	int slots;            // ring slots per warp
 };
 
 // MT rows of x per pass (grid.y walks the row groups).
@@ -95,227 +93,190 @@ template <int MT>
 __global__ void __launch_bounds__(kGemvThreads)
 k_gemv(LinearArgs a, GemvPlan p) {
 	extern __shared__ __align__(128) unsigned char smem[];
-	const int K = a.K, k16 = p.k16, S = p.stages;
+	const int K = a.K, k16 = K >> 4;
 	const int n0 = blockIdx.x * p.rows_per_block;
 	const int nrows = min(p.rows_per_block, a.N - n0);
 	const int m0 = blockIdx.y * MT;
 	const int mcount = min(MT, a.M - m0);
-	// carve: ring | x rows | accumulators | fold rows | maxima | barriers
-	unsigned char* ring = smem;
-	int8_t* sx = (int8_t*)(ring + (size_t)S * kChunkBytes);
+	const int slot_bytes = p.seg16 * 16;
+	// carve: rings | x rows | accumulators | fold rows | maxima | barriers
+	unsigned char* rings = smem;
+	int8_t* sx = (int8_t*)(rings + (size_t)kGemvWarps * p.slots * slot_bytes);
 	int* sacc = (int*)(sx + (size_t)MT * K);                                   // [MT][rows_per_block]
 	int32_t* sfold = sacc + (size_t)MT * p.rows_per_block;                     // [rows_per_block][3]
 	unsigned long long* smax = (unsigned long long*)(((uintptr_t)(sfold + 3 * (size_t)p.rows_per_block) + 7) & ~(uintptr_t)7);   // [4][MT]
-	const uint32_t bars = smem_addr(smax + 4 * MT);
-	auto full_bar = [&](int s) { return bars + 8u * s; };
-	auto empty_bar = [&](int s) { return bars + 8u * (kMaxStages + s); };
+	const uint32_t bars = smem_addr(smax + 4 * MT);                            // [warps][kMaxSlots]
 	__shared__ int s_timeout;
 
 	const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-	const size_t total_bytes = (size_t)nrows * K;
-	const int nchunks = (int)((total_bytes + kChunkBytes - 1) / kChunkBytes);
-	const int8_t* wsrc = a.w + (size_t)n0 * K;
+	unsigned char* ring = rings + (size_t)warp * p.slots * slot_bytes;
+	auto full_bar = [&](int s) { return bars + 8u * (warp * kMaxSlots + s); };
+	// this warp's work items: channel `warp + kGemvWarps * (i / nseg)` of the block, segment `i % nseg`
+	const int my_rows = nrows > warp ? (nrows - warp + kGemvWarps - 1) / kGemvWarps : 0;
+	const int items = my_rows * p.nseg;
+	auto issue = [&](int i) {      // (lane 0 only)
+		const int rl = warp + kGemvWarps * (i / p.nseg), sg = i % p.nseg;
+		const int first = sg * p.seg16, count = min(p.seg16, k16 - first);
+		const int s = i % p.slots;
+		bar_expect_tx(full_bar(s), (uint32_t)count * 16u);
+		bulk_load(smem_addr(ring + (size_t)s * slot_bytes), a.w + ((size_t)(n0 + rl) * K + (size_t)first * 16), (uint32_t)count * 16u,
+		          full_bar(s));
+	};
 
-	if (t == 0) {
-		for (int s = 0; s < S; ++s) {
-			bar_init(full_bar(s), 1);
-			bar_init(empty_bar(s), kGemvConsumers / 32);
-		}
-		s_timeout = 0;
+	if (lane == 0) {
+		for (int s = 0; s < p.slots; ++s) bar_init(full_bar(s), 1);
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
+	if (t == 0) s_timeout = 0;
+	__syncwarp();
+	// ahead of the dependency wait: the first copies of every ring, the block's fold rows, cleared maxima
+	int issued = items < p.slots ? items : p.slots;      // items whose copies have been requested
+	if (lane == 0)
+		for (int i = 0; i < issued; ++i) issue(i);
+	if (a.fold != nullptr) {
+		const int32_t* f = a.fold + (size_t)n0 * 3;
+		for (int i = t; i < nrows * 3; i += kGemvThreads) sfold[i] = __ldg(f + i);
+	}
+	if (t < 4 * MT) smax[t] = 0ull;
+	pdl_wait();
+	pdl_release();
+	// the activation rows (written by the kernel in front: read past the L1)
+	for (int i = t; i < MT * k16; i += kGemvThreads) {
+		const int m = i / k16, c = i - m * k16;
+		int4 v = make_int4(0, 0, 0, 0);
+		if (m < mcount) v = __ldcg((const int4*)(a.x + (size_t)(m0 + m) * K) + c);
+		((int4*)sx)[i] = v;
+	}
 	__syncthreads();
 
-	if (warp == kGemvConsumers / 32) {
-		// ---- producer: one thread keeps the ring full. Its first S copies go out ahead of the
-		// dependency wait (weights are not written by any kernel).
-		auto issue = [&](int c) {
-			const int s = c % S;
-			const size_t off = (size_t)c * kChunkBytes;
-			const uint32_t bytes = (uint32_t)min((size_t)kChunkBytes, total_bytes - off);
-			bar_expect_tx(full_bar(s), bytes);
-			bulk_load(smem_addr(ring + (size_t)s * kChunkBytes), wsrc + off, bytes, full_bar(s));
-		};
-		if (lane == 0)
-			for (int c = 0; c < nchunks && c < S; ++c) issue(c);
-		pdl_wait();
-		pdl_release();
-		if (lane == 0) {
-			for (int c = S; c < nchunks; ++c) {
-				if (!bar_wait(empty_bar(c % S), ((uint32_t)(c / S) & 1u) ^ 1u)) {
-					atomicExch(&s_timeout, 1);
-					break;
-				}
-				if (*(volatile int*)&s_timeout) break;
-				issue(c);
-			}
+	int acc[MT];
+#pragma unroll
+	for (int m = 0; m < MT; ++m) acc[m] = 0;
+	bool ok = true;
+	for (int i = 0; i < items; ++i) {
+		const int s = i % p.slots;
+		// (the whole warp agrees on the outcome of a wait)
+		if (!__all_sync(0xffffffffu, bar_wait(full_bar(s), (uint32_t)(i / p.slots) & 1u) ? 1 : 0)) {
+			atomicExch(&s_timeout, 1);
+			ok = false;
+			break;
 		}
-	} else {
-		// ---- consumers. Ahead of the wait: the block's fold rows (weights), cleared accumulators.
-		for (int i = t; i < MT * p.rows_per_block; i += kGemvConsumers) sacc[i] = 0;
-		if (a.fold != nullptr) {
-			const int32_t* f = a.fold + (size_t)n0 * 3;
-			for (int i = t; i < nrows * 3; i += kGemvConsumers) sfold[i] = __ldg(f + i);
+		const int sg = i % p.nseg;
+		const int first = sg * p.seg16, count = min(p.seg16, k16 - first);
+		const int4* wv = (const int4*)(ring + (size_t)s * slot_bytes);
+#pragma unroll 2
+		for (int c = lane; c < count; c += 32) {
+			const int4 w4 = wv[c];
+#pragma unroll
+			for (int m = 0; m < MT; ++m) acc[m] = dot16(w4, ((const int4*)(sx + (size_t)m * K))[first + c], acc[m]);
 		}
-		if (t < 4 * MT) smax[t] = 0ull;
-		pdl_wait();
-		pdl_release();
-		// the activation rows (written by the kernel in front: read past the L1)
-		for (int i = t; i < MT * k16; i += kGemvConsumers) {
-			const int m = i / k16, c = i - m * k16;
-			int4 v = make_int4(0, 0, 0, 0);
-			if (m < mcount) v = __ldcg((const int4*)(a.x + (size_t)(m0 + m) * K) + c);
-			((int4*)sx)[i] = v;
+		__syncwarp();      // every lane has read the slot: it may be refilled
+		if (i + p.slots < items) {
+			if (lane == 0) issue(i + p.slots);
+			issued = i + p.slots + 1;
 		}
-		asm volatile("bar.sync 1, 256;" ::: "memory");
-
-		// this thread's piece in pass j of chunk c is flat index c * kChunkVec + j * 256 + t
-		int row = t / k16, kc = t - row * k16;
-		bool ok = true;
-		for (int c = 0; c < nchunks && ok; ++c) {
-			const int s = c % S;
-			// (the whole warp agrees on the outcome: the warp-wide instructions below need all lanes)
-			if (!__all_sync(0xffffffffu, bar_wait(full_bar(s), (uint32_t)(c / S) & 1u) ? 1 : 0)) {
-				atomicExch(&s_timeout, 1);
-				ok = false;
-				break;
-			}
-			const int4* wv = (const int4*)(ring + (size_t)s * kChunkBytes);
-			const int vec_left = (int)((total_bytes - (size_t)c * kChunkBytes) >> 4);   // pieces from this chunk's start to the end
+		if (sg == p.nseg - 1) {      // the channel is complete: one reduction per row of x
+			const int rl = warp + kGemvWarps * (i / p.nseg);
 #pragma unroll
-			for (int j = 0; j < kChunkVec / kGemvConsumers; ++j) {
-				const int i = j * kGemvConsumers + t;
-				const bool live = i < vec_left;
-				int4 w4 = make_int4(0, 0, 0, 0);
-				if (live) w4 = wv[i];
-				// rows this warp's 32 consecutive pieces touch: one or two when a weight row holds
-				// at least 32 pieces, several otherwise
-				const int row_lo = __shfl_sync(0xffffffffu, row, 0);
-				const int row_hi = __shfl_sync(0xffffffffu, row, 31);
-				if (row_hi <= row_lo + 1) {
-#pragma unroll
-					for (int m = 0; m < MT; ++m) {
-						int v = 0;
-						if (live) v = dot16(w4, ((const int4*)(sx + (size_t)m * K))[kc], 0);
-						const int s0 = __reduce_add_sync(0xffffffffu, row == row_lo ? v : 0);
-						if (lane == 0 && row_lo < nrows) atomicAdd(&sacc[m * p.rows_per_block + row_lo], s0);
-						if (row_hi != row_lo) {
-							const int s1 = __reduce_add_sync(0xffffffffu, row == row_lo ? 0 : v);
-							if (lane == 0 && row_hi < nrows) atomicAdd(&sacc[m * p.rows_per_block + row_hi], s1);
-						}
-					}
-				} else if (live) {
-#pragma unroll
-					for (int m = 0; m < MT; ++m)
-						atomicAdd(&sacc[m * p.rows_per_block + row], dot16(w4, ((const int4*)(sx + (size_t)m * K))[kc], 0));
-				}
-				row += p.step_row;
-				kc += p.step_kc;
-				if (kc >= k16) { kc -= k16; ++row; }
-			}
-			__syncwarp();
-			if (lane == 0) bar_arrive(empty_bar(s));
-		}
-		asm volatile("bar.sync 1, 256;" ::: "memory");
-
-		if (*(volatile int*)&s_timeout) {
-			if (a.status != nullptr && t < mcount) atomicCAS(&a.status[m0 + t], 0, (int32_t)kInternalWaitTimeout);
-		} else {
-			// ---- epilogue: thread i takes output (m, n) = (i / nrows, i % nrows)
-			unsigned long long lmax[3] = {0ull, 0ull, 0ull};
-			unsigned long long lbest = 0ull;
-			int my_m = -1;
-			for (int i = t; i < mcount * nrows; i += kGemvConsumers) {
-				const int m = i / nrows, nl0 = i - m * nrows;
-				if (m != my_m) {
-					// (a thread's outputs belong to one row except when nrows < 256: flush per row)
-					if (my_m >= 0) {
-						if (a.best != nullptr) {
-							if (lbest) atomicMax(&smax[3 * MT + my_m], lbest);
-						} else {
-#pragma unroll
-							for (int sg = 0; sg < 3; ++sg)
-								if (lmax[sg]) atomicMax(&smax[sg * MT + my_m], lmax[sg]);
-						}
-						lmax[0] = lmax[1] = lmax[2] = 0ull;
-						lbest = 0ull;
-					}
-					my_m = m;
-				}
-				const int n = n0 + nl0, rowg = m0 + m;
-				const int mine = sacc[m * p.rows_per_block + nl0];
-				int seg = 0;
-				while (seg + 1 < a.nseg && n >= a.seg_end[seg]) ++seg;
-				int32_t v32 = mine;
-				if (a.fold) v32 = fold(mine, sfold[3 * nl0], sfold[3 * nl0 + 1], sfold[3 * nl0 + 2]);
-				int64_t v = v32;
-				if (a.rows != nullptr && a.seg_lora[seg] >= 0) {
-					const LoraLayerDev* ll = a.rows[rowg].lora;
-					if (ll != nullptr) {
-						const LoraLayerDev& L = ll[a.layer];
-						const LoraProjDev& pj = L.p[a.seg_lora[seg]];
-						if (pj.a != nullptr) {
-							const int nl = n - (seg ? a.seg_end[seg - 1] : 0);
-							const int8_t* brow = pj.b + (size_t)nl * L.rank;
-							const int8_t* u = a.lora_u + ((size_t)rowg * 3 + seg) * kMaxLoraRank;
-							int dsum = 0;
-							for (uint32_t r = 0; r < L.rank; ++r) dsum += (int)brow[r] * (int)u[r];
-							v += (int64_t)amp_fold(dsum, pj.df[3 * nl], pj.df[3 * nl + 1], pj.df[3 * nl + 2]);
-						}
-					}
-				}
-				if (a.best != nullptr) {
-					if (a.row_mask != nullptr) {
-						const uint8_t* page = a.row_mask[rowg];
-						if (page != nullptr && !((page[n >> 3] >> (n & 7)) & 1u)) v32 = INT32_MIN;
-					}
-					const unsigned long long key =
-					    ((unsigned long long)((uint32_t)v32 ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)n);
-					lbest = key > lbest ? key : lbest;
-					if (a.logits) a.logits[(size_t)rowg * a.N + n] = v32;
-				} else {
-					if (a.out64) ((int64_t*)a.out)[(size_t)rowg * a.out_ld + n] = v;
-					else ((int32_t*)a.out)[(size_t)rowg * a.out_ld + n] = (int32_t)v;
-					if (a.seg_slot[seg] >= 0) {
-						const unsigned long long ab = v < 0 ? (~(unsigned long long)v + 1ull) : (unsigned long long)v;
-						lmax[seg] = ab > lmax[seg] ? ab : lmax[seg];
-					}
-				}
-			}
-			if (my_m >= 0) {
-				if (a.best != nullptr) {
-					if (lbest) atomicMax(&smax[3 * MT + my_m], lbest);
-				} else {
-#pragma unroll
-					for (int sg = 0; sg < 3; ++sg)
-						if (lmax[sg]) atomicMax(&smax[sg * MT + my_m], lmax[sg]);
-				}
-			}
-			asm volatile("bar.sync 1, 256;" ::: "memory");
-			if (t < 4 * MT) {
-				const int sg = t / MT, m = t % MT;
-				const unsigned long long v = smax[t];
-				if (v != 0ull && m < mcount) {
-					if (sg == 3) atomicMax(&a.best[m0 + m], v);
-					else if (a.rowmax != nullptr && sg < a.nseg && a.seg_slot[sg] >= 0)
-						atomicMax(&a.rowmax[(size_t)(m0 + m) * 4 + a.seg_slot[sg]], v);
-				}
+			for (int m = 0; m < MT; ++m) {
+				const int v = __reduce_add_sync(0xffffffffu, acc[m]);
+				if (lane == 0) sacc[m * p.rows_per_block + rl] = v;
+				acc[m] = 0;
 			}
 		}
 	}
-	// No copy may still be landing in this block's shared memory when the block ends. In the normal
-	// course every chunk was waited for by the consumers; after a timeout the producer's copies
-	// that did complete are drained here, bounded.
+	if (!ok && lane == 0) {
+		// the copies this warp still has in flight must land before the block's shared memory is given up
+		for (int s = 0; s < p.slots && s < issued; ++s) {
+			const int last = ((issued - 1 - s) / p.slots) * p.slots + s;     // last requested item that uses slot s
+			bar_wait(full_bar(s), (uint32_t)(last / p.slots) & 1u);
+		}
+	}
 	__syncthreads();
-	if (t == 0 && *(volatile int*)&s_timeout) {
-		for (int c = max(0, nchunks - S); c < nchunks; ++c) bar_wait(full_bar(c % S), (uint32_t)(c / S) & 1u);
+
+	if (*(volatile int*)&s_timeout) {
+		if (a.status != nullptr && t < mcount) atomicCAS(&a.status[m0 + t], 0, (int32_t)kInternalWaitTimeout);
+		return;
+	}
+	// ---- epilogue: thread i takes output (m, n) = (i / nrows, i % nrows)
+	unsigned long long lmax[3] = {0ull, 0ull, 0ull};
+	unsigned long long lbest = 0ull;
+	int my_m = -1;
+	auto flush = [&]() {
+		if (my_m < 0) return;
+		if (a.best != nullptr) {
+			if (lbest) atomicMax(&smax[3 * MT + my_m], lbest);
+		} else {
+#pragma unroll
+			for (int sg = 0; sg < 3; ++sg)
+				if (lmax[sg]) atomicMax(&smax[sg * MT + my_m], lmax[sg]);
+		}
+		lmax[0] = lmax[1] = lmax[2] = 0ull;
+		lbest = 0ull;
+	};
+	for (int i = t; i < mcount * nrows; i += kGemvThreads) {
+		const int m = i / nrows, nl0 = i - m * nrows;
+		if (m != my_m) {      // (a thread's outputs belong to one row of x except when the block has few channels)
+			flush();
+			my_m = m;
+		}
+		const int n = n0 + nl0, rowg = m0 + m;
+		const int mine = sacc[m * p.rows_per_block + nl0];
+		int seg = 0;
+		while (seg + 1 < a.nseg && n >= a.seg_end[seg]) ++seg;
+		int32_t v32 = mine;
+		if (a.fold) v32 = fold(mine, sfold[3 * nl0], sfold[3 * nl0 + 1], sfold[3 * nl0 + 2]);
+		int64_t v = v32;
+		if (a.rows != nullptr && a.seg_lora[seg] >= 0) {
+			const LoraLayerDev* ll = a.rows[rowg].lora;
+			if (ll != nullptr) {
+				const LoraLayerDev& L = ll[a.layer];
+				const LoraProjDev& pj = L.p[a.seg_lora[seg]];
+				if (pj.a != nullptr) {
+					const int nl = n - (seg ? a.seg_end[seg - 1] : 0);
+					const int8_t* brow = pj.b + (size_t)nl * L.rank;
+					const int8_t* u = a.lora_u + ((size_t)rowg * 3 + seg) * kMaxLoraRank;
+					int dsum = 0;
+					for (uint32_t r = 0; r < L.rank; ++r) dsum += (int)brow[r] * (int)u[r];
+					v += (int64_t)amp_fold(dsum, pj.df[3 * nl], pj.df[3 * nl + 1], pj.df[3 * nl + 2]);
+				}
+			}
+		}
+		if (a.best != nullptr) {
+			if (a.row_mask != nullptr) {
+				const uint8_t* page = a.row_mask[rowg];
+				if (page != nullptr && !((page[n >> 3] >> (n & 7)) & 1u)) v32 = INT32_MIN;
+			}
+			const unsigned long long key =
+			    ((unsigned long long)((uint32_t)v32 ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)n);
+			lbest = key > lbest ? key : lbest;
+			if (a.logits) a.logits[(size_t)rowg * a.N + n] = v32;
+		} else {
+			if (a.out64) ((int64_t*)a.out)[(size_t)rowg * a.out_ld + n] = v;
+			else ((int32_t*)a.out)[(size_t)rowg * a.out_ld + n] = (int32_t)v;
+			if (a.seg_slot[seg] >= 0) {
+				const unsigned long long ab = v < 0 ? (~(unsigned long long)v + 1ull) : (unsigned long long)v;
+				lmax[seg] = ab > lmax[seg] ? ab : lmax[seg];
+			}
+		}
+	}
+	flush();
+	__syncthreads();
+	if (t < 4 * MT) {
+		const int sg = t / MT, m = t % MT;
+		const unsigned long long v = smax[t];
+		if (v != 0ull && m < mcount) {
+			if (sg == 3) atomicMax(&a.best[m0 + m], v);
+			else if (a.rowmax != nullptr && sg < a.nseg && a.seg_slot[sg] >= 0)
+				atomicMax(&a.rowmax[(size_t)(m0 + m) * 4 + a.seg_slot[sg]], v);
+		}
 	}
 }
 
-// shared memory of one block: ring, activation rows, accumulators, fold rows, maxima, barriers
-static size_t gemv_smem_bytes(int mt, int K, int rows_per_block, int stages) {
-	return (size_t)stages * kChunkBytes + (size_t)mt * K + (size_t)mt * rows_per_block * 4 + (size_t)rows_per_block * 12 +
-	       8 + (size_t)4 * mt * 8 + (size_t)2 * kMaxStages * 8 + 16;
+// shared memory of one block: rings, activation rows, accumulators, fold rows, maxima, barriers
+static size_t gemv_smem_bytes(int mt, int K, int rows_per_block, int slots, int seg16) {
+	return (size_t)kGemvWarps * slots * seg16 * 16 + (size_t)mt * K + (size_t)mt * rows_per_block * 4 +
+	       (size_t)rows_per_block * 12 + 8 + (size_t)4 * mt * 8 + (size_t)kGemvWarps * kMaxSlots * 8 + 16;
 }
 
 template <int MT>
@@ -329,26 +290,24 @@ static cudaError_t launch_mt(const LinearArgs& a, int grid_y, cudaStream_t st) {
 	if (e != cudaSuccess) return e;
 	GemvPlan p;
 	// one block per multiprocessor when the matrix is large enough to keep them all streaming;
-	// never fewer than 8 channels per block
+	// never fewer channels per block than it has warps
 	const int sms = sm_count();
 	int rpb = (a.N + sms - 1) / sms;
-	if (rpb < 8) rpb = 8;
+	if (rpb < kGemvWarps) rpb = kGemvWarps;
 	if (rpb > a.N) rpb = a.N;
 	p.rows_per_block = rpb;
-	p.k16 = a.K / 16;
-	p.step_row = kGemvConsumers / p.k16;
-	p.step_kc = kGemvConsumers % p.k16;
-	// ring depth: as deep as lets two blocks share a multiprocessor (this kernel's blocks then
-	// start their weight stream while the kernel in front still runs), shallower when the
-	// activation rows are long, never more than the block's chunks
-	const size_t chunks = ((size_t)rpb * a.K + kChunkBytes - 1) / kChunkBytes;
-	int stages = kMaxStages;
-	const size_t budget = (size_t)MT * a.K > 40 * 1024 ? 200 * 1024 : 110 * 1024;
-	while (stages > 2 && gemv_smem_bytes(MT, a.K, rpb, stages) > budget) --stages;
-	if ((size_t)stages > chunks) stages = (int)chunks;
-	if (stages < 1) stages = 1;
-	p.stages = stages;
-	const size_t smem = gemv_smem_bytes(MT, a.K, rpb, stages);
+	// a weight row travels as one copy when it is short, else in segments of 4 KiB
+	const int k16 = a.K / 16;
+	p.seg16 = k16 < kSegBytes / 16 ? k16 : kSegBytes / 16;
+	p.nseg = (k16 + p.seg16 - 1) / p.seg16;
+	// ring slots per warp: as many as fit its share of the ring, fewer when the block has little to stream
+	int slots = kRingBytesPerWarp / (p.seg16 * 16);
+	if (slots > kMaxSlots) slots = kMaxSlots;
+	if (slots < 2) slots = 2;
+	const int items_per_warp = ((rpb + kGemvWarps - 1) / kGemvWarps) * p.nseg;
+	if (slots > items_per_warp) slots = items_per_warp;
+	p.slots = slots;
+	const size_t smem = gemv_smem_bytes(MT, a.K, rpb, slots, p.seg16);
 	if (smem > 220 * 1024) return cudaErrorInvalidConfiguration;
 	const int gx = (a.N + rpb - 1) / rpb;
 	return launch_pdl(k_gemv<MT>, dim3(gx, grid_y), dim3(kGemvThreads), smem, st, a, p);
