@@ -557,6 +557,340 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	cluster_sync_all();      // nobody leaves while its shared memory may still be read
 }
 
+// ------------------------------------------------------------ prefill: query-tiled attention
+// The rows of a prefill chunk are consecutive positions of ONE sequence, so neighbouring tokens
+// read almost the same K / V prefix. A block takes a tile of TQ consecutive tokens of one kv head
+// -- TQ * G = up to 64 query rows (token, q head), four 16-row MMA blocks -- and walks the prefix
+// in steps of 64 positions staged in shared memory (cp.async, double buffered): every K / V byte
+// is fetched once per tile instead of once per token. The exact integer softmax needs the row
+// maximum before any exponential and the row total before any probability, so the prefix is
+// walked three times: (1) scores -> row maxima, (2) scores -> exponentials -> row totals,
+// (3) scores -> probabilities -> P.V. Scores are recomputed each time (tensor-core work, cheap
+// beside the integer softmax); nothing of size rows x width is ever stored. The causal limit is
+// per row: token i of the tile sees positions <= pos0 + i.
+// Warp w works on MMA block w / 2 (16 query rows) and on half w % 2 of each 64-position step
+// (scores) respectively half w % 2 of the channels (P.V).
+constexpr int kTileRows = 64;
+constexpr int kTileKeys = 64;
+constexpr int kTileThreads = 256;
+constexpr int kTilePStride = 80;      // bytes per row of the probability planes (64 + padding against bank conflicts)
+
+__device__ __forceinline__ void mma_s8s8_full(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+	asm volatile(
+	    "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+	    : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+	    : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8s8_full(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+	asm volatile(
+	    "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+	    : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+	    : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int HD>
+struct TileSmem {
+	static constexpr int kKStride = HD + 16;                       // bytes per staged K row (padding against bank conflicts)
+	static constexpr size_t kK = (size_t)2 * kTileKeys * kKStride;
+	static constexpr size_t kV = (size_t)2 * kTileKeys * HD;
+	static constexpr size_t kP = (size_t)2 * kTileRows * kTilePStride;
+	static constexpr size_t kFx = (size_t)kTileRows * sizeof(IExpFast);
+	static constexpr size_t kMisc = (size_t)kTileRows * (4 + 4 + 2 * 4 + 2 * 8) + 8 * 3 * 4 + 64;
+	static constexpr size_t kBytes = kK + kV + kP + kFx + kMisc;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kTileThreads, 2)
+k_attention_tile(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int tq) {
+	using L = TileSmem<HD>;
+	constexpr int KS = HD / 32;          // MMA steps along the head dimension
+	constexpr int NGW = HD / 16;         // 8-channel groups a warp owns in P.V
+	extern __shared__ __align__(16) unsigned char smem[];
+	int8_t* Ks = (int8_t*)smem;
+	int8_t* Vs = (int8_t*)(smem + L::kK);
+	uint8_t* Pl = (uint8_t*)(smem + L::kK + L::kV);
+	uint8_t* Ph = Pl + (size_t)kTileRows * kTilePStride;
+	IExpFast* fxs = (IExpFast*)(smem + L::kK + L::kV + L::kP);
+	unsigned long long* wsum = (unsigned long long*)(fxs + kTileRows);      // [2][64]
+	int32_t* wmax = (int32_t*)(wsum + 2 * kTileRows);                        // [2][64]
+	int32_t* tok_ok = wmax + 2 * kTileRows;                                  // [64] 1: the token takes part
+	int32_t* tok_bad = tok_ok + kTileRows;                                   // [64] an element of the token was refused
+	int32_t* l_fold = tok_bad + kTileRows;                                   // [8][3]
+
+	const int kvh = blockIdx.x;
+	const int tile = (int)gridDim.y - 1 - (int)blockIdx.y;      // the last (widest) tiles start first
+	const int G = d.heads / d.kv_heads;
+	const int r0 = tile * tq, nt = min(tq, b.m - r0);
+	const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, c = lane & 3;
+	const int mb = warp >> 1, ph = warp & 1;
+	// this lane's two query rows (token, head)
+	const int rho_a = mb * 16 + g, rho_b = rho_a + 8;
+	const int tok_a = rho_a / G, tok_b = rho_b / G;
+	const int head_a = rho_a - tok_a * G, head_b = rho_b - tok_b * G;
+	// uploaded before the step's first launch: the tile's first position and the sequence's page table
+	const int pos0 = b.rows[r0].pos;
+	const int32_t* pages = b.rows[r0].pages;
+	const int width = pos0 + nt;
+	const int nblk = (width + kTileKeys - 1) / kTileKeys;
+	const int8_t* kplane = pool.base + kv_plane_offset(d, pool, layer_index, kvh, 0);
+	const int8_t* vplane = pool.base + kv_plane_offset(d, pool, layer_index, kvh, 1);
+	if (t < 3 * G) l_fold[t] = layer->f_ctx[3 * kvh * G + t];
+	pdl_wait();
+	pdl_release();
+	if (t < kTileRows) {
+		int okv = 0;
+		if (t < nt) {
+			okv = __ldcg(&b.status[r0 + t]) == 0 ? 1 : 0;
+			fxs[t] = iexp_fast_prepare(b.smc[(size_t)(r0 + t) * d.kv_heads + kvh]);
+		}
+		tok_ok[t] = okv;
+		tok_bad[t] = 0;
+	}
+	__syncthreads();
+	const bool in_a = tok_a < nt && tok_ok[tok_a] != 0, in_b = tok_b < nt && tok_ok[tok_b] != 0;
+	const int lim_a = in_a ? pos0 + tok_a : -1, lim_b = in_b ? pos0 + tok_b : -1;    // last position each row sees
+	// q fragments (A operand) of this warp's MMA block, kept in registers for all three walks
+	uint32_t qa[KS][4];
+	{
+		const int8_t* qpa = b.qrot + (size_t)(r0 + (in_a ? tok_a : 0)) * d.hidden + (size_t)(kvh * G + head_a) * HD;
+		const int8_t* qpb = b.qrot + (size_t)(r0 + (in_b ? tok_b : 0)) * d.hidden + (size_t)(kvh * G + head_b) * HD;
+#pragma unroll
+		for (int ks = 0; ks < KS; ++ks) {
+			qa[ks][0] = in_a ? *(const uint32_t*)(qpa + 32 * ks + 4 * c) : 0u;
+			qa[ks][1] = in_b ? *(const uint32_t*)(qpb + 32 * ks + 4 * c) : 0u;
+			qa[ks][2] = in_a ? *(const uint32_t*)(qpa + 32 * ks + 16 + 4 * c) : 0u;
+			qa[ks][3] = in_b ? *(const uint32_t*)(qpb + 32 * ks + 16 + 4 * c) : 0u;
+		}
+	}
+	const IExpFast fa = fxs[in_a ? tok_a : 0], fb = fxs[in_b ? tok_b : 0];
+
+	// stage step `blk` of the prefix: K rows (and V pages) of positions blk * 64 ...; positions
+	// beyond the tile's width are left as they are (their scores are masked, their probabilities zero)
+	auto load_block = [&](int stage, int blk, bool with_v) {
+		int8_t* kd = Ks + (size_t)stage * kTileKeys * L::kKStride;
+		for (int idx = t; idx < kTileKeys * (HD / 16); idx += kTileThreads) {
+			const int row = idx / (HD / 16), piece = idx - row * (HD / 16);
+			const int pos = blk * kTileKeys + row;
+			if (pos < width)
+				cp_async16(kd + (size_t)row * L::kKStride + piece * 16,
+				           kplane + (int64_t)pages[pos >> 4] * (kPageTokens * HD) + (pos & 15) * HD + piece * 16);
+		}
+		if (with_v) {
+			int8_t* vd = Vs + (size_t)stage * kTileKeys * HD;
+			for (int idx = t; idx < 4 * HD; idx += kTileThreads) {
+				const int pg = idx / HD, piece = idx - pg * HD;
+				const int page = blk * 4 + pg;
+				if (page * kPageTokens < width)
+					cp_async16(vd + (size_t)pg * HD * kPageTokens + piece * 16,
+					           vplane + (int64_t)pages[page] * (kPageTokens * HD) + piece * 16);
+			}
+		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+	// scores of this warp's 16 rows x 32 positions of the staged step
+	auto scores = [&](int stage, int (&acc)[4][4]) {
+		const int8_t* kd = Ks + (size_t)stage * kTileKeys * L::kKStride;
+#pragma unroll
+		for (int j = 0; j < 4; ++j) {
+#pragma unroll
+			for (int q = 0; q < 4; ++q) acc[j][q] = 0;
+			const int8_t* krow = kd + (size_t)(32 * ph + 8 * j + g) * L::kKStride;
+#pragma unroll
+			for (int ks = 0; ks < KS; ++ks) {
+				const uint32_t b0 = *(const uint32_t*)(krow + 32 * ks + 4 * c);
+				const uint32_t b1 = *(const uint32_t*)(krow + 32 * ks + 16 + 4 * c);
+				mma_s8s8_full(acc[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+			}
+		}
+	};
+	// walk the prefix: `body(stage, blk)` runs with step blk staged; the next step loads meanwhile
+	auto walk = [&](bool with_v, auto&& body) {
+		load_block(0, 0, with_v);
+		for (int blk = 0; blk < nblk; ++blk) {
+			const int stage = blk & 1;
+			if (blk + 1 < nblk) {
+				load_block(stage ^ 1, blk + 1, with_v);
+				asm volatile("cp.async.wait_group 1;" ::: "memory");
+			} else {
+				asm volatile("cp.async.wait_group 0;" ::: "memory");
+			}
+			__syncthreads();
+			body(stage, blk);
+			__syncthreads();      // the stage (and the probability planes) may be overwritten
+		}
+	};
+
+	// ---- walk 1: row maxima
+	int mx_a = INT32_MIN, mx_b = INT32_MIN;
+	walk(false, [&](int stage, int blk) {
+		int acc[4][4];
+		scores(stage, acc);
+#pragma unroll
+		for (int j = 0; j < 4; ++j) {
+			const int k0 = blk * kTileKeys + 32 * ph + 8 * j + 2 * c;
+			if (k0 <= lim_a) mx_a = max(mx_a, acc[j][0]);
+			if (k0 + 1 <= lim_a) mx_a = max(mx_a, acc[j][1]);
+			if (k0 <= lim_b) mx_b = max(mx_b, acc[j][2]);
+			if (k0 + 1 <= lim_b) mx_b = max(mx_b, acc[j][3]);
+		}
+	});
+	mx_a = max(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+	mx_a = max(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+	mx_b = max(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+	mx_b = max(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+	if (c == 0) {
+		wmax[ph * kTileRows + rho_a] = mx_a;
+		wmax[ph * kTileRows + rho_b] = mx_b;
+	}
+	__syncthreads();
+	mx_a = max(wmax[rho_a], wmax[kTileRows + rho_a]);
+	mx_b = max(wmax[rho_b], wmax[kTileRows + rho_b]);
+
+	// ---- walk 2: exponentials and row totals
+	unsigned long long sum_a = 0, sum_b = 0;
+	bool bad_a = false, bad_b = false;
+	walk(false, [&](int stage, int blk) {
+		int acc[4][4];
+		scores(stage, acc);
+#pragma unroll
+		for (int j = 0; j < 4; ++j) {
+			const int k0 = blk * kTileKeys + 32 * ph + 8 * j + 2 * c;
+#pragma unroll
+			for (int q = 0; q < 2; ++q) {
+				int64_t e;
+				uint32_t parts;
+				if (k0 + q <= lim_a) {
+					const bool ok = iexp_fast((uint32_t)mx_a - (uint32_t)acc[j][q], fa, &e, &parts);
+					sum_a += ok ? (unsigned long long)e : 0ull;
+					bad_a |= !ok;
+				}
+				if (k0 + q <= lim_b) {
+					const bool ok = iexp_fast((uint32_t)mx_b - (uint32_t)acc[j][2 + q], fb, &e, &parts);
+					sum_b += ok ? (unsigned long long)e : 0ull;
+					bad_b |= !ok;
+				}
+			}
+		}
+	});
+	sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+	sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+	sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+	sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+	if (c == 0) {
+		wsum[ph * kTileRows + rho_a] = sum_a;
+		wsum[ph * kTileRows + rho_b] = sum_b;
+	}
+	if (bad_a) tok_bad[tok_a] = 1;
+	if (bad_b) tok_bad[tok_b] = 1;
+	__syncthreads();
+	sum_a = wsum[rho_a] + wsum[kTileRows + rho_a];
+	sum_b = wsum[rho_b] + wsum[kTileRows + rho_b];
+	const unsigned long long tot_a = sum_a > 1ull ? sum_a : 1ull, tot_b = sum_b > 1ull ? sum_b : 1ull;
+	const float inv_a = 32768.0f / (float)tot_a, inv_b = 32768.0f / (float)tot_b;
+	// a token with a refused element is refused as a whole (SoftmaxKernelRefusedAfterGateAccepted)
+	const bool go_a = in_a && tok_bad[tok_a] == 0, go_b = in_b && tok_bad[tok_b] == 0;
+	if (t < nt && tok_bad[t] != 0)
+		atomicCAS(&b.status[r0 + t], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
+
+	// ---- walk 3: probabilities and P.V
+	int accl[NGW][4], acch[NGW][4];
+#pragma unroll
+	for (int i = 0; i < NGW; ++i)
+#pragma unroll
+		for (int q = 0; q < 4; ++q) accl[i][q] = acch[i][q] = 0;
+	walk(true, [&](int stage, int blk) {
+		int acc[4][4];
+		scores(stage, acc);
+#pragma unroll
+		for (int j = 0; j < 4; ++j) {
+			const int col = 32 * ph + 8 * j + 2 * c;
+			const int k0 = blk * kTileKeys + col;
+			uint32_t pa[2], pb[2];
+#pragma unroll
+			for (int q = 0; q < 2; ++q) {
+				int64_t e;
+				uint32_t parts;
+				pa[q] = pb[q] = 0;
+				if (go_a && k0 + q <= lim_a) {
+					iexp_fast((uint32_t)mx_a - (uint32_t)acc[j][q], fa, &e, &parts);
+					pa[q] = prob_q15(e, tot_a, inv_a);
+				}
+				if (go_b && k0 + q <= lim_b) {
+					iexp_fast((uint32_t)mx_b - (uint32_t)acc[j][2 + q], fb, &e, &parts);
+					pb[q] = prob_q15(e, tot_b, inv_b);
+				}
+			}
+			*(uint16_t*)(Pl + (size_t)rho_a * kTilePStride + col) = (uint16_t)((pa[0] & 0xffu) | ((pa[1] & 0xffu) << 8));
+			*(uint16_t*)(Ph + (size_t)rho_a * kTilePStride + col) = (uint16_t)((pa[0] >> 8) | ((pa[1] >> 8) << 8));
+			*(uint16_t*)(Pl + (size_t)rho_b * kTilePStride + col) = (uint16_t)((pb[0] & 0xffu) | ((pb[1] & 0xffu) << 8));
+			*(uint16_t*)(Ph + (size_t)rho_b * kTilePStride + col) = (uint16_t)((pb[0] >> 8) | ((pb[1] >> 8) << 8));
+		}
+		// the two warps of an MMA block wrote its rows' 64 probabilities between them
+		asm volatile("bar.sync %0, 64;" ::"r"(1 + mb) : "memory");
+		const int8_t* vd = Vs + (size_t)stage * kTileKeys * HD;
+#pragma unroll
+		for (int ks = 0; ks < 2; ++ks) {
+			const uint8_t* la = Pl + (size_t)rho_a * kTilePStride + 32 * ks + 4 * c;
+			const uint8_t* lb = Pl + (size_t)rho_b * kTilePStride + 32 * ks + 4 * c;
+			const uint8_t* ha = Ph + (size_t)rho_a * kTilePStride + 32 * ks + 4 * c;
+			const uint8_t* hb = Ph + (size_t)rho_b * kTilePStride + 32 * ks + 4 * c;
+			const uint32_t l0 = *(const uint32_t*)la, l1 = *(const uint32_t*)lb, l2 = *(const uint32_t*)(la + 16), l3 = *(const uint32_t*)(lb + 16);
+			const uint32_t h0 = *(const uint32_t*)ha, h1 = *(const uint32_t*)hb, h2 = *(const uint32_t*)(ha + 16), h3 = *(const uint32_t*)(hb + 16);
+#pragma unroll
+			for (int i = 0; i < NGW; ++i) {
+				const int ch = 8 * (ph * NGW + i) + g;
+				const uint32_t b0 = *(const uint32_t*)(vd + (size_t)(2 * ks) * HD * kPageTokens + ch * kPageTokens + 4 * c);
+				const uint32_t b1 = *(const uint32_t*)(vd + (size_t)(2 * ks + 1) * HD * kPageTokens + ch * kPageTokens + 4 * c);
+				mma_u8s8_full(accl[i], l0, l1, l2, l3, b0, b1);
+				mma_u8s8_full(acch[i], h0, h1, h2, h3, b0, b1);
+			}
+		}
+	});
+
+	// ---- per-head context fold (forward_sites.cpp:1889-1896), store, row maximum for the funnel
+	uint32_t lm_a = 0, lm_b = 0;
+#pragma unroll
+	for (int i = 0; i < NGW; ++i) {
+		const int ch = 8 * (ph * NGW + i) + 2 * c;
+		if (go_a) {
+			int2 o;
+			o.x = fold(accl[i][0] + 256 * acch[i][0], l_fold[3 * head_a], l_fold[3 * head_a + 1], l_fold[3 * head_a + 2]);
+			o.y = fold(accl[i][1] + 256 * acch[i][1], l_fold[3 * head_a], l_fold[3 * head_a + 1], l_fold[3 * head_a + 2]);
+			*(int2*)(b.ctxw + (size_t)(r0 + tok_a) * d.hidden + (size_t)(kvh * G + head_a) * HD + ch) = o;
+			lm_a = max(lm_a, max(o.x < 0 ? 0u - (uint32_t)o.x : (uint32_t)o.x, o.y < 0 ? 0u - (uint32_t)o.y : (uint32_t)o.y));
+		}
+		if (go_b) {
+			int2 o;
+			o.x = fold(accl[i][2] + 256 * acch[i][2], l_fold[3 * head_b], l_fold[3 * head_b + 1], l_fold[3 * head_b + 2]);
+			o.y = fold(accl[i][3] + 256 * acch[i][3], l_fold[3 * head_b], l_fold[3 * head_b + 1], l_fold[3 * head_b + 2]);
+			*(int2*)(b.ctxw + (size_t)(r0 + tok_b) * d.hidden + (size_t)(kvh * G + head_b) * HD + ch) = o;
+			lm_b = max(lm_b, max(o.x < 0 ? 0u - (uint32_t)o.x : (uint32_t)o.x, o.y < 0 ? 0u - (uint32_t)o.y : (uint32_t)o.y));
+		}
+	}
+	lm_a = max(lm_a, __shfl_xor_sync(0xffffffffu, lm_a, 1));
+	lm_a = max(lm_a, __shfl_xor_sync(0xffffffffu, lm_a, 2));
+	lm_b = max(lm_b, __shfl_xor_sync(0xffffffffu, lm_b, 1));
+	lm_b = max(lm_b, __shfl_xor_sync(0xffffffffu, lm_b, 2));
+	if (c == 0) {
+		if (go_a && lm_a) atomicMax(&b.rowmax[(size_t)(r0 + tok_a) * 4 + 3], (unsigned long long)lm_a);
+		if (go_b && lm_b) atomicMax(&b.rowmax[(size_t)(r0 + tok_b) * 4 + 3], (unsigned long long)lm_b);
+	}
+}
+
+template <int HD>
+static cudaError_t launch_attn_tile(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index, KvPoolDev pool,
+                                    cudaStream_t st) {
+	const int G = d.heads / d.kv_heads;
+	const int tq = kTileRows / G;
+	return launch_pdl(k_attention_tile<HD>, dim3(d.kv_heads, (b.m + tq - 1) / tq), dim3(kTileThreads), TileSmem<HD>::kBytes, st, b,
+	                  d, layer, layer_index, pool, tq);
+}
+
 static int pad64(int w) { return (w + 63) / 64 * 64; }
 constexpr int kAttnMaxSlice = 2048;      // positions one block holds at most
 
@@ -584,13 +918,13 @@ static AttnPlan attn_plan(const Dims& d, int m, int max_width) {
 	if (forced > 0) {
 		while (splits * 2 <= forced && splits * 2 <= 16) splits *= 2;
 	} else {
-		// Slices of about 256 positions shorten each block's chain of dependent loads; when there
-		// are rows enough to fill the machine several times over (a prefill chunk) one slice per
-		// row has the least overhead; when there are few rows, more slices put more
-		// multiprocessors to work.
+		// A block's time is mostly a fixed chain of dependent steps, so cutting rows into slices
+		// pays only while the extra blocks still run side by side: with many rows (a decode batch
+		// of hundreds of sequences, a prefill chunk) a row is one slice; with few rows the width is
+		// cut until the blocks fill the machine once.
 		const int blocks = m * d.kv_heads;
-		int want = blocks >= 4 * sm_count() ? 1 : (max_width + 255) / 256;
-		while (want < 8 && blocks * want < sm_count()) want *= 2;
+		int want = 1;
+		while (want < 8 && blocks * want * 2 <= 4 * sm_count()) want *= 2;
 		while (splits * 2 <= want && splits * 2 <= 8) splits *= 2;
 		if (splits > per_kv_max) splits = per_kv_max;              // prefer the fused funnel ...
 	}
@@ -643,11 +977,33 @@ cudaError_t attn_configure(const Dims& d) {
 	e = cudaFuncSetAttribute(f, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
 	if (e != cudaSuccess) return e;
 	// same carve-out as the kernels around it (see rows_configure)
-	return cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+	e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+	if (e != cudaSuccess) return e;
+	const void* ft = nullptr;
+	size_t tile_bytes = 0;
+	if (d.head_dim == 128) { ft = (const void*)k_attention_tile<128>; tile_bytes = TileSmem<128>::kBytes; }
+	else if (d.head_dim == 64) { ft = (const void*)k_attention_tile<64>; tile_bytes = TileSmem<64>::kBytes; }
+	else { ft = (const void*)k_attention_tile<32>; tile_bytes = TileSmem<32>::kBytes; }
+	e = cudaFuncSetAttribute(ft, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_bytes);
+	if (e != cudaSuccess) return e;
+	return cudaFuncSetAttribute(ft, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
 bool launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
                       KvPoolDev pool, int max_width, int reverse_rows, cudaStream_t st, cudaError_t* err) {
+	// the rows of a prefill chunk (consecutive positions of one sequence) take the query-tiled kernel
+	static const bool tile_off = [] {
+		const char* e = getenv("SSLM_B200_ATTN_TILE");
+		return e && e[0] == '0';
+	}();
+	if (reverse_rows && b.m >= 4 && !tile_off) {
+		cudaError_t e;
+		if (d.head_dim == 128) e = launch_attn_tile<128>(b, d, layer, layer_index, pool, st);
+		else if (d.head_dim == 64) e = launch_attn_tile<64>(b, d, layer, layer_index, pool, st);
+		else e = launch_attn_tile<32>(b, d, layer, layer_index, pool, st);
+		if (err) *err = e;
+		return false;
+	}
 	const AttnPlan p = attn_plan(d, b.m, max_width);
 	cudaError_t e;
 	if (d.head_dim == 128) e = launch_attn<128>(b, d, layer, layer_index, pool, p, reverse_rows, st);

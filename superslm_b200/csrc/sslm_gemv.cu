@@ -31,11 +31,14 @@
 
 namespace sslm {
 
-constexpr int kGemvWarps = 8;
+// Sixteen warps per block and (shared memory allowing) two blocks per multiprocessor: a warp's
+// loop over its channels is one dependent chain (wait, load, dp4a, reduce), so the memory system
+// is kept busy by the number of warps that run such chains side by side, not by any one of them.
+constexpr int kGemvWarps = 16;
 constexpr int kGemvThreads = kGemvWarps * 32;
-constexpr int kSegBytes = 4096;                     // longest single copy (a row, or a segment of a long row)
-constexpr int kRingBytesPerWarp = 12 * 1024;
-constexpr int kMaxSlots = 8;
+constexpr int kSegBytes = 2048;                     // longest single copy (a row, or a segment of a long row)
+constexpr int kRingBytesPerWarp = 6 * 1024;
+constexpr int kMaxSlots = 4;
 constexpr uint32_t kGemvMaxPolls = 1u << 22;
 
 __device__ __forceinline__ int dot16(const int4& a, const int4& b, int acc) {
@@ -114,13 +117,18 @@ k_gemv(LinearArgs a, GemvPlan p) {
 	// this warp's work items: channel `warp + kGemvWarps * (i / nseg)` of the block, segment `i % nseg`
 	const int my_rows = nrows > warp ? (nrows - warp + kGemvWarps - 1) / kGemvWarps : 0;
 	const int items = my_rows * p.nseg;
-	auto issue = [&](int i) {      // (lane 0 only)
-		const int rl = warp + kGemvWarps * (i / p.nseg), sg = i % p.nseg;
-		const int first = sg * p.seg16, count = min(p.seg16, k16 - first);
-		const int s = i % p.slots;
-		bar_expect_tx(full_bar(s), (uint32_t)count * 16u);
-		bulk_load(smem_addr(ring + (size_t)s * slot_bytes), a.w + ((size_t)(n0 + rl) * K + (size_t)first * 16), (uint32_t)count * 16u,
-		          full_bar(s));
+	// requests are made in item order, so the request side keeps its own (channel, segment, slot) counters
+	int q_rl = warp, q_sg = 0, q_sl = 0;
+	auto issue = [&](int) {      // (lane 0 only)
+		const int first = q_sg * p.seg16, count = min(p.seg16, k16 - first);
+		bar_expect_tx(full_bar(q_sl), (uint32_t)count * 16u);
+		bulk_load(smem_addr(ring + (size_t)q_sl * slot_bytes), a.w + ((size_t)(n0 + q_rl) * K + (size_t)first * 16),
+		          (uint32_t)count * 16u, full_bar(q_sl));
+		if (++q_sg == p.nseg) {
+			q_sg = 0;
+			q_rl += kGemvWarps;
+		}
+		if (++q_sl == p.slots) q_sl = 0;
 	};
 
 	if (lane == 0) {
@@ -153,17 +161,18 @@ k_gemv(LinearArgs a, GemvPlan p) {
 #pragma unroll
 	for (int m = 0; m < MT; ++m) acc[m] = 0;
 	bool ok = true;
+	// item i = (channel rl, segment sg) in ring slot sl with wait parity par; item `nxt` is the next to request
+	int rl = warp, sg = 0, sl = 0;
+	uint32_t par = 0;
 	for (int i = 0; i < items; ++i) {
-		const int s = i % p.slots;
 		// (the whole warp agrees on the outcome of a wait)
-		if (!__all_sync(0xffffffffu, bar_wait(full_bar(s), (uint32_t)(i / p.slots) & 1u) ? 1 : 0)) {
+		if (!__all_sync(0xffffffffu, bar_wait(full_bar(sl), par) ? 1 : 0)) {
 			atomicExch(&s_timeout, 1);
 			ok = false;
 			break;
 		}
-		const int sg = i % p.nseg;
 		const int first = sg * p.seg16, count = min(p.seg16, k16 - first);
-		const int4* wv = (const int4*)(ring + (size_t)s * slot_bytes);
+		const int4* wv = (const int4*)(ring + (size_t)sl * slot_bytes);
 #pragma unroll 2
 		for (int c = lane; c < count; c += 32) {
 			const int4 w4 = wv[c];
@@ -171,18 +180,25 @@ k_gemv(LinearArgs a, GemvPlan p) {
 			for (int m = 0; m < MT; ++m) acc[m] = dot16(w4, ((const int4*)(sx + (size_t)m * K))[first + c], acc[m]);
 		}
 		__syncwarp();      // every lane has read the slot: it may be refilled
-		if (i + p.slots < items) {
-			if (lane == 0) issue(i + p.slots);
-			issued = i + p.slots + 1;
+		if (issued < items) {
+			if (lane == 0) issue(issued);
+			++issued;
 		}
 		if (sg == p.nseg - 1) {      // the channel is complete: one reduction per row of x
-			const int rl = warp + kGemvWarps * (i / p.nseg);
 #pragma unroll
 			for (int m = 0; m < MT; ++m) {
 				const int v = __reduce_add_sync(0xffffffffu, acc[m]);
 				if (lane == 0) sacc[m * p.rows_per_block + rl] = v;
 				acc[m] = 0;
 			}
+			sg = 0;
+			rl += kGemvWarps;
+		} else {
+			++sg;
+		}
+		if (++sl == p.slots) {
+			sl = 0;
+			par ^= 1u;
 		}
 	}
 	if (!ok && lane == 0) {
@@ -289,10 +305,11 @@ static cudaError_t launch_mt(const LinearArgs& a, int grid_y, cudaStream_t st) {
 	});
 	if (e != cudaSuccess) return e;
 	GemvPlan p;
-	// one block per multiprocessor when the matrix is large enough to keep them all streaming;
-	// never fewer channels per block than it has warps
+	// never fewer channels per block than it has warps;
+	// two blocks per multiprocessor when the activation rows leave room for two rings
 	const int sms = sm_count();
-	int rpb = (a.N + sms - 1) / sms;
+	const int per_sm = (size_t)MT * a.K <= 16 * 1024 ? 2 : 1;
+	int rpb = (a.N + per_sm * sms - 1) / (per_sm * sms);
 	if (rpb < kGemvWarps) rpb = kGemvWarps;
 	if (rpb > a.N) rpb = a.N;
 	p.rows_per_block = rpb;
@@ -306,6 +323,7 @@ static cudaError_t launch_mt(const LinearArgs& a, int grid_y, cudaStream_t st) {
 	if (slots < 2) slots = 2;
 	const int items_per_warp = ((rpb + kGemvWarps - 1) / kGemvWarps) * p.nseg;
 	if (slots > items_per_warp) slots = items_per_warp;
+	while (slots > 2 && gemv_smem_bytes(MT, a.K, rpb, slots, p.seg16) > 220 * 1024) --slots;   // long activation rows: shallower rings
 	p.slots = slots;
 	const size_t smem = gemv_smem_bytes(MT, a.K, rpb, slots, p.seg16);
 	if (smem > 220 * 1024) return cudaErrorInvalidConfiguration;
