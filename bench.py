@@ -71,6 +71,7 @@ def parse_args():
                     help="workload sequences compared with the CPU reference's records (up to 16)")
     ap.add_argument("--no-sweep", action="store_true", help="skip the standalone linear-layer grid")
     ap.add_argument("--no-single", action="store_true", help="skip the single-sequence measurement")
+    ap.add_argument("--only-sweep", action="store_true", help="just the standalone linear-layer grid (no model)")
     return ap.parse_args()
 
 
@@ -731,10 +732,19 @@ def run_reference(args):
     }))
 
 
+def run_only_sweep(args):
+    from superslm_b200 import build as B
+    lib = abi.SslmLib(B.LIB if os.path.exists(B.LIB) else B.build())
+    d = bind_extras(lib)
+    print(json.dumps({"linear_sweep": linear_sweep(d, A.SHAPES[args.shape])}))
+
+
 if __name__ == "__main__":
     a = parse_args()
     try:
-        if a.impl == "reference":
+        if a.only_sweep:
+            run_only_sweep(a)
+        elif a.impl == "reference":
             run_reference(a)
         else:
             run_ours(a)

@@ -32,11 +32,11 @@
 namespace sslm {
 
 // Sixteen warps per block and (shared memory allowing) two blocks per multiprocessor: a warp's
-// loop over its channels is one dependent chain (wait, load, dp4a, reduce), so the memory system
+// loop over its items is one dependent chain (wait, load, dp4a, reduce), so the memory system
 // is kept busy by the number of warps that run such chains side by side, not by any one of them.
 constexpr int kGemvWarps = 16;
 constexpr int kGemvThreads = kGemvWarps * 32;
-constexpr int kSegBytes = 2048;                     // longest single copy (a row, or a segment of a long row)
+constexpr int kItemBytes = 3072;                    // largest single copy: whole rows, or one segment of a long row
 constexpr int kRingBytesPerWarp = 6 * 1024;
 constexpr int kMaxSlots = 4;
 constexpr uint32_t kGemvMaxPolls = 1u << 22;
@@ -83,12 +83,16 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 
 }  // namespace
 
-// What the host decides per launch.
+// What the host decides per launch. A work item is one bulk copy: `rows_per_item` whole weight
+// rows when a row is short (then nseg = 1), else one of the `nseg` segments of one row. The items
+// of a block are dealt round-robin to its warps.
 struct GemvPlan {
 	int rows_per_block;   // output channels per block
-	int seg16;            // 16-byte pieces per copy (a whole row when K is short)
-	int nseg;             // copies per weight row
+	int rows_per_item;    // whole rows per copy (1 when rows are cut into segments)
+	int seg16;            // 16-byte pieces per segment (= K / 16 when nseg == 1)
+	int nseg;             // segments per weight row
 	int slots;            // ring slots per warp
+	int step_g, step_s;   // item index + kGemvWarps = (group + step_g, segment + step_s), segment taken mod nseg
 };
 
 // MT rows of x per pass (grid.y walks the row groups).
@@ -101,7 +105,7 @@ k_gemv(LinearArgs a, GemvPlan p) {
 	const int nrows = min(p.rows_per_block, a.N - n0);
 	const int m0 = blockIdx.y * MT;
 	const int mcount = min(MT, a.M - m0);
-	const int slot_bytes = p.seg16 * 16;
+	const int slot_bytes = p.rows_per_item * p.seg16 * 16;
 	// carve: rings | x rows | accumulators | fold rows | maxima | barriers
 	unsigned char* rings = smem;
 	int8_t* sx = (int8_t*)(rings + (size_t)kGemvWarps * p.slots * slot_bytes);
@@ -114,19 +118,26 @@ k_gemv(LinearArgs a, GemvPlan p) {
 	const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
 	unsigned char* ring = rings + (size_t)warp * p.slots * slot_bytes;
 	auto full_bar = [&](int s) { return bars + 8u * (warp * kMaxSlots + s); };
-	// this warp's work items: channel `warp + kGemvWarps * (i / nseg)` of the block, segment `i % nseg`
-	const int my_rows = nrows > warp ? (nrows - warp + kGemvWarps - 1) / kGemvWarps : 0;
-	const int items = my_rows * p.nseg;
-	// requests are made in item order, so the request side keeps its own (channel, segment, slot) counters
-	int q_rl = warp, q_sg = 0, q_sl = 0;
-	auto issue = [&](int) {      // (lane 0 only)
-		const int first = q_sg * p.seg16, count = min(p.seg16, k16 - first);
-		bar_expect_tx(full_bar(q_sl), (uint32_t)count * 16u);
-		bulk_load(smem_addr(ring + (size_t)q_sl * slot_bytes), a.w + ((size_t)(n0 + q_rl) * K + (size_t)first * 16),
-		          (uint32_t)count * 16u, full_bar(q_sl));
-		if (++q_sg == p.nseg) {
-			q_sg = 0;
-			q_rl += kGemvWarps;
+	// the block's items: (row group, segment), item q = group * nseg + segment; this warp takes
+	// q = warp, warp + kGemvWarps, ...
+	const int groups = (nrows + p.rows_per_item - 1) / p.rows_per_item;
+	const int total_items = groups * p.nseg;
+	const int items = total_items > warp ? (total_items - warp + kGemvWarps - 1) / kGemvWarps : 0;
+	// requests are made in item order, so the request side keeps its own (group, segment, slot) counters
+	int q_g = warp / p.nseg, q_s = warp % p.nseg, q_sl = 0;
+	auto issue = [&]() {      // (lane 0 only)
+		const int row0 = q_g * p.rows_per_item;
+		const int nr = min(p.rows_per_item, nrows - row0);
+		const int first = q_s * p.seg16, count = min(p.seg16, k16 - first);
+		const uint32_t bytes = (uint32_t)nr * (uint32_t)count * 16u;     // (nr > 1 only with whole rows: contiguous)
+		bar_expect_tx(full_bar(q_sl), bytes);
+		bulk_load(smem_addr(ring + (size_t)q_sl * slot_bytes), a.w + ((size_t)(n0 + row0) * K + (size_t)first * 16), bytes,
+		          full_bar(q_sl));
+		q_g += p.step_g;
+		q_s += p.step_s;
+		if (q_s >= p.nseg) {
+			q_s -= p.nseg;
+			++q_g;
 		}
 		if (++q_sl == p.slots) q_sl = 0;
 	};
@@ -137,14 +148,16 @@ k_gemv(LinearArgs a, GemvPlan p) {
 	}
 	if (t == 0) s_timeout = 0;
 	__syncwarp();
-	// ahead of the dependency wait: the first copies of every ring, the block's fold rows, cleared maxima
+	// ahead of the dependency wait: the first copies of every ring, the block's fold rows, cleared
+	// accumulators and maxima
 	int issued = items < p.slots ? items : p.slots;      // items whose copies have been requested
 	if (lane == 0)
-		for (int i = 0; i < issued; ++i) issue(i);
+		for (int i = 0; i < issued; ++i) issue();
 	if (a.fold != nullptr) {
 		const int32_t* f = a.fold + (size_t)n0 * 3;
 		for (int i = t; i < nrows * 3; i += kGemvThreads) sfold[i] = __ldg(f + i);
 	}
+	for (int i = t; i < MT * p.rows_per_block; i += kGemvThreads) sacc[i] = 0;
 	if (t < 4 * MT) smax[t] = 0ull;
 	pdl_wait();
 	pdl_release();
@@ -157,12 +170,9 @@ k_gemv(LinearArgs a, GemvPlan p) {
 	}
 	__syncthreads();
 
-	int acc[MT];
-#pragma unroll
-	for (int m = 0; m < MT; ++m) acc[m] = 0;
 	bool ok = true;
-	// item i = (channel rl, segment sg) in ring slot sl with wait parity par; item `nxt` is the next to request
-	int rl = warp, sg = 0, sl = 0;
+	// item being consumed: (group c_g, segment c_s) in ring slot sl with wait parity par
+	int c_g = warp / p.nseg, c_s = warp % p.nseg, sl = 0;
 	uint32_t par = 0;
 	for (int i = 0; i < items; ++i) {
 		// (the whole warp agrees on the outcome of a wait)
@@ -171,30 +181,41 @@ k_gemv(LinearArgs a, GemvPlan p) {
 			ok = false;
 			break;
 		}
-		const int first = sg * p.seg16, count = min(p.seg16, k16 - first);
+		const int row0 = c_g * p.rows_per_item;
+		const int nr = min(p.rows_per_item, nrows - row0);
+		const int first = c_s * p.seg16, count = min(p.seg16, k16 - first);
 		const int4* wv = (const int4*)(ring + (size_t)sl * slot_bytes);
-#pragma unroll 2
-		for (int c = lane; c < count; c += 32) {
-			const int4 w4 = wv[c];
+		for (int rr = 0; rr < nr; ++rr) {
+			int acc[MT];
 #pragma unroll
-			for (int m = 0; m < MT; ++m) acc[m] = dot16(w4, ((const int4*)(sx + (size_t)m * K))[first + c], acc[m]);
-		}
-		__syncwarp();      // every lane has read the slot: it may be refilled
-		if (issued < items) {
-			if (lane == 0) issue(issued);
-			++issued;
-		}
-		if (sg == p.nseg - 1) {      // the channel is complete: one reduction per row of x
+			for (int m = 0; m < MT; ++m) acc[m] = 0;
+#pragma unroll 2
+			for (int c = lane; c < count; c += 32) {
+				const int4 w4 = wv[rr * count + c];
+#pragma unroll
+				for (int m = 0; m < MT; ++m) acc[m] = dot16(w4, ((const int4*)(sx + (size_t)m * K))[first + c], acc[m]);
+			}
+			// one reduction per (row of x, weight row segment); segments of one weight row may
+			// belong to different warps, so the sums meet in shared memory
 #pragma unroll
 			for (int m = 0; m < MT; ++m) {
 				const int v = __reduce_add_sync(0xffffffffu, acc[m]);
-				if (lane == 0) sacc[m * p.rows_per_block + rl] = v;
-				acc[m] = 0;
+				if (lane == 0) {
+					if (p.nseg == 1) sacc[m * p.rows_per_block + row0 + rr] = v;
+					else atomicAdd(&sacc[m * p.rows_per_block + row0 + rr], v);
+				}
 			}
-			sg = 0;
-			rl += kGemvWarps;
-		} else {
-			++sg;
+		}
+		__syncwarp();      // every lane has read the slot: it may be refilled
+		if (issued < items) {
+			if (lane == 0) issue();
+			++issued;
+		}
+		c_g += p.step_g;
+		c_s += p.step_s;
+		if (c_s >= p.nseg) {
+			c_s -= p.nseg;
+			++c_g;
 		}
 		if (++sl == p.slots) {
 			sl = 0;
@@ -290,8 +311,8 @@ k_gemv(LinearArgs a, GemvPlan p) {
 }
 
 // shared memory of one block: rings, activation rows, accumulators, fold rows, maxima, barriers
-static size_t gemv_smem_bytes(int mt, int K, int rows_per_block, int slots, int seg16) {
-	return (size_t)kGemvWarps * slots * seg16 * 16 + (size_t)mt * K + (size_t)mt * rows_per_block * 4 +
+static size_t gemv_smem_bytes(int mt, int K, int rows_per_block, int slots, int slot_bytes) {
+	return (size_t)kGemvWarps * slots * slot_bytes + (size_t)mt * K + (size_t)mt * rows_per_block * 4 +
 	       (size_t)rows_per_block * 12 + 8 + (size_t)4 * mt * 8 + (size_t)kGemvWarps * kMaxSlots * 8 + 16;
 }
 
@@ -305,27 +326,41 @@ static cudaError_t launch_mt(const LinearArgs& a, int grid_y, cudaStream_t st) {
 	});
 	if (e != cudaSuccess) return e;
 	GemvPlan p;
-	// never fewer channels per block than it has warps;
-	// two blocks per multiprocessor when the activation rows leave room for two rings
+	const int k16 = a.K / 16;
+	// a copy carries whole rows while a row is short, else one segment of a row
+	if (a.K * 2 <= kItemBytes) {
+		p.rows_per_item = kItemBytes / a.K;
+		p.nseg = 1;
+		p.seg16 = k16;
+	} else {
+		p.rows_per_item = 1;
+		p.nseg = (a.K + kItemBytes - 1) / kItemBytes;
+		p.seg16 = (k16 + p.nseg - 1) / p.nseg;
+		p.nseg = (k16 + p.seg16 - 1) / p.seg16;
+	}
+	// Two blocks per multiprocessor when the activation rows leave room for two rings. A block
+	// takes whole row groups; it should have at least one item per warp, but never so many rows
+	// that blocks are fewer than the multiprocessors while rows remain to hand out.
 	const int sms = sm_count();
 	const int per_sm = (size_t)MT * a.K <= 16 * 1024 ? 2 : 1;
 	int rpb = (a.N + per_sm * sms - 1) / (per_sm * sms);
-	if (rpb < kGemvWarps) rpb = kGemvWarps;
+	const int min_rows = (kGemvWarps + p.nseg - 1) / p.nseg * p.rows_per_item;      // rows that make one item per warp
+	if (rpb < min_rows && (a.N + min_rows - 1) / min_rows >= sms) rpb = min_rows;
+	rpb = (rpb + p.rows_per_item - 1) / p.rows_per_item * p.rows_per_item;
 	if (rpb > a.N) rpb = a.N;
 	p.rows_per_block = rpb;
-	// a weight row travels as one copy when it is short, else in segments of 4 KiB
-	const int k16 = a.K / 16;
-	p.seg16 = k16 < kSegBytes / 16 ? k16 : kSegBytes / 16;
-	p.nseg = (k16 + p.seg16 - 1) / p.seg16;
-	// ring slots per warp: as many as fit its share of the ring, fewer when the block has little to stream
-	int slots = kRingBytesPerWarp / (p.seg16 * 16);
+	p.step_g = kGemvWarps / p.nseg;
+	p.step_s = kGemvWarps % p.nseg;
+	const int slot_bytes = p.rows_per_item * p.seg16 * 16;
+	int slots = kRingBytesPerWarp / slot_bytes;
 	if (slots > kMaxSlots) slots = kMaxSlots;
 	if (slots < 2) slots = 2;
-	const int items_per_warp = ((rpb + kGemvWarps - 1) / kGemvWarps) * p.nseg;
+	const int groups = (rpb + p.rows_per_item - 1) / p.rows_per_item;
+	const int items_per_warp = (groups * p.nseg + kGemvWarps - 1) / kGemvWarps;
 	if (slots > items_per_warp) slots = items_per_warp;
-	while (slots > 2 && gemv_smem_bytes(MT, a.K, rpb, slots, p.seg16) > 220 * 1024) --slots;   // long activation rows: shallower rings
+	while (slots > 2 && gemv_smem_bytes(MT, a.K, rpb, slots, slot_bytes) > 220 * 1024) --slots;   // long activation rows: shallower rings
 	p.slots = slots;
-	const size_t smem = gemv_smem_bytes(MT, a.K, rpb, slots, p.seg16);
+	const size_t smem = gemv_smem_bytes(MT, a.K, rpb, slots, slot_bytes);
 	if (smem > 220 * 1024) return cudaErrorInvalidConfiguration;
 	const int gx = (a.N + rpb - 1) / rpb;
 	return launch_pdl(k_gemv<MT>, dim3(gx, grid_y), dim3(kGemvThreads), smem, st, a, p);

@@ -36,6 +36,7 @@ def lib():
         "dev_iexp_element": (C.c_int, [i64] * 5 + [P64]),
         "dev_bias_reconcile": (C.c_int, [i64] * 3 + [P64]),
         "dev_bias_accumulate": (C.c_int, [i64] * 2 + [P64]),
+        "dev_dyn_recip_sweep": (i64, [i64, i64, i64, P64]),
     }
     for n, (r, a) in sig.items():
         f = getattr(d, n)

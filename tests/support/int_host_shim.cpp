@@ -68,4 +68,20 @@ int dev_iexp_element(int64_t q, int64_t ln2, int64_t b, int64_t c, int64_t peak,
 	IExpConsts k{ln2, b, c};
 	return iexp_element(q, k, peak, v) ? 1 : 0;
 }
+
+// dyn_recip's one-division form against the reference's operation sequence (seed, three Newton
+// steps, two corrections) on normalised divisors start, start + stride, ... : mismatches found
+// (the first one through *first_bad). With stride 1 and count 2^30 this is the exhaustive check.
+int64_t dev_dyn_recip_sweep(int64_t start, int64_t stride, int64_t count, int64_t* first_bad) {
+	int64_t bad = 0;
+	for (int64_t i = 0; i < count; ++i) {
+		const int64_t dn = start + i * stride;
+		if (dn < ((int64_t)1 << 30) || dn >= ((int64_t)1 << 31)) break;
+		if (dyn_recip(dn) != dyn_recip_sequence(dn)) {
+			if (bad == 0 && first_bad) *first_bad = dn;
+			++bad;
+		}
+	}
+	return bad;
+}
 }

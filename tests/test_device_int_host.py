@@ -199,3 +199,22 @@ def test_iexp_constants_and_elements(port):
             assert dom in (0, 4)
             assert v1.value == v2.value
             assert bool(ok) == (0 <= v2.value <= pk.value)
+
+
+def test_single_division_reciprocal_equals_the_newton_sequence(port):
+    """dyn_recip replaces DynamicScaleReciprocal's seed / Newton / correction sequence by one
+    rounded division on normalised divisors [2^30, 2^31). Checked against the sequence (itself
+    held to the oracle above) on every 1021st divisor plus both ends; SSLM_EXHAUSTIVE=1 walks
+    all 2^30 of them (about a minute)."""
+    import os
+    d = devint.lib()
+    first = I64(0)
+    lo, hi = 1 << 30, 1 << 31
+    if os.environ.get("SSLM_EXHAUSTIVE") == "1":
+        assert d.dev_dyn_recip_sweep(lo, 1, hi - lo, C.byref(first)) == 0, first.value
+    else:
+        assert d.dev_dyn_recip_sweep(lo, 1021, (hi - lo) // 1021 + 1, C.byref(first)) == 0, first.value
+        assert d.dev_dyn_recip_sweep(lo, 1, 1 << 16, C.byref(first)) == 0, first.value
+        assert d.dev_dyn_recip_sweep(hi - (1 << 16), 1, 1 << 16, C.byref(first)) == 0, first.value
+    for dn in (lo, lo + 1, hi - 1, 1090717716, 1156622235):
+        assert d.dev_dyn_recip(dn) == port.osc_dyn_recip(dn)
