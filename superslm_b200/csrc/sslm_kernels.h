@@ -89,13 +89,12 @@ cudaError_t rows_configure(const Dims& d);
 void launch_begin(const RowBatch& b, const Dims& d, const int8_t* embed, Scale c_embed,
                   const RowSource* src, const LayerDev* layer, cudaStream_t st);
 void launch_rmsnorm(const RowBatch& b, const Dims& d, const int8_t* gain, Scale site, cudaStream_t st);
-void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev& h, int layer_index,
+void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
                      KvPoolDev pool, const int32_t* cos, const int32_t* sin, cudaStream_t st);
-void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev& h, cudaStream_t st);
-// (layer / next: device copies of the layer records; h / h_next: the host copies of the same)
-void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev& h, cudaStream_t st);
-void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev& h, const LayerDev* next,
-                 const LayerDev* h_next, cudaStream_t st);
+void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st);
+void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st);
+void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev* next,
+                 cudaStream_t st);
 void launch_act(const RowBatch& b, const Dims& d, const LayerDev* layer, const int32_t* silu,
                 cudaStream_t st);
 void launch_scatter(const RowBatch& b, const Dims& d, const RowSink* sink, cudaStream_t st);

@@ -809,355 +809,6 @@ k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	set_status(b, r, st, site, site_layer);
 }
 
-// ------------------------------------------------------------ warp-per-row residual sites
-// The same two sites (projection funnel -> residual reconciliation -> RMSNorm) with one WARP per
-// row instead of one block: a lane owns n / 32 elements in groups of four and keeps them in
-// registers from the staged projection row to the last code, every reduction is a warp
-// reduction (no block barrier anywhere), and the per-row scalar derivations are computed by 32
-// lanes instead of 256 threads. A block-per-row kernel is one long chain of short phases
-// separated by barriers, so its time is that chain's latency whatever the row count; here a
-// row's chain is shorter and many rows' chains run side by side on one multiprocessor. Used for
-// rows of up to 2048 elements (a multiple of 128) held as int32; wider rows and rows with
-// adapters (int64 accumulators) take the block-per-row kernels above.
-constexpr int kWarpRowGroups = 16;       // 4-element groups per lane: n <= 2048
-constexpr int kWarpRowsPerBlock = 4;
-
-struct ResidualSite {
-	const Scale* proj_in_scale;   // [m] incoming scale of the projection's funnel
-	Scale c_proj, c_res;          // site constants: projection, residual
-	const int8_t* stream;         // [m, n] stream codes the branch is reconciled with
-	const Scale* stream_scale;    // [m]
-	int8_t* out;                  // [m, n] reconciled stream codes
-	Scale* out_scale;             // [m]
-	const int8_t* gain;           // [n] gain of the RMSNorm that follows, or nullptr
-	Scale c_norm;
-	int site_proj, site_res;      // where a refusal is recorded
-	int norm_next_layer;          // 1: the RMSNorm belongs to the next layer (and the residual completes this one)
-};
-
-__device__ __forceinline__ unsigned long long warp_max_u64_all(unsigned long long v) { return warp_max_u64(v); }
-
-__global__ void __launch_bounds__(kWarpRowsPerBlock * 32)
-k_residual_w(RowBatch b, Dims d, ResidualSite s) {
-	__shared__ int64_t s_lut[kWarpRowsPerBlock][256];
-	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-	const int r = blockIdx.x * kWarpRowsPerBlock + warp;
-	const int n = d.hidden, ng = n >> 7;          // groups of four elements per lane
-	if (r >= b.m) return;
-	// ahead of the projection: the stream row and its scale, the scale the projection's input
-	// carried, the gain, and every scalar that needs only those
-	uint32_t sw[kWarpRowGroups], gw[kWarpRowGroups];
-	const uint32_t* srow = (const uint32_t*)(s.stream + (size_t)r * n);
-#pragma unroll
-	for (int j = 0; j < kWarpRowGroups; ++j) {
-		sw[j] = 0;
-		gw[j] = 0;
-		if (j < ng) {
-			sw[j] = srow[lane + 32 * j];
-			if (s.gain != nullptr) gw[j] = ((const uint32_t*)s.gain)[lane + 32 * j];
-		}
-	}
-	const Scale in_scale = s.proj_in_scale[r], ss = s.stream_scale[r];
-	const FunnelFold fold_proj = funnel_prefold(&in_scale, 1, s.c_proj);
-	const FunnelFold fold_res = funnel_prefold(&ss, 1, s.c_res);
-	const int64_t r_h = dyn_recip(ss.m);
-	pdl_wait();
-	pdl_release();
-	const unsigned long long mx = __ldcg(&b.rowmax[(size_t)r * 4]);
-	const int32_t row_status = __ldcg(&b.status[r]);
-	__syncwarp();
-	if (lane == 0) b.rowmax[(size_t)r * 4] = 0ull;      // left zero for the slot's next producer
-	if (row_status != 0) return;
-	auto refuse = [&](int32_t st, int site, int layer) {
-		if (lane == 0) atomicCAS(&b.status[r], 0, pack_status(st, site, layer));
-	};
-	// ---- projection funnel
-	const FunnelParams fp = funnel_finish(mx, fold_proj);
-	if (fp.status != kOk) {
-		refuse(fp.status, s.site_proj, b.layer);
-		return;
-	}
-	const Coder cd = make_coder(fp.r, fp.s);
-	const Scale bs = fp.out;
-	// ---- residual reconciliation: wide_i = LandingRescale(branch_i, S[branch], Recip(S[stream].m), ...) + stream_i
-	if (!fits_i32(ss.m)) {
-		refuse(kCarriedScaleMantissaOutOfDomain, s.site_res, b.layer);
-		return;
-	}
-	// LandingRescale with the row's constants hoisted: for 33 <= k <= 94 and |m| < 2^31, 0 < R <= 2^32
-	// the rounded quotient of |code| * |m| * R by 2^k is ((|code| * P) >> 32 + 2^(k-33)) >> (k - 32)
-	// with P = |m| * R (the short form of landing_rescale, where its proof is)
-	int64_t k = sat_sub64(62, sat_sub64(bs.e, ss.e));
-	if (k > 4096) k = 4096;
-	if (k < -4096) k = -4096;
-	const uint64_t am = bs.m < 0 ? (~(uint64_t)bs.m + 1u) : (uint64_t)bs.m;
-	const bool fast = k >= 33 && k <= 94 && am < ((uint64_t)1 << 31) && r_h > 0 && (uint64_t)r_h <= ((uint64_t)1 << 32);
-	const uint64_t pp = am * (uint64_t)r_h;
-	const uint64_t p_hi = pp >> 32, p_lo = pp & 0xFFFFFFFFull;
-	const uint64_t half = fast ? ((uint64_t)1 << (k - 33)) : 0;
-	const int sh = fast ? (int)(k - 32) : 0;
-	const bool neg_m = bs.m < 0;
-	const int32_t* wrow = wide_row32(b, r);
-	uint32_t mag[kWarpRowGroups][4];       // |wide_i|, saturated at 2^32 - 1 (a row that large is refused)
-	uint64_t negbits = 0;                  // sign of wide_i, bit 4 * j + q
-	unsigned long long lmax = 0;
-	bool exceeded = false;
-#pragma unroll
-	for (int j = 0; j < kWarpRowGroups; ++j) {
-		if (j < ng) {
-			const int4 pv = __ldcg((const int4*)wrow + lane + 32 * j);
-			const int pvv[4] = {pv.x, pv.y, pv.z, pv.w};
-#pragma unroll
-			for (int q = 0; q < 4; ++q) {
-				const int c = code_of(pvv[q], cd);
-				int64_t v;
-				if (fast) {
-					const uint64_t ac = (uint64_t)(c < 0 ? -c : c);
-					const uint64_t a = ac * p_hi + ((ac * p_lo) >> 32);
-					const uint64_t qm = (a + half) >> sh;
-					v = ((c < 0) != neg_m) ? -(int64_t)qm : (int64_t)qm;
-				} else {
-					bool ex;
-					v = landing_rescale((int64_t)c, bs.m, r_h, bs.e, ss.e, nullptr, &ex);
-					exceeded |= ex;
-				}
-				v += (int64_t)(int8_t)(sw[j] >> (8 * q));
-				const unsigned long long a = abs_u64(v);
-				lmax = a > lmax ? a : lmax;
-				mag[j][q] = a > 0xFFFFFFFFull ? 0xFFFFFFFFu : (uint32_t)a;
-				if (v < 0) negbits |= (uint64_t)1 << (4 * j + q);
-			}
-		}
-	}
-	if (__any_sync(0xffffffffu, exceeded ? 1 : 0)) {
-		refuse(kResidualMagnitudeOutOfDomain, s.site_res, b.layer);
-		return;
-	}
-	lmax = warp_max_u64(lmax);
-	const FunnelParams fr = funnel_finish(lmax, fold_res);
-	if (fr.status != kOk) {
-		refuse(fr.status, s.site_res, b.layer);
-		return;
-	}
-	// ---- codes of the reconciled stream (every magnitude is at most 2^31 here: the funnel accepted the row)
-	const Coder cr = make_coder(fr.r, fr.s);
-	uint32_t aw[kWarpRowGroups];
-	int sumsq = 0;
-	uint32_t* orow = (uint32_t*)(s.out + (size_t)r * n);
-#pragma unroll
-	for (int j = 0; j < kWarpRowGroups; ++j) {
-		aw[j] = 0;
-		if (j < ng) {
-#pragma unroll
-			for (int q = 0; q < 4; ++q) {
-				const bool neg = (negbits >> (4 * j + q)) & 1u;
-				int c;
-				if (cr.narrow) c = code_narrow(mag[j][q], neg, cr);
-				else c = requant_code_general(neg ? -(int64_t)mag[j][q] : (int64_t)mag[j][q], cr.r, cr.s);
-				sumsq += c * c;
-				aw[j] |= (uint32_t)(uint8_t)c << (8 * q);
-			}
-			orow[lane + 32 * j] = aw[j];
-		}
-	}
-	if (lane == 0) {
-		s.out_scale[r] = fr.out;
-		if (s.norm_next_layer) b.done[r] += 1;      // the layer is complete for this row
-	}
-	if (s.gain == nullptr) return;
-	// ---- RMSNorm of the reconciled stream (RmsNormSite): root, floor((h << 32) / root) * gain, funnel
-	const int norm_layer = b.layer + (s.norm_next_layer ? 1 : 0);
-	const long long ssq = (long long)__reduce_add_sync(0xffffffffu, (uint32_t)sumsq);     // n * 127^2 < 2^32
-	const double inv_n = rcp_estimate((double)n);
-	int64_t root = isqrt64((int64_t)udiv_small_quotient((uint64_t)ssq << 32, (uint64_t)n, inv_n));
-	if (root < 1) root = 1;
-	const double inv_root = rcp_estimate((double)root);
-	int64_t* lut = s_lut[warp];
-	for (int t = lane; t < 255; t += 32) lut[t] = floor_div_h32(t - 127, root, inv_root);
-	__syncwarp();
-	unsigned long long nmax = 0;
-	int32_t wv[kWarpRowGroups][4];         // |.| <= sqrt(n) * 2^16 * 127 < 2^31 for n <= 2048
-#pragma unroll
-	for (int j = 0; j < kWarpRowGroups; ++j) {
-		if (j < ng) {
-#pragma unroll
-			for (int q = 0; q < 4; ++q) {
-				const int64_t v = lut[(int)(int8_t)(aw[j] >> (8 * q)) + 127] * (int64_t)(int8_t)(gw[j] >> (8 * q));
-				wv[j][q] = (int32_t)v;
-				const unsigned long long a = abs_u64(v);
-				nmax = a > nmax ? a : nmax;
-			}
-		}
-	}
-	nmax = warp_max_u64(nmax);
-	const FunnelParams fn = funnel_finish(nmax, funnel_prefold(nullptr, 0, s.c_norm));
-	if (fn.status != kOk) {
-		refuse(fn.status, kSiteAttnNorm + (s.norm_next_layer ? 0 : (kSiteMlpNorm - kSiteAttnNorm)), norm_layer);
-		return;
-	}
-	const Coder cn = make_coder(fn.r, fn.s);
-	uint32_t* nrow = (uint32_t*)(b.nrm + (size_t)r * n);
-#pragma unroll
-	for (int j = 0; j < kWarpRowGroups; ++j) {
-		if (j < ng) {
-			uint32_t w = 0;
-#pragma unroll
-			for (int q = 0; q < 4; ++q) w |= (uint32_t)(uint8_t)code_of(wv[j][q], cn) << (8 * q);
-			nrow[lane + 32 * j] = w;
-		}
-	}
-	if (lane == 0) b.ns[r] = fn.out;
-}
-
-// Attention-context funnel, one warp per row (forward_sites.cpp:1898-1903).
-__global__ void __launch_bounds__(kWarpRowsPerBlock * 32)
-k_ctx_funnel_w(RowBatch b, Dims d, Scale c_ctx) {
-	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-	const int r = blockIdx.x * kWarpRowsPerBlock + warp;
-	const int n = d.hidden, ng = n >> 7;
-	if (r >= b.m) return;
-	const FunnelFold fold_ctx = funnel_prefold(nullptr, 0, c_ctx);
-	pdl_wait();
-	pdl_release();
-	const unsigned long long mx = __ldcg(&b.rowmax[(size_t)r * 4 + 3]);
-	const int32_t row_status = __ldcg(&b.status[r]);
-	__syncwarp();
-	if (lane == 0) b.rowmax[(size_t)r * 4 + 3] = 0ull;
-	if (row_status != 0) return;
-	const FunnelParams fp = funnel_finish(mx, fold_ctx);
-	if (fp.status != kOk) {
-		if (lane == 0) atomicCAS(&b.status[r], 0, pack_status(fp.status, kSiteCtx, b.layer));
-		return;
-	}
-	const Coder cd = make_coder(fp.r, fp.s);
-	const int4* w = (const int4*)(b.ctxw + (size_t)r * n);
-	uint32_t* out = (uint32_t*)(b.ctx + (size_t)r * n);
-#pragma unroll 4
-	for (int j = 0; j < ng; ++j) {
-		const int4 p = __ldcg(w + lane + 32 * j);
-		out[lane + 32 * j] = (uint32_t)(uint8_t)code_of(p.x, cd) | ((uint32_t)(uint8_t)code_of(p.y, cd) << 8) |
-		                     ((uint32_t)(uint8_t)code_of(p.z, cd) << 16) | ((uint32_t)(uint8_t)code_of(p.w, cd) << 24);
-	}
-	if (lane == 0) b.cs[r] = fp.out;
-}
-
-// After the fused q/k/v projection, one warp per row: q funnel, K/V landing with the saturation
-// counter, RoPE on q and on the landed K, the page write, and the per-kv-head softmax constants
-// with their gates -- the sites of k_qkv_post, for layers without q/k/v biases.
-__global__ void __launch_bounds__(kWarpRowsPerBlock * 32)
-k_qkv_post_w(RowBatch b, Dims d, const LayerDev* layer, Scale c_q, int layer_index, KvPoolDev pool,
-             const int32_t* rope_cos, const int32_t* rope_sin) {
-	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-	const int r = blockIdx.x * kWarpRowsPerBlock + warp;
-	const int H = d.hidden, hd = d.head_dim, half = hd >> 1, KVH = d.kv_hidden;
-	const int ngq = H >> 7;                       // q groups per lane
-	const int ngkv = (KVH + 127) >> 7;            // k (and v) groups per lane; the last may be partly beyond the row
-	if (r >= b.m) return;
-	// ahead of the projection: the normed row's scale, the position, its page, the landing constants
-	const LayerDev& lw = *layer;
-	const Scale ns = b.ns[r];
-	const int pos = b.rows[r].pos;
-	const int page = b.rows[r].pages[pos / kPageTokens];
-	const int slot = pos % kPageTokens;
-	const int32_t* cos_row = rope_cos + (size_t)pos * half;
-	const int32_t* sin_row = rope_sin + (size_t)pos * half;
-	const FunnelFold fold_q = funnel_prefold(&ns, 1, c_q);
-	pdl_wait();
-	pdl_release();
-	const unsigned long long mx = __ldcg(&b.rowmax[(size_t)r * 4]);
-	const int32_t row_status = __ldcg(&b.status[r]);
-	__syncwarp();
-	if (lane == 0) b.rowmax[(size_t)r * 4] = 0ull;
-	if (row_status != 0) return;
-	const FunnelParams fp = funnel_finish(mx, fold_q);
-	if (fp.status != kOk) {
-		if (lane == 0) atomicCAS(&b.status[r], 0, pack_status(fp.status, kSiteQ, b.layer));
-		return;
-	}
-	const Coder cd = make_coder(fp.r, fp.s);
-	const int32_t* wrow = wide_row32(b, r);
-	// two interleaved pairs (one word of codes) rotated by the table row of this position
-	auto rope_word = [&](uint32_t w4, int pi) -> uint32_t {
-		const int2 c = __ldg((const int2*)&cos_row[pi]), sn = __ldg((const int2*)&sin_row[pi]);
-		int8_t o0, o1, o2, o3;
-		rope_pair_clamped((int8_t)w4, (int8_t)(w4 >> 8), c.x, sn.x, &o0, &o1);
-		rope_pair_clamped((int8_t)(w4 >> 16), (int8_t)(w4 >> 24), c.y, sn.y, &o2, &o3);
-		return (uint32_t)(uint8_t)o0 | ((uint32_t)(uint8_t)o1 << 8) | ((uint32_t)(uint8_t)o2 << 16) |
-		       ((uint32_t)(uint8_t)o3 << 24);
-	};
-	// ---- q: codes, rotation
-	uint32_t* qrot = (uint32_t*)(b.qrot + (size_t)r * H);
-#pragma unroll 4
-	for (int j = 0; j < ngq; ++j) {
-		const int gi = lane + 32 * j;                     // group index: elements 4 gi .. 4 gi + 3
-		const int4 p = __ldcg((const int4*)wrow + gi);
-		const uint32_t w4 = (uint32_t)(uint8_t)code_of(p.x, cd) | ((uint32_t)(uint8_t)code_of(p.y, cd) << 8) |
-		                    ((uint32_t)(uint8_t)code_of(p.z, cd) << 16) | ((uint32_t)(uint8_t)code_of(p.w, cd) << 24);
-		qrot[gi] = rope_word(w4, (2 * gi) % half);
-	}
-	// ---- K / V landing (LandTokenKVRow): clamp127(LandingRescale(acc, S[n], R_t, ...)), saturation counter
-	int sat = 0;
-	for (int j = 0; j < ngkv; ++j) {
-		const int gi = lane + 32 * j;
-		if (4 * gi < KVH) {
-			const int h = (4 * gi) / hd, dd = 4 * gi - h * hd;
-			const int64_t k_rt = lw.k_recip[3 * h + 2], k_et = lw.k_recip[3 * h + 1];
-			const int64_t v_rt = lw.v_recip[3 * h + 2], v_et = lw.v_recip[3 * h + 1];
-			const int4 kp = __ldcg((const int4*)(wrow + H) + gi), vp = __ldcg((const int4*)(wrow + H + KVH) + gi);
-			const int ka[4] = {kp.x, kp.y, kp.z, kp.w}, va[4] = {vp.x, vp.y, vp.z, vp.w};
-			uint32_t kw = 0;
-			int8_t* vdst = pool.base + kv_plane_offset(d, pool, layer_index, h, 1) + ((int64_t)page * hd + dd) * kPageTokens + slot;
-#pragma unroll
-			for (int q = 0; q < 4; ++q) {
-				bool s1, s2;
-				const int64_t kraw = landing_rescale((int64_t)ka[q], ns.m, k_rt, ns.e, k_et, &s1, nullptr);
-				const int64_t vraw = landing_rescale((int64_t)va[q], ns.m, v_rt, ns.e, v_et, &s2, nullptr);
-				sat += (s1 ? 1 : 0) + (s2 ? 1 : 0);
-				kw |= (uint32_t)(uint8_t)(int8_t)clamp127(kraw) << (8 * q);
-				vdst[q * kPageTokens] = (int8_t)clamp127(vraw);      // V pages are stored transposed: [head_dim][16 positions]
-			}
-			int8_t* kdst = pool.base + kv_plane_offset(d, pool, layer_index, h, 0) + ((int64_t)page * kPageTokens + slot) * hd + dd;
-			*(uint32_t*)kdst = rope_word(kw, dd / 2);
-		}
-	}
-	sat = (int)__reduce_add_sync(0xffffffffu, (uint32_t)sat);
-	if (lane == 0 && sat) b.sat[r] += (unsigned long long)sat;
-	// ---- softmax constants per kv head: sm = Combine(S[q], softmax_khead) -> C30 constants -> width gate
-	int32_t st = kOk;
-	if (lane < d.kv_heads) {
-		const int h = lane;
-		const Scale kh = Scale{lw.sm_khead[2 * h], lw.sm_khead[2 * h + 1]};
-		SoftmaxConsts sc;
-		sc.c = IExpConsts{0, 0, 0};
-		sc.peak = 0;
-		if (!fits_i32(fp.out.m) || !fits_i32(kh.m)) {
-			st = kCarriedScaleMantissaOutOfDomain;
-		} else {
-			const Scale sm = combine(fp.out, kh);
-			if (!fits_i32(sm.m)) st = kCarriedScaleMantissaOutOfDomain;
-			else if (iexp_scale_constants(sm.m, sm.e, &sc.c) != 0) st = kIExpScaleDerivationOutOfDomain;
-			else if (!softmax_width_in_domain(sc.c.q_b, sc.c.q_c, (uint64_t)pos + 1, &sc.peak)) st = kSoftmaxRowWidthOutOfDomain;
-			else if (sc.c.q_ln2 < 1) st = kSoftmaxKernelRefused;      // (q_ln2 <= q_b always holds: see k_qkv_post)
-		}
-		b.smc[(size_t)r * d.kv_heads + h] = sc;
-	}
-	// the first kv head (in head order) that failed decides the status
-	const uint32_t failed = __ballot_sync(0xffffffffu, st != kOk);
-	if (failed != 0u) {
-		const int first = __ffs((int)failed) - 1;
-		const int32_t fst = __shfl_sync(0xffffffffu, st, first);
-		if (lane == 0) atomicCAS(&b.status[r], 0, pack_status(fst, kSiteSoftmaxConsts, b.layer));
-	}
-}
-
-static bool warp_rows_ok(const RowBatch& b, const Dims& d) {
-	static const bool off = [] {
-		const char* e = getenv("SSLM_B200_WARP_ROWS");
-		return e && e[0] == '0';
-	}();
-	return !off && !b.wide64 && d.hidden % 128 == 0 && d.hidden <= 128 * kWarpRowGroups && (b.wide_ld & 3) == 0;
-}
-
 // The activation row is the longest a row kernel walks (intermediate width, three codes per
 // element), and its passes are bound by instruction issue: the row's coders are checked once
 // and the passes below are compiled for the 32-bit coder and for the general one.
@@ -1319,50 +970,20 @@ void launch_begin(const RowBatch& b, const Dims& d, const int8_t* embed, Scale c
 void launch_rmsnorm(const RowBatch& b, const Dims& d, const int8_t* gain, Scale site, cudaStream_t st) {
 	launch_pdl(k_rmsnorm, dim3(b.m), dim3(kRowThreads), smem_wide(d), st, b, d, gain, site);
 }
-void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev& h, int layer_index,
+void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, int layer_index,
                      KvPoolDev pool, const int32_t* cos, const int32_t* sin, cudaStream_t st) {
-	if (warp_rows_ok(b, d) && h.b_q == nullptr && h.b_k == nullptr && h.b_v == nullptr && d.kv_heads <= 32 &&
-	    d.head_dim % 4 == 0 && d.kv_hidden % 4 == 0 && (d.head_dim / 2) % 2 == 0) {
-		launch_pdl(k_qkv_post_w, dim3((b.m + kWarpRowsPerBlock - 1) / kWarpRowsPerBlock), dim3(kWarpRowsPerBlock * 32), 0, st, b, d, layer,
-		           h.c_q, layer_index, pool, cos, sin);
-		return;
-	}
 	const size_t sm = kRedBytes + 64 + (size_t)((d.hidden + d.kv_hidden + 15) & ~15) +
 	                  (size_t)(d.qkv_rows + d.head_dim) * 4;
 	launch_pdl(k_qkv_post, dim3(b.m), dim3(kRowThreads), sm, st, b, d, layer, layer_index, pool, cos, sin);
 }
-void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev& h, cudaStream_t st) {
-	if (warp_rows_ok(b, d)) {
-		launch_pdl(k_ctx_funnel_w, dim3((b.m + kWarpRowsPerBlock - 1) / kWarpRowsPerBlock), dim3(kWarpRowsPerBlock * 32), 0, st, b, d, h.c_ctx);
-		return;
-	}
+void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
 	launch_pdl(k_ctx_funnel, dim3(b.m), dim3(kRowThreads), kRedBytes + (size_t)d.hidden * 4, st, b, d, layer);
 }
-// (host copies of the layer constants: the warp-per-row kernels take them by value)
-void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev& h, cudaStream_t st) {
-	if (warp_rows_ok(b, d)) {
-		ResidualSite s{};
-		s.proj_in_scale = b.cs; s.c_proj = h.c_o; s.c_res = h.c_attn_res;
-		s.stream = b.x; s.stream_scale = b.xs; s.out = b.a; s.out_scale = b.as;
-		s.gain = h.g_mlp; s.c_norm = h.c_mlp_norm;
-		s.site_proj = kSiteO; s.site_res = kSiteAttnRes; s.norm_next_layer = 0;
-		launch_pdl(k_residual_w, dim3((b.m + kWarpRowsPerBlock - 1) / kWarpRowsPerBlock), dim3(kWarpRowsPerBlock * 32), 0, st, b, d, s);
-		return;
-	}
+void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
 	launch_pdl(k_res1, dim3(b.m), dim3(kRowThreads), res_smem_bytes(d), st, b, d, layer);
 }
-void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev& h, const LayerDev* next,
-                 const LayerDev* h_next, cudaStream_t st) {
-	if (warp_rows_ok(b, d)) {
-		ResidualSite s{};
-		s.proj_in_scale = b.acts; s.c_proj = h.c_down; s.c_res = h.c_mlp_res;
-		s.stream = b.a; s.stream_scale = b.as; s.out = b.x; s.out_scale = b.xs;
-		s.gain = h_next ? h_next->g_attn : nullptr;
-		s.c_norm = h_next ? h_next->c_attn_norm : Scale{0, 0};
-		s.site_proj = kSiteDown; s.site_res = kSiteMlpRes; s.norm_next_layer = 1;
-		launch_pdl(k_residual_w, dim3((b.m + kWarpRowsPerBlock - 1) / kWarpRowsPerBlock), dim3(kWarpRowsPerBlock * 32), 0, st, b, d, s);
-		return;
-	}
+void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev* next,
+                 cudaStream_t st) {
 	launch_pdl(k_res2, dim3(b.m), dim3(kRowThreads), res_smem_bytes(d), st, b, d, layer, next);
 }
 size_t act_smem_bytes(const Dims& d) { return kRedBytes + 256 * 4 + (size_t)d.inter * 8; }
