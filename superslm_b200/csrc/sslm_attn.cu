@@ -905,7 +905,7 @@ struct AttnPlan {
 static std::atomic<int> g_forced_splits{-1};     // -1: not set yet (the environment decides), 0: automatic
 void attn_force_splits(int splits) { g_forced_splits.store(splits < 0 ? 0 : splits); }
 
-static AttnPlan attn_plan(const Dims& d, int m, int max_width) {
+static AttnPlan attn_plan(const Dims& d, int m, int max_width, bool one_sequence) {
 	AttnPlan p;
 	int forced = g_forced_splits.load();
 	if (forced < 0) {      // SSLM_B200_ATTN_SPLITS=n fixes the slices per kv head (tuning, tests)
@@ -932,6 +932,9 @@ static AttnPlan attn_plan(const Dims& d, int m, int max_width) {
 	// ... unless the width does not fit the slices: then up to 16 slices of one kv head per cluster
 	while (splits < 16 && pad64((max_width + splits - 1) / splits) > kAttnMaxSlice) splits *= 2;
 	p.whole_row = splits <= per_kv_max ? 1 : 0;
+	// The rows of a prefill chunk are many and of very different widths: blocks that wait for one
+	// another at cluster barriers cost more there than the separate funnel kernel does.
+	if (one_sequence && forced <= 0 && splits == 1) p.whole_row = 0;
 	p.splits = splits;
 	p.cp = pad64((max_width + splits - 1) / splits);
 	return p;
@@ -1004,7 +1007,7 @@ bool launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, i
 		if (err) *err = e;
 		return false;
 	}
-	const AttnPlan p = attn_plan(d, b.m, max_width);
+	const AttnPlan p = attn_plan(d, b.m, max_width, reverse_rows != 0);
 	cudaError_t e;
 	if (d.head_dim == 128) e = launch_attn<128>(b, d, layer, layer_index, pool, p, reverse_rows, st);
 	else if (d.head_dim == 64) e = launch_attn<64>(b, d, layer, layer_index, pool, p, reverse_rows, st);
