@@ -209,7 +209,7 @@ __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefe
 // (forward_sites.cpp:1898-1903): largest folded magnitude of the row -> codes and carried scale,
 // so that no separate funnel kernel runs. HD = head_dim (32, 64 or 128); threads = 2 * HD.
 template <int HD>
-__global__ void __launch_bounds__(2 * HD)
+__global__ void __launch_bounds__(2 * HD, HD == 128 ? 4 : 8)
 k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev pool, int cp, int splits, int whole_row,
             int reverse_rows) {
 	extern __shared__ __align__(16) unsigned char smem[];
@@ -263,6 +263,10 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	const SoftmaxConsts smc = b.smc[(size_t)r * d.kv_heads + kvh];   // wanted after the scores; asked for now
 	__syncthreads();
 	const bool live = s.x_flags[2] == 0u;
+	// A row that is one slice of one kv head has nobody to meet: the block keeps everything local
+	// (and may leave early).
+	const bool solo = splits == 1 && !whole_row;
+	if (solo && !live) return;
 
 	// ---- stage 1: scores, 8 positions per MMA group, groups dealt round-robin to the warps
 	if (live) {
@@ -329,23 +333,34 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		}
 	}
 	__syncthreads();
-	if (t < G) {
-		int m = redi[t * kAttnWarps];
-		for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[t * kAttnWarps + w]);
-		s.x_max[t] = m;
-	}
-	cluster_sync_all();      // ---- exchange 1: every slice's maxima are up
-	// (one thread per head fetches the peers' values; reading them from every thread would put
-	// thousands of remote loads on the cluster's shared-memory network)
-	if (t < G) {
-		int m = INT32_MIN;
-		for (int j = 0; j < splits; ++j) m = max(m, (int)peer_ld32(peer_addr(&s.x_max[t], kv_rank0 + (uint32_t)j)));
-		s.l_max[t] = m;
-	}
-	__syncthreads();
+	if (solo) {
 #pragma unroll
-	for (int h = 0; h < 8; ++h)
-		if (h < G) mx[h] = s.l_max[h];
+		for (int h = 0; h < 8; ++h) {
+			int m = redi[h * kAttnWarps];
+#pragma unroll
+			for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[h * kAttnWarps + w]);
+			mx[h] = m;
+		}
+		__syncthreads();
+	} else {
+		if (t < G) {
+			int m = redi[t * kAttnWarps];
+			for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[t * kAttnWarps + w]);
+			s.x_max[t] = m;
+		}
+		cluster_sync_all();      // ---- exchange 1: every slice's maxima are up
+		// (one thread per head fetches the peers' values; reading them from every thread would put
+		// thousands of remote loads on the cluster's shared-memory network)
+		if (t < G) {
+			int m = INT32_MIN;
+			for (int j = 0; j < splits; ++j) m = max(m, (int)peer_ld32(peer_addr(&s.x_max[t], kv_rank0 + (uint32_t)j)));
+			s.l_max[t] = m;
+		}
+		__syncthreads();
+#pragma unroll
+		for (int h = 0; h < 8; ++h)
+			if (h < G) mx[h] = s.l_max[h];
+	}
 
 	unsigned long long tot[8];
 #pragma unroll
@@ -388,33 +403,51 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		}
 	}
 	const int any_bad = __syncthreads_or(bad ? 1 : 0);
-	if (t < G) {
-		unsigned long long x = 0;
-		for (int w = 0; w < kAttnWarps; ++w) x += s.red[t * kAttnWarps + w];
-		s.x_sum[t] = x;
-	}
-	if (t == 0 && any_bad) s.x_flags[0] = 1u;
-	cluster_sync_all();      // ---- exchange 2: every slice's sums and refusal flags are up
-	// the reference refuses the whole row when any element of any head is out of bounds
-	// (SoftmaxKernelRefusedAfterGateAccepted): every block of the cluster learns it here
-	if (t < G) {
-		unsigned long long x = 0;
-		for (int j = 0; j < splits; ++j) x += peer_ld64(peer_addr(&s.x_sum[t], kv_rank0 + (uint32_t)j));
-		s.l_sum[t] = x;
-	} else if (t == 32) {
-		uint32_t any = 0;
-		for (uint32_t j = 0; j < cluster_blocks; ++j) any |= peer_ld32(peer_addr(&s.x_flags[0], j));
-		s.l_misc[0] = any;
-	}
-	__syncthreads();
-	const bool refused = s.l_misc[0] != 0u;
-	if (refused && my_rank == 0 && t == 0) atomicCAS(&b.status[r], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
+	bool refused;
 	float inv[8];
+	if (solo) {
+		refused = any_bad != 0;
+		if (refused) {
+			// the reference refuses the row (SoftmaxKernelRefusedAfterGateAccepted)
+			if (t == 0) atomicCAS(&b.status[r], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
+			return;
+		}
 #pragma unroll
-	for (int h = 0; h < 8; ++h) {
-		const unsigned long long x = h < G ? s.l_sum[h] : 0ull;
-		tot[h] = x > 1ull ? x : 1ull;
-		inv[h] = 32768.0f / (float)tot[h];
+		for (int h = 0; h < 8; ++h) {
+			unsigned long long x = 0;
+#pragma unroll
+			for (int w = 0; w < kAttnWarps; ++w) x += s.red[h * kAttnWarps + w];
+			tot[h] = x > 1ull ? x : 1ull;
+			inv[h] = 32768.0f / (float)tot[h];
+		}
+	} else {
+		if (t < G) {
+			unsigned long long x = 0;
+			for (int w = 0; w < kAttnWarps; ++w) x += s.red[t * kAttnWarps + w];
+			s.x_sum[t] = x;
+		}
+		if (t == 0 && any_bad) s.x_flags[0] = 1u;
+		cluster_sync_all();      // ---- exchange 2: every slice's sums and refusal flags are up
+		// the reference refuses the whole row when any element of any head is out of bounds
+		// (SoftmaxKernelRefusedAfterGateAccepted): every block of the cluster learns it here
+		if (t < G) {
+			unsigned long long x = 0;
+			for (int j = 0; j < splits; ++j) x += peer_ld64(peer_addr(&s.x_sum[t], kv_rank0 + (uint32_t)j));
+			s.l_sum[t] = x;
+		} else if (t == 32) {
+			uint32_t any = 0;
+			for (uint32_t j = 0; j < cluster_blocks; ++j) any |= peer_ld32(peer_addr(&s.x_flags[0], j));
+			s.l_misc[0] = any;
+		}
+		__syncthreads();
+		refused = s.l_misc[0] != 0u;
+		if (refused && my_rank == 0 && t == 0) atomicCAS(&b.status[r], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
+#pragma unroll
+		for (int h = 0; h < 8; ++h) {
+			const unsigned long long x = h < G ? s.l_sum[h] : 0ull;
+			tot[h] = x > 1ull ? x : 1ull;
+			inv[h] = 32768.0f / (float)tot[h];
+		}
 	}
 	const bool work = live && !refused;
 	// probabilities, zero beyond the slice up to the next multiple of 64 (stage 3 reads whole pages)
@@ -487,6 +520,29 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 				}
 			}
 		}
+	}
+	if (solo) {
+		// per-head context fold (forward_sites.cpp:1889-1896), store, row maximum for the funnel
+		uint32_t smax = 0;
+		if (g < G) {
+			const int head = kvh * G + g;
+			const int32_t fi = s.l_fold[3 * g], fm = s.l_fold[3 * g + 1], fs = s.l_fold[3 * g + 2];
+#pragma unroll
+			for (int i = 0; i < NDB; ++i) {
+				int2 o;
+				o.x = fold(accl[i][0] + 256 * acch[i][0], fi, fm, fs);
+				o.y = fold(accl[i][1] + 256 * acch[i][1], fi, fm, fs);
+				const int ch = (warp * NDB + i) * 8 + c * 2;
+				*(int2*)(b.ctxw + (size_t)r * d.hidden + (size_t)head * HD + ch) = o;
+				const uint32_t ax = o.x < 0 ? 0u - (uint32_t)o.x : (uint32_t)o.x;
+				const uint32_t ay = o.y < 0 ? 0u - (uint32_t)o.y : (uint32_t)o.y;
+				smax = max(smax, max(ax, ay));
+			}
+		}
+#pragma unroll
+		for (int o = 16; o > 0; o >>= 1) smax = max(smax, __shfl_xor_sync(0xffffffffu, smax, o));
+		if (lane == 0 && smax) atomicMax(&b.rowmax[(size_t)r * 4 + 3], (unsigned long long)smax);
+		return;
 	}
 	// the slice's share, [head][channel], for the block that reduces that channel
 	if (g < G) {
@@ -918,13 +974,14 @@ static AttnPlan attn_plan(const Dims& d, int m, int max_width, bool one_sequence
 	if (forced > 0) {
 		while (splits * 2 <= forced && splits * 2 <= 16) splits *= 2;
 	} else {
-		// A block's time is mostly a fixed chain of dependent steps, so cutting rows into slices
-		// pays only while the extra blocks still run side by side: with many rows (a decode batch
-		// of hundreds of sequences, a prefill chunk) a row is one slice; with few rows the width is
-		// cut until the blocks fill the machine once.
+		// A block's time is mostly a fixed chain of dependent steps, and blocks of a cluster wait
+		// for one another at every exchange, so cutting rows into slices pays only when the rows
+		// are so few that most multiprocessors would otherwise idle (a single long sequence): then
+		// the width is cut until the blocks fill a fifth of the machine. Otherwise a row is one
+		// slice per kv head, unclustered, and the funnel kernel follows.
 		const int blocks = m * d.kv_heads;
 		int want = 1;
-		while (want < 8 && blocks * want * 2 <= 4 * sm_count()) want *= 2;
+		while (want < 8 && blocks * want * 2 <= sm_count() / 5) want *= 2;
 		while (splits * 2 <= want && splits * 2 <= 8) splits *= 2;
 		if (splits > per_kv_max) splits = per_kv_max;              // prefer the fused funnel ...
 	}
@@ -934,7 +991,7 @@ static AttnPlan attn_plan(const Dims& d, int m, int max_width, bool one_sequence
 	p.whole_row = splits <= per_kv_max ? 1 : 0;
 	// The rows of a prefill chunk are many and of very different widths: blocks that wait for one
 	// another at cluster barriers cost more there than the separate funnel kernel does.
-	if (one_sequence && forced <= 0 && splits == 1) p.whole_row = 0;
+	if (forced <= 0 && splits == 1) p.whole_row = 0;
 	p.splits = splits;
 	p.cp = pad64((max_width + splits - 1) / splits);
 	return p;
