@@ -72,6 +72,7 @@ def parse_args():
     ap.add_argument("--no-sweep", action="store_true", help="skip the standalone linear-layer grid")
     ap.add_argument("--no-single", action="store_true", help="skip the single-sequence measurement")
     ap.add_argument("--only-sweep", action="store_true", help="just the standalone linear-layer grid (no model)")
+    ap.add_argument("--sweep-cell", default="", help="K,N,M: restrict the grid to one cell (for profiler captures)")
     return ap.parse_args()
 
 
@@ -344,7 +345,7 @@ def measured_peaks():
     return 6650.0, 2.0 * 1590.0, "fallback"
 
 
-def linear_sweep(d, art_sh):
+def linear_sweep(d, art_sh, only_cell=None):
     """The standalone linear layer (projection + fold + per-row funnel) on operands resident in
     HBM, every (K x N) x M cell: device time per launch from CUDA events over a chain of launches
     that rotates through enough weight copies to defeat the L2. Cells with M <= 16 run the
@@ -362,6 +363,8 @@ def linear_sweep(d, art_sh):
     rng = np.random.default_rng(7)
     for K, N in SWEEP_KN:
         for M in SWEEP_M:
+            if only_cell is not None and (K, N, M) != only_cell:
+                continue
             use_tc = 1 if M > 8 else 0
             iters = 200 if M <= 16 else (40 if M <= 512 else 10)
             if N > 100000:
@@ -736,7 +739,8 @@ def run_only_sweep(args):
     from superslm_b200 import build as B
     lib = abi.SslmLib(B.LIB if os.path.exists(B.LIB) else B.build())
     d = bind_extras(lib)
-    print(json.dumps({"linear_sweep": linear_sweep(d, A.SHAPES[args.shape])}))
+    cell = tuple(int(v) for v in args.sweep_cell.split(",")) if args.sweep_cell else None
+    print(json.dumps({"linear_sweep": linear_sweep(d, A.SHAPES[args.shape], cell)}))
 
 
 if __name__ == "__main__":

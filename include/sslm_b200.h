@@ -251,6 +251,20 @@ SSLM_API sslm_status sslm_b200_tc_variant_counts(uint64_t* counts, int32_t n);
  * Results do not depend on it. For tuning and for tests that walk every cut. */
 SSLM_API sslm_status sslm_b200_set_attention_splits(int32_t splits);
 
+/* Tests only: the device integer library's primitives evaluated ON THE DEVICE over n operand
+ * tuples (host arrays a, b, c, e; three host result arrays), so that their device-only halves
+ * (reciprocal / root estimates, 32-bit short forms) are held to the CPU oracle as well. `which`:
+ *   0 DynamicScaleReciprocal(a)            1 ISqrt(a)            2 floor((a << 32) / b), |a| <= 127
+ *   3 RequantTokenCodeWide(x = a, R = b, s = c): out0 the code, out1 / out2 the per-row coders' code
+ *   4 LandingRescale(code a, m b, R c, e_a = e >> 32, e_t = low half of e): out0 value, out1 flags
+ *   5 a / b (unsigned, small quotient)     6 the funnel's scalars for a one-element row of magnitude a,
+ *     incoming scale (b, c), site constant (e >> 32, low half of e): out0/out1 the output scale, out2 status
+ *   7 one i-exp softmax element: shifted score a, constants (q_ln2 b, q_b c, q_c e >> 32), peak = low
+ *     half of e << 16: out0 value, out1 refused, out2 the value rebuilt from its (shift, remainder)
+ *   8 Q15 probability floor((a << 15) / b). */
+SSLM_API sslm_status sslm_b200_int_sweep(int32_t which, const int64_t* a, const int64_t* b, const int64_t* c,
+                                const int64_t* e, int64_t n, int64_t* out0, int64_t* out1, int64_t* out2);
+
 /* The vocabulary head on host buffers: logits[m, n] = sum_k x[m,k] w[n,k] (int32, no fold), and per
  * row the greedy token = the lowest index of the row's maximum (LogitsSite + NarrowRowChecked +
  * ArgmaxLowestIndexTieBreak, src/forward/forward_sites.cpp:2412-2437). out_logits ([M,N], may be

@@ -100,6 +100,7 @@ def port():
             "osc_rope_pair": (None, [i32, i32, i32, i32, C.POINTER(i64), C.POINTER(i64)]),
             "osc_fold": (i64, [i64, i32, i32, i32]), "osc_amp_fold": (i64, [i64, i32, i32, i32]),
             "osc_fold_matrix": (None, [p, C.c_size_t, C.c_size_t, p, p]),
+            "osc_sweep": (None, [C.c_int, p, p, p, p, i64, p, p, p]),
             "osc_combine": (Scale, [Scale, Scale]),
             "osc_landing_rescale": (i64, [i64, i64, i64, i64, i64, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
             "osc_silu_sigmoid_q15": (i32, [p, C.c_int8, i64, C.c_int]),

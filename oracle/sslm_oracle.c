@@ -695,3 +695,48 @@ int osc_logits_argmax(const osc_model* m, const osc_seq* s, int32_t* out_logits,
 	*out_token = best_i;
 	return OSC_OK;
 }
+
+
+/* The primitives over arrays of operands, one call per sweep: the CPU side of the device
+ * primitive sweep (tests/test_gpu_int_sweep.py). Operand meaning per `which` is documented at
+ * sslm_b200_int_sweep in include/sslm_b200.h; every case forwards to the function above that
+ * restates the reference primitive. */
+void osc_sweep(int which, const int64_t* a, const int64_t* b, const int64_t* c, const int64_t* e, int64_t n,
+               int64_t* out0, int64_t* out1, int64_t* out2) {
+	for (int64_t i = 0; i < n; ++i) {
+		out0[i] = out1[i] = out2[i] = 0;
+		switch (which) {
+		case 0: out0[i] = osc_dyn_recip(a[i]); break;
+		case 1: out0[i] = osc_isqrt(a[i]); break;
+		case 2: out0[i] = osc_floor_div((int64_t)((uint64_t)a[i] << 32), b[i]); break;
+		case 3: out0[i] = osc_requant_code_wide(a[i], b[i], (int)c[i]); break;
+		case 4: {
+			uint64_t sat = 0;
+			int ex = 0;
+			out0[i] = osc_landing_rescale(a[i], b[i], c[i], e[i] >> 32, (int64_t)(int32_t)(uint32_t)e[i], &sat, &ex);
+			out1[i] = (int64_t)sat | ((int64_t)ex << 1);
+			break;
+		}
+		case 5: out0[i] = (int64_t)((uint64_t)a[i] / (uint64_t)b[i]); break;
+		case 6: {      /* the scalar half of the funnel on a one-element row of magnitude a */
+			osc_scale inc = {b[i], c[i]}, site = {e[i] >> 32, (int64_t)(int32_t)(uint32_t)e[i]}, out = {0, 0};
+			int64_t row = a[i];
+			int8_t code = 0;
+			out2[i] = osc_funnel(&row, 1, &inc, 1, site, &code, &out);
+			out0[i] = out.m;
+			out1[i] = out.e;
+			break;
+		}
+		case 7: {      /* one softmax element: value and whether the row would be refused (peak = e) */
+			int64_t v = 0;
+			const int st = osc_iexp(-a[i], b[i], c[i], e[i] >> 32, 0, 0, &v);
+			const int64_t peak = (int64_t)(uint32_t)e[i] | 0;      /* unused here: the caller derives the bound */
+			(void)peak;
+			out0[i] = v;
+			out1[i] = st;
+			break;
+		}
+		default: break;
+		}
+	}
+}

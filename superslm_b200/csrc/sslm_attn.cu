@@ -1056,7 +1056,10 @@ bool launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, i
 		const char* e = getenv("SSLM_B200_ATTN_TILE");
 		return e && e[0] == '0';
 	}();
-	if (reverse_rows && b.m >= 4 && !tile_off) {
+	// ... once their prefix is long: up to about a thousand positions the per-row kernel, with
+	// thousands of independent blocks, is as fast or faster; beyond that re-reading the prefix per
+	// token costs more than the tiled kernel's lower parallelism (measured on the 0.5B / 1.5B / 3B widths).
+	if (reverse_rows && b.m >= 4 && max_width >= 1536 && !tile_off) {
 		cudaError_t e;
 		if (d.head_dim == 128) e = launch_attn_tile<128>(b, d, layer, layer_index, pool, st);
 		else if (d.head_dim == 64) e = launch_attn_tile<64>(b, d, layer, layer_index, pool, st);
@@ -1071,6 +1074,70 @@ bool launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, i
 	else e = launch_attn<32>(b, d, layer, layer_index, pool, p, reverse_rows, st);
 	if (err) *err = e;
 	return p.whole_row != 0;
+}
+
+// ------------------------------------------------------------ primitive sweep (tests)
+// The integer primitives of the device library evaluated on arrays of operands ON THE DEVICE, so
+// that their device-only halves (rcp.approx / rsqrt.approx estimates, 32-bit short forms) are
+// compared with the CPU oracle too. Operand meaning per `which`: see sslm_b200_int_sweep.
+__global__ void k_int_sweep(int which, const int64_t* a, const int64_t* b, const int64_t* c, const int64_t* e, long long n,
+                            int64_t* out0, int64_t* out1, int64_t* out2) {
+	for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+		int64_t o0 = 0, o1 = 0, o2 = 0;
+		switch (which) {
+		case 0: o0 = dyn_recip(a[i]); break;
+		case 1: o0 = isqrt64(a[i]); break;
+		case 2: o0 = floor_div_h32((int)a[i], b[i], rcp_estimate((double)b[i])); break;
+		case 3: {
+			o0 = requant_code(a[i], b[i], (int)c[i]);
+			const Coder cd = make_coder(b[i], (int)c[i]);       // the per-row coder the kernels use must agree
+			o1 = code_of(a[i], cd);
+			o2 = fits_i32(a[i]) ? code_of((int32_t)a[i], cd) : o1;
+			break;
+		}
+		case 4: {
+			bool sat = false, ex = false;
+			o0 = landing_rescale(a[i], b[i], c[i], e[i] >> 32, (int64_t)(int32_t)(uint32_t)e[i], &sat, &ex);
+			o1 = (sat ? 1 : 0) | (ex ? 2 : 0);
+			break;
+		}
+		case 5: o0 = (int64_t)udiv_small_quotient((uint64_t)a[i], (uint64_t)b[i], rcp_estimate((double)b[i])); break;
+		case 6: {
+			const Scale inc{b[i], c[i]}, site{e[i] >> 32, (int64_t)(int32_t)(uint32_t)e[i]};
+			const FunnelParams fp = funnel_params((uint64_t)a[i], &inc, 1, site);
+			o0 = fp.out.m;
+			o1 = fp.out.e;
+			o2 = fp.status;
+			break;
+		}
+		case 7: {      // one softmax element on the attention kernels' 32-bit form; peak in the low half of e
+			SoftmaxConsts k;
+			k.c = IExpConsts{b[i], c[i], e[i] >> 32};
+			k.peak = (int64_t)(uint32_t)e[i] << 16;
+			const IExpFast f = iexp_fast_prepare(k);
+			int64_t v = 0;
+			uint32_t parts = 0;
+			const bool ok = iexp_fast((uint32_t)a[i], f, &v, &parts);
+			o0 = v;
+			o1 = ok ? 0 : 1;
+			o2 = iexp_from_parts(parts, f);
+			break;
+		}
+		case 8: {      // Q15 probability: floor((e << 15) / total), 0 <= e <= total
+			const unsigned long long tot = (unsigned long long)b[i];
+			o0 = prob_q15(a[i], tot, 32768.0f / (float)tot);
+			break;
+		}
+		default: break;
+		}
+		out0[i] = o0;
+		out1[i] = o1;
+		out2[i] = o2;
+	}
+}
+void launch_int_sweep(int which, const int64_t* a, const int64_t* b, const int64_t* c, const int64_t* e, long long n, int64_t* out0,
+                      int64_t* out1, int64_t* out2, cudaStream_t st) {
+	k_int_sweep<<<592, 256, 0, st>>>(which, a, b, c, e, n, out0, out1, out2);
 }
 
 // ------------------------------------------------------------ canonical KV export

@@ -162,6 +162,9 @@ bool launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, i
 // [layer][K|V][kv_head][position][head_dim]; positions beyond `valid(layer)` are zero
 void launch_kv_export(const Dims& d, KvPoolDev pool, const int32_t* pages, int context_length,
                       int layer_index, int8_t* out, cudaStream_t st);
+// tests: the device integer primitives over arrays of operands (device pointers)
+void launch_int_sweep(int which, const int64_t* a, const int64_t* b, const int64_t* c, const int64_t* e, long long n, int64_t* out0,
+                      int64_t* out1, int64_t* out2, cudaStream_t st);
 // copy page src_page to dst_page in every (layer, kv head, K|V) plane
 void launch_page_copy(const Dims& d, KvPoolDev pool, int src_page, int dst_page, cudaStream_t st);
 // the inverse: scatter a canonical block into the sequence's pages (valid positions only)
