@@ -31,13 +31,18 @@ namespace sslm {
 constexpr int kAttnMaxWarps = 8;
 
 // One softmax element for constants that passed the gates of k_qkv_post (1 <= q_ln2 <= q_b
-// < 2^24, q_c >= 0): the value iexp_element() computes, on 32-bit words. dq = max - score
-// (0 <= dq < 2^32). z = floor(x / q_ln2) comes from a float estimate repaired with the
-// exact remainder.
+// < 2^24, q_c >= 0, peak = q_b^2 + q_c within the width gate): the value iexp_element()
+// computes, on 32-bit words and without a branch. dq = max - score (0 <= dq < 2^32).
+// z = floor(x / q_ln2) comes from a float estimate (within 1) repaired with the exact remainder.
+//
+// The reference also refuses an element whose value leaves [0, peak] (SoftmaxRowQ15's per-element
+// bound, src/intmath.cpp:870-888). Under the gates above that cannot happen, so the kernels carry
+// no such test: 0 <= rem < q_ln2 <= q_b gives 1 <= base = q_b - rem <= q_b, hence
+// 0 <= (base^2 + q_c) >> z <= q_b^2 + q_c = peak (and peak >= 1 because q_b >= 1).
 struct IExpFast {
 	uint32_t ln2, clip;     // q_ln2, 30 * q_ln2
 	int32_t qb;
-	int64_t qc, peak;
+	int64_t qc;
 	float inv_ln2;
 };
 __device__ __forceinline__ IExpFast iexp_fast_prepare(const SoftmaxConsts& k) {
@@ -46,36 +51,43 @@ __device__ __forceinline__ IExpFast iexp_fast_prepare(const SoftmaxConsts& k) {
 	f.clip = 30u * f.ln2;
 	f.qb = (int32_t)k.c.q_b;
 	f.qc = k.c.q_c;
-	f.peak = k.peak;
 	f.inv_ln2 = 1.0f / (float)f.ln2;
 	return f;
 }
 // *parts = (z << 24) | rem with x = z * q_ln2 + rem (rem < q_ln2 < 2^24, z <= 30): the second
 // softmax pass rebuilds the element from it (iexp_from_parts) instead of dividing again.
-__device__ __forceinline__ bool iexp_fast(uint32_t dq, const IExpFast& f, int64_t* value, uint32_t* parts) {
-	const uint32_t x = dq < f.clip ? dq : f.clip;
-	int32_t z = (int32_t)((float)x * f.inv_ln2);
+constexpr uint32_t kPartsOfZero = 63u << 24;      // parts that rebuild to the value 0 (shift by 63)
+__device__ __forceinline__ int64_t iexp_fast(uint32_t dq, const IExpFast& f, uint32_t* parts) {
+	const uint32_t x = min(dq, f.clip);
+	int32_t z = __float2int_rz(__uint2float_rn(x) * f.inv_ln2);
 	int32_t rem = (int32_t)(x - (uint32_t)z * f.ln2);
-	if (rem < 0) { --z; rem += (int32_t)f.ln2; }
-	if (rem >= (int32_t)f.ln2) { ++z; rem -= (int32_t)f.ln2; }
+	const int32_t adj = rem < 0 ? -1 : (rem >= (int32_t)f.ln2 ? 1 : 0);
+	z += adj;
+	rem -= adj * (int32_t)f.ln2;
 	const int32_t base = f.qb - rem;
-	const int64_t v = ((int64_t)base * (int64_t)base + f.qc) >> z;
-	*value = v;
 	*parts = ((uint32_t)z << 24) | (uint32_t)rem;
-	return f.peak >= 1 && v >= 0 && v <= f.peak;
+	return ((int64_t)base * (int64_t)base + f.qc) >> z;
 }
 __device__ __forceinline__ int64_t iexp_from_parts(uint32_t parts, const IExpFast& f) {
 	const int32_t base = f.qb - (int32_t)(parts & 0xFFFFFFu);
 	return ((int64_t)base * (int64_t)base + f.qc) >> (parts >> 24);
 }
-// floor((e << 15) / tot) for 0 <= e <= tot, tot >= 1: float estimate (within 1), exact repair
+// floor((e << 15) / tot) for 0 <= e <= min(tot, 2^47), 1 <= tot < 2^63, rinv = 32768 / tot in
+// float: the float quotient is within 2^-6 of the true one, so its floor is off by at most one
+// either way, and one signed remainder settles it (|e * 2^15 - p * tot| < 2 * tot stays inside
+// 64 bits because e * 2^15 <= 2^62).
 __device__ __forceinline__ uint32_t prob_q15(int64_t e, unsigned long long tot, float rinv) {
 	const unsigned long long num = (unsigned long long)e << 15;
-	unsigned long long p = (unsigned long long)((float)e * rinv);
-	if (p > 32768ull) p = 32768ull;
-	while (p * tot > num) --p;
-	while (num - p * tot >= tot) ++p;
-	return (uint32_t)p;
+	uint32_t p = min(__float2uint_rz(__ll2float_rn(e) * rinv), 32768u);
+	const long long r = (long long)(num - (unsigned long long)p * tot);
+	p -= r < 0 ? 1u : 0u;
+	p += r >= (long long)tot ? 1u : 0u;
+	return p;
+}
+// bytes 0 (low plane) or 1 (high plane) of four probabilities, packed into one word
+__device__ __forceinline__ uint32_t pack_plane(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3, int byte) {
+	const uint32_t sel = byte ? 0x0051u : 0x0040u;
+	return __byte_perm(__byte_perm(p0, p1, sel), __byte_perm(p2, p3, sel), 0x5410u);
 }
 
 // D += A(16x32, row) * B(32x8, col); rows 8..15 of A are always zero here (a1 = a3 = 0)
@@ -238,8 +250,11 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	const int8_t* vplane = pool.base + kv_plane_offset(d, pool, layer_index, kvh, 1);
 	const int npages = (n + kPageTokens - 1) / kPageTokens;
 	{
+		// entries beyond the slice's last page, up to the 64-position group stage 3 reads, repeat
+		// that page: their probabilities are zero, so any readable V words will do
 		const int32_t* pages = b.rows[r].pages + p0 / kPageTokens;
-		for (int j = t; j < npages; j += kAttnThreads) s.pbase[j] = (int64_t)pages[j] * (kPageTokens * HD);
+		for (int j = t; j < (n64 >> 4); j += kAttnThreads)
+			s.pbase[j] = (int64_t)pages[min(j, npages - 1)] * (kPageTokens * HD);
 	}
 	const FunnelFold fold_ctx = funnel_prefold(nullptr, 0, layer->c_ctx);
 	if (t < 3 * G) s.l_fold[t] = layer->f_ctx[3 * kvh * G + t];      // (weights: ahead of the wait)
@@ -268,24 +283,21 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	const bool solo = splits == 1 && !whole_row;
 	if (solo && !live) return;
 
-	// ---- stage 1: scores, 8 positions per MMA group, groups dealt round-robin to the warps
+	// ---- stage 1: scores, 8 positions per MMA group, groups dealt round-robin to the warps.
+	// Lanes beyond the slice's end read its last position again (no predicated loads); their
+	// columns are stored as INT32_MIN, which the row maximum ignores.
 	if (live) {
 		constexpr int NW = HD / 16;
 		uint32_t qw[NW];
-#pragma unroll
-		for (int j = 0; j < NW; ++j) qw[j] = 0;
-		if (g < G) load_row_words<HD>(b.qrot + (size_t)r * d.hidden + (size_t)(kvh * G + g) * HD, c, qw);
+		load_row_words<HD>(b.qrot + (size_t)r * d.hidden + (size_t)(kvh * G + min(g, G - 1)) * HD, c, qw);
 		const int nblk = (n + 7) >> 3;
 		constexpr int U = 4;
 		for (int blk0 = warp * U; blk0 < nblk; blk0 += kAttnWarps * U) {
 			uint32_t kw[U][NW];
 #pragma unroll
 			for (int u = 0; u < U; ++u) {
-				const int pos = (blk0 + u) * 8 + g;
-#pragma unroll
-				for (int j = 0; j < NW; ++j) kw[u][j] = 0;
-				if (pos < n)
-					load_row_words<HD>(kplane + s.pbase[pos >> 4] + (pos & 15) * HD, c, kw[u]);
+				const int pos = min((blk0 + u) * 8 + g, n - 1);
+				load_row_words<HD>(kplane + s.pbase[pos >> 4] + (pos & 15) * HD, c, kw[u]);
 			}
 #pragma unroll
 			for (int u = 0; u < U; ++u) {
@@ -293,7 +305,8 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 #pragma unroll
 				for (int j = 0; j < NW / 2; ++j) mma_s8s8(acc, qw[2 * j], qw[2 * j + 1], kw[u][2 * j], kw[u][2 * j + 1]);
 				const int k = (blk0 + u) * 8 + c * 2;
-				if (g < G && blk0 + u < nblk) *(int2*)&s.sc[(size_t)g * cp + k] = make_int2(acc[0], acc[1]);
+				if (g < G && blk0 + u < nblk)
+					*(int2*)&s.sc[(size_t)g * cp + k] = make_int2(k < n ? acc[0] : INT32_MIN, k + 1 < n ? acc[1] : INT32_MIN);
 			}
 		}
 	}
@@ -304,50 +317,34 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		for (int ln = t; ln < npages * (kPageTokens * HD / 128); ln += kAttnThreads)
 			prefetch_l2(vplane + s.pbase[ln / (kPageTokens * HD / 128)] + (ln % (kPageTokens * HD / 128)) * 128);
 
-	// ---- stage 2: softmax. Each thread takes 4 consecutive positions of every head.
+	// ---- stage 2: softmax, one head after the other (the loop over heads is kept rolled: a small
+	// body that stays in the instruction cache beats eight unrolled copies); a thread takes 4
+	// consecutive positions per trip.
 	const IExpFast fx = iexp_fast_prepare(smc);
-	int mx[8];
-#pragma unroll
-	for (int h = 0; h < 8; ++h) mx[h] = INT32_MIN;
-	if (live) {
-		for (int k4 = t * 4; k4 < n; k4 += kAttnThreads * 4) {
-#pragma unroll
-			for (int h = 0; h < 8; ++h) {
-				if (h < G) {
-					const int4 v = *(const int4*)&s.sc[(size_t)h * cp + k4];
-					int m = v.x;
-					if (k4 + 1 < n) m = max(m, v.y);
-					if (k4 + 2 < n) m = max(m, v.z);
-					if (k4 + 3 < n) m = max(m, v.w);
-					mx[h] = max(mx[h], m);
-				}
+	int* redi = (int*)s.red;
+#pragma unroll 1
+	for (int h = 0; h < G; ++h) {
+		int m = INT32_MIN;
+		if (live) {
+			const int32_t* row = s.sc + (size_t)h * cp;
+			for (int k4 = t * 4; k4 < n; k4 += kAttnThreads * 4) {
+				const int4 v = *(const int4*)&row[k4];
+				m = max(m, max(max(v.x, v.y), max(v.z, v.w)));
 			}
 		}
-	}
-	int* redi = (int*)s.red;
-#pragma unroll
-	for (int h = 0; h < 8; ++h) {
-		if (h < G) {
-			mx[h] = __reduce_max_sync(0xffffffffu, mx[h]);
-			if (lane == 0) redi[h * kAttnWarps + warp] = mx[h];
-		}
+		m = __reduce_max_sync(0xffffffffu, m);
+		if (lane == 0) redi[h * kAttnWarps + warp] = m;
 	}
 	__syncthreads();
+	if (t < G) {
+		int m = redi[t * kAttnWarps];
+#pragma unroll
+		for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[t * kAttnWarps + w]);
+		(solo ? s.l_max : s.x_max)[t] = m;
+	}
 	if (solo) {
-#pragma unroll
-		for (int h = 0; h < 8; ++h) {
-			int m = redi[h * kAttnWarps];
-#pragma unroll
-			for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[h * kAttnWarps + w]);
-			mx[h] = m;
-		}
 		__syncthreads();
 	} else {
-		if (t < G) {
-			int m = redi[t * kAttnWarps];
-			for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[t * kAttnWarps + w]);
-			s.x_max[t] = m;
-		}
 		cluster_sync_all();      // ---- exchange 1: every slice's maxima are up
 		// (one thread per head fetches the peers' values; reading them from every thread would put
 		// thousands of remote loads on the cluster's shared-memory network)
@@ -357,127 +354,93 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 			s.l_max[t] = m;
 		}
 		__syncthreads();
-#pragma unroll
-		for (int h = 0; h < 8; ++h)
-			if (h < G) mx[h] = s.l_max[h];
 	}
 
-	unsigned long long tot[8];
-#pragma unroll
-	for (int h = 0; h < 8; ++h) tot[h] = 0;
-	bool bad = false;
-	if (live) {
-		for (int k4 = t * 4; k4 < n; k4 += kAttnThreads * 4) {
-#pragma unroll
-			for (int h = 0; h < 8; ++h) {
-				if (h < G) {
-					const int4 v = *(const int4*)&s.sc[(size_t)h * cp + k4];
-					const int sv[4] = {v.x, v.y, v.z, v.w};
-					uint32_t parts[4];
-#pragma unroll
-					for (int j = 0; j < 4; ++j) {
-						int64_t e;
-						const bool ok = iexp_fast((uint32_t)mx[h] - (uint32_t)sv[j], fx, &e, &parts[j]);
-						if (k4 + j < n) {
-							tot[h] += ok ? (unsigned long long)e : 0ull;
-							bad |= !ok;
-						}
-					}
-					// the score has done its work: its place now holds the element's (shift, remainder),
-					// which this same thread reads back in the probability pass
-					*(int4*)&s.sc[(size_t)h * cp + k4] = make_int4((int)parts[0], (int)parts[1], (int)parts[2], (int)parts[3]);
+	// exponentials and their sum; the score's place then holds the element's (shift, remainder),
+	// which the same thread reads back in the probability pass
+#pragma unroll 1
+	for (int h = 0; h < G; ++h) {
+		unsigned long long tot = 0;
+		if (live) {
+			int32_t* row = s.sc + (size_t)h * cp;
+			const uint32_t m = (uint32_t)s.l_max[h];
+			for (int k4 = t * 4; k4 < n; k4 += kAttnThreads * 4) {
+				const int4 v = *(const int4*)&row[k4];
+				uint32_t q0, q1, q2, q3;
+				const int64_t e0 = iexp_fast(m - (uint32_t)v.x, fx, &q0);
+				int64_t e1 = iexp_fast(m - (uint32_t)v.y, fx, &q1);
+				int64_t e2 = iexp_fast(m - (uint32_t)v.z, fx, &q2);
+				int64_t e3 = iexp_fast(m - (uint32_t)v.w, fx, &q3);
+				if (k4 + 3 >= n) {       // the row's last trip: positions beyond its end count for nothing
+					if (k4 + 1 >= n) { e1 = 0; q1 = kPartsOfZero; }
+					if (k4 + 2 >= n) { e2 = 0; q2 = kPartsOfZero; }
+					e3 = 0; q3 = kPartsOfZero;
 				}
+				tot += (unsigned long long)(e0 + e1) + (unsigned long long)(e2 + e3);
+				*(int4*)&row[k4] = make_int4((int)q0, (int)q1, (int)q2, (int)q3);
 			}
 		}
+		// a thread's partial is below 2^62; three 24-bit limbs (the top one 16 bits) add up
+		// across the warp without leaving 32 bits, one warp-reduce instruction each
+		const uint32_t l0 = __reduce_add_sync(0xffffffffu, (uint32_t)tot & 0xFFFFFFu);
+		const uint32_t l1 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot >> 24) & 0xFFFFFFu);
+		const uint32_t l2 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot >> 48));
+		if (lane == 0)
+			s.red[h * kAttnWarps + warp] = (unsigned long long)l0 + ((unsigned long long)l1 << 24) + ((unsigned long long)l2 << 48);
 	}
+	__syncthreads();
+	if (t < G) {
+		unsigned long long x = 0;
 #pragma unroll
-	for (int h = 0; h < 8; ++h) {
-		if (h < G) {
-			// a thread's partial is below 2^62; three 24-bit limbs (the top one 16 bits) add up
-			// across the warp without leaving 32 bits, one warp-reduce instruction each
-			const uint32_t l0 = __reduce_add_sync(0xffffffffu, (uint32_t)tot[h] & 0xFFFFFFu);
-			const uint32_t l1 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot[h] >> 24) & 0xFFFFFFu);
-			const uint32_t l2 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot[h] >> 48));
-			if (lane == 0)
-				s.red[h * kAttnWarps + warp] = (unsigned long long)l0 + ((unsigned long long)l1 << 24) + ((unsigned long long)l2 << 48);
-		}
+		for (int w = 0; w < kAttnWarps; ++w) x += s.red[t * kAttnWarps + w];
+		(solo ? s.l_sum : s.x_sum)[t] = x;
 	}
-	const int any_bad = __syncthreads_or(bad ? 1 : 0);
-	bool refused;
-	float inv[8];
 	if (solo) {
-		refused = any_bad != 0;
-		if (refused) {
-			// the reference refuses the row (SoftmaxKernelRefusedAfterGateAccepted)
-			if (t == 0) atomicCAS(&b.status[r], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
-			return;
-		}
-#pragma unroll
-		for (int h = 0; h < 8; ++h) {
-			unsigned long long x = 0;
-#pragma unroll
-			for (int w = 0; w < kAttnWarps; ++w) x += s.red[h * kAttnWarps + w];
-			tot[h] = x > 1ull ? x : 1ull;
-			inv[h] = 32768.0f / (float)tot[h];
-		}
+		__syncthreads();
 	} else {
-		if (t < G) {
-			unsigned long long x = 0;
-			for (int w = 0; w < kAttnWarps; ++w) x += s.red[t * kAttnWarps + w];
-			s.x_sum[t] = x;
-		}
-		if (t == 0 && any_bad) s.x_flags[0] = 1u;
-		cluster_sync_all();      // ---- exchange 2: every slice's sums and refusal flags are up
-		// the reference refuses the whole row when any element of any head is out of bounds
-		// (SoftmaxKernelRefusedAfterGateAccepted): every block of the cluster learns it here
+		cluster_sync_all();      // ---- exchange 2: every slice's sums are up
 		if (t < G) {
 			unsigned long long x = 0;
 			for (int j = 0; j < splits; ++j) x += peer_ld64(peer_addr(&s.x_sum[t], kv_rank0 + (uint32_t)j));
 			s.l_sum[t] = x;
-		} else if (t == 32) {
-			uint32_t any = 0;
-			for (uint32_t j = 0; j < cluster_blocks; ++j) any |= peer_ld32(peer_addr(&s.x_flags[0], j));
-			s.l_misc[0] = any;
 		}
 		__syncthreads();
-		refused = s.l_misc[0] != 0u;
-		if (refused && my_rank == 0 && t == 0) atomicCAS(&b.status[r], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
-#pragma unroll
-		for (int h = 0; h < 8; ++h) {
-			const unsigned long long x = h < G ? s.l_sum[h] : 0ull;
-			tot[h] = x > 1ull ? x : 1ull;
-			inv[h] = 32768.0f / (float)tot[h];
-		}
 	}
-	const bool work = live && !refused;
-	// probabilities, zero beyond the slice up to the next multiple of 64 (stage 3 reads whole pages)
+	const bool work = live;
+	// probabilities as two u8 planes, zero beyond the slice up to the next multiple of 64 (stage 3
+	// reads whole 64-position groups)
 	if (work) {
-		for (int k4 = t * 4; k4 < n64; k4 += kAttnThreads * 4) {
-#pragma unroll
-			for (int h = 0; h < 8; ++h) {
-				if (h < G) {
-					const int4 v = *(const int4*)&s.sc[(size_t)h * cp + k4];
-					const int sv[4] = {v.x, v.y, v.z, v.w};
-					uint32_t lo = 0, hi = 0;
-#pragma unroll
-					for (int j = 0; j < 4; ++j) {
-						if (k4 + j < n) {
-							const int64_t e = iexp_from_parts((uint32_t)sv[j], fx);
-							const uint32_t p = prob_q15(e, tot[h], inv[h]);
-							lo |= (p & 0xffu) << (8 * j);
-							hi |= (p >> 8) << (8 * j);
-						}
-					}
-					*(uint32_t*)&s.pl[(size_t)h * cp + k4] = lo;
-					*(uint32_t*)&s.ph[(size_t)h * cp + k4] = hi;
-				}
+		const int n4 = (n + 3) & ~3;
+#pragma unroll 1
+		for (int h = 0; h < G; ++h) {
+			const unsigned long long x = s.l_sum[h];
+			const unsigned long long tot = x > 1ull ? x : 1ull;
+			const float inv = 32768.0f / (float)tot;
+			const int32_t* row = s.sc + (size_t)h * cp;
+			uint8_t* pl = s.pl + (size_t)h * cp;
+			uint8_t* ph = s.ph + (size_t)h * cp;
+			for (int k4 = t * 4; k4 < n4; k4 += kAttnThreads * 4) {
+				const int4 v = *(const int4*)&row[k4];
+				const uint32_t p0 = prob_q15(iexp_from_parts((uint32_t)v.x, fx), tot, inv);
+				const uint32_t p1 = prob_q15(iexp_from_parts((uint32_t)v.y, fx), tot, inv);
+				const uint32_t p2 = prob_q15(iexp_from_parts((uint32_t)v.z, fx), tot, inv);
+				const uint32_t p3 = prob_q15(iexp_from_parts((uint32_t)v.w, fx), tot, inv);
+				*(uint32_t*)&pl[k4] = pack_plane(p0, p1, p2, p3, 0);
+				*(uint32_t*)&ph[k4] = pack_plane(p0, p1, p2, p3, 1);
+			}
+			for (int k4 = n4 + t * 4; k4 < n64; k4 += kAttnThreads * 4) {
+				*(uint32_t*)&pl[k4] = 0u;
+				*(uint32_t*)&ph[k4] = 0u;
 			}
 		}
 	}
 	__syncthreads();
 
 	// ---- stage 3: the slice's share of ctx = P V. Lane column c owns page 4*grp + c of each
-	// 64-position group; its 16-byte row of the transposed page feeds two MMAs (positions 0..7 and 8..15).
+	// 64-position group; its 16-byte row of the transposed page feeds two MMAs (positions 0..7 and
+	// 8..15). Nothing is predicated: the page table and the planes are padded to whole groups, and
+	// lanes of MMA rows beyond the group's heads read head 0's probabilities (their output rows are
+	// never stored).
 	constexpr int NDB = 2;            // 8-channel blocks per warp
 	int accl[NDB][4], acch[NDB][4];
 #pragma unroll
@@ -486,38 +449,24 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		for (int j = 0; j < 4; ++j) accl[i][j] = acch[i][j] = 0;
 	if (work) {
 		const int ngrp = n64 >> 6;
-		constexpr int UG = 2;
-		for (int grp0 = 0; grp0 < ngrp; grp0 += UG) {
-			int4 vv[UG][NDB];
-			int4 al[UG], ah[UG];
+		const uint8_t* pl = s.pl + (size_t)(g < G ? g : 0) * cp + c * kPageTokens;
+		const uint8_t* ph = s.ph + (size_t)(g < G ? g : 0) * cp + c * kPageTokens;
+		const int8_t* vch = vplane + (warp * NDB * 8 + g) * kPageTokens;
+#pragma unroll 2
+		for (int grp = 0; grp < ngrp; ++grp) {
+			const int64_t pb = s.pbase[grp * 4 + c];
+			const int4 al = *(const int4*)(pl + grp * 64);
+			const int4 ah = *(const int4*)(ph + grp * 64);
+			int4 vv[NDB];
 #pragma unroll
-			for (int u = 0; u < UG; ++u) {
-				const int page = (grp0 + u) * 4 + c;
-				const bool in = page * kPageTokens < n;
-				al[u] = ah[u] = make_int4(0, 0, 0, 0);
-				if (g < G && in) {
-					al[u] = *(const int4*)&s.pl[(size_t)g * cp + page * kPageTokens];
-					ah[u] = *(const int4*)&s.ph[(size_t)g * cp + page * kPageTokens];
-				}
+			for (int i = 0; i < NDB; ++i) vv[i] = *(const int4*)(vch + pb + i * 8 * kPageTokens);
 #pragma unroll
-				for (int i = 0; i < NDB; ++i) {
-					vv[u][i] = make_int4(0, 0, 0, 0);
-					if (in) {
-						const int ch = (warp * NDB + i) * 8 + g;
-						vv[u][i] = *(const int4*)(vplane + s.pbase[page] + ch * kPageTokens);
-					}
-				}
-			}
-#pragma unroll
-			for (int u = 0; u < UG; ++u) {
-#pragma unroll
-				for (int i = 0; i < NDB; ++i) {
-					const int4 v = vv[u][i];
-					mma_u8s8(accl[i], (uint32_t)al[u].x, (uint32_t)al[u].y, (uint32_t)v.x, (uint32_t)v.y);
-					mma_u8s8(accl[i], (uint32_t)al[u].z, (uint32_t)al[u].w, (uint32_t)v.z, (uint32_t)v.w);
-					mma_u8s8(acch[i], (uint32_t)ah[u].x, (uint32_t)ah[u].y, (uint32_t)v.x, (uint32_t)v.y);
-					mma_u8s8(acch[i], (uint32_t)ah[u].z, (uint32_t)ah[u].w, (uint32_t)v.z, (uint32_t)v.w);
-				}
+			for (int i = 0; i < NDB; ++i) {
+				const int4 v = vv[i];
+				mma_u8s8(accl[i], (uint32_t)al.x, (uint32_t)al.y, (uint32_t)v.x, (uint32_t)v.y);
+				mma_u8s8(accl[i], (uint32_t)al.z, (uint32_t)al.w, (uint32_t)v.z, (uint32_t)v.w);
+				mma_u8s8(acch[i], (uint32_t)ah.x, (uint32_t)ah.y, (uint32_t)v.x, (uint32_t)v.y);
+				mma_u8s8(acch[i], (uint32_t)ah.z, (uint32_t)ah.w, (uint32_t)v.z, (uint32_t)v.w);
 			}
 		}
 	}
@@ -656,7 +605,7 @@ struct TileSmem {
 	static constexpr size_t kV = (size_t)2 * kTileKeys * HD;
 	static constexpr size_t kP = (size_t)2 * kTileRows * kTilePStride;
 	static constexpr size_t kFx = (size_t)kTileRows * sizeof(IExpFast);
-	static constexpr size_t kMisc = (size_t)kTileRows * (4 + 4 + 2 * 4 + 2 * 8) + 8 * 3 * 4 + 64;
+	static constexpr size_t kMisc = (size_t)kTileRows * (4 + 2 * 4 + 2 * 8) + 8 * 3 * 4 + 64;
 	static constexpr size_t kBytes = kK + kV + kP + kFx + kMisc;
 };
 
@@ -675,8 +624,7 @@ k_attention_tile(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvP
 	unsigned long long* wsum = (unsigned long long*)(fxs + kTileRows);      // [2][64]
 	int32_t* wmax = (int32_t*)(wsum + 2 * kTileRows);                        // [2][64]
 	int32_t* tok_ok = wmax + 2 * kTileRows;                                  // [64] 1: the token takes part
-	int32_t* tok_bad = tok_ok + kTileRows;                                   // [64] an element of the token was refused
-	int32_t* l_fold = tok_bad + kTileRows;                                   // [8][3]
+	int32_t* l_fold = tok_ok + kTileRows;                                    // [8][3]
 
 	const int kvh = blockIdx.x;
 	const int tile = (int)gridDim.y - 1 - (int)blockIdx.y;      // the last (widest) tiles start first
@@ -705,7 +653,6 @@ k_attention_tile(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvP
 			fxs[t] = iexp_fast_prepare(b.smc[(size_t)(r0 + t) * d.kv_heads + kvh]);
 		}
 		tok_ok[t] = okv;
-		tok_bad[t] = 0;
 	}
 	__syncthreads();
 	const bool in_a = tok_a < nt && tok_ok[tok_a] != 0, in_b = tok_b < nt && tok_ok[tok_b] != 0;
@@ -807,9 +754,9 @@ k_attention_tile(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvP
 	mx_a = max(wmax[rho_a], wmax[kTileRows + rho_a]);
 	mx_b = max(wmax[rho_b], wmax[kTileRows + rho_b]);
 
-	// ---- walk 2: exponentials and row totals
+	// ---- walk 2: exponentials and row totals (elements beyond a row's causal limit are computed
+	// and dropped by a select: no branch in the element code)
 	unsigned long long sum_a = 0, sum_b = 0;
-	bool bad_a = false, bad_b = false;
 	walk(false, [&](int stage, int blk) {
 		int acc[4][4];
 		scores(stage, acc);
@@ -818,18 +765,11 @@ k_attention_tile(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvP
 			const int k0 = blk * kTileKeys + 32 * ph + 8 * j + 2 * c;
 #pragma unroll
 			for (int q = 0; q < 2; ++q) {
-				int64_t e;
 				uint32_t parts;
-				if (k0 + q <= lim_a) {
-					const bool ok = iexp_fast((uint32_t)mx_a - (uint32_t)acc[j][q], fa, &e, &parts);
-					sum_a += ok ? (unsigned long long)e : 0ull;
-					bad_a |= !ok;
-				}
-				if (k0 + q <= lim_b) {
-					const bool ok = iexp_fast((uint32_t)mx_b - (uint32_t)acc[j][2 + q], fb, &e, &parts);
-					sum_b += ok ? (unsigned long long)e : 0ull;
-					bad_b |= !ok;
-				}
+				const int64_t ea = iexp_fast((uint32_t)mx_a - (uint32_t)acc[j][q], fa, &parts);
+				const int64_t eb = iexp_fast((uint32_t)mx_b - (uint32_t)acc[j][2 + q], fb, &parts);
+				sum_a += k0 + q <= lim_a ? (unsigned long long)ea : 0ull;
+				sum_b += k0 + q <= lim_b ? (unsigned long long)eb : 0ull;
 			}
 		}
 	});
@@ -841,17 +781,12 @@ k_attention_tile(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvP
 		wsum[ph * kTileRows + rho_a] = sum_a;
 		wsum[ph * kTileRows + rho_b] = sum_b;
 	}
-	if (bad_a) tok_bad[tok_a] = 1;
-	if (bad_b) tok_bad[tok_b] = 1;
 	__syncthreads();
 	sum_a = wsum[rho_a] + wsum[kTileRows + rho_a];
 	sum_b = wsum[rho_b] + wsum[kTileRows + rho_b];
 	const unsigned long long tot_a = sum_a > 1ull ? sum_a : 1ull, tot_b = sum_b > 1ull ? sum_b : 1ull;
 	const float inv_a = 32768.0f / (float)tot_a, inv_b = 32768.0f / (float)tot_b;
-	// a token with a refused element is refused as a whole (SoftmaxKernelRefusedAfterGateAccepted)
-	const bool go_a = in_a && tok_bad[tok_a] == 0, go_b = in_b && tok_bad[tok_b] == 0;
-	if (t < nt && tok_bad[t] != 0)
-		atomicCAS(&b.status[r0 + t], 0, pack_status(kSoftmaxKernelRefused, kSiteSoftmax, b.layer));
+	const bool go_a = in_a, go_b = in_b;
 
 	// ---- walk 3: probabilities and P.V
 	int accl[NGW][4], acch[NGW][4];
@@ -869,17 +804,11 @@ k_attention_tile(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvP
 			uint32_t pa[2], pb[2];
 #pragma unroll
 			for (int q = 0; q < 2; ++q) {
-				int64_t e;
 				uint32_t parts;
-				pa[q] = pb[q] = 0;
-				if (go_a && k0 + q <= lim_a) {
-					iexp_fast((uint32_t)mx_a - (uint32_t)acc[j][q], fa, &e, &parts);
-					pa[q] = prob_q15(e, tot_a, inv_a);
-				}
-				if (go_b && k0 + q <= lim_b) {
-					iexp_fast((uint32_t)mx_b - (uint32_t)acc[j][2 + q], fb, &e, &parts);
-					pb[q] = prob_q15(e, tot_b, inv_b);
-				}
+				const uint32_t va = prob_q15(iexp_fast((uint32_t)mx_a - (uint32_t)acc[j][q], fa, &parts), tot_a, inv_a);
+				const uint32_t vb = prob_q15(iexp_fast((uint32_t)mx_b - (uint32_t)acc[j][2 + q], fb, &parts), tot_b, inv_b);
+				pa[q] = k0 + q <= lim_a ? va : 0u;
+				pb[q] = k0 + q <= lim_b ? vb : 0u;
 			}
 			*(uint16_t*)(Pl + (size_t)rho_a * kTilePStride + col) = (uint16_t)((pa[0] & 0xffu) | ((pa[1] & 0xffu) << 8));
 			*(uint16_t*)(Ph + (size_t)rho_a * kTilePStride + col) = (uint16_t)((pa[0] >> 8) | ((pa[1] >> 8) << 8));
@@ -1115,11 +1044,10 @@ __global__ void k_int_sweep(int which, const int64_t* a, const int64_t* b, const
 			k.c = IExpConsts{b[i], c[i], e[i] >> 32};
 			k.peak = (int64_t)(uint32_t)e[i] << 16;
 			const IExpFast f = iexp_fast_prepare(k);
-			int64_t v = 0;
 			uint32_t parts = 0;
-			const bool ok = iexp_fast((uint32_t)a[i], f, &v, &parts);
+			const int64_t v = iexp_fast((uint32_t)a[i], f, &parts);
 			o0 = v;
-			o1 = ok ? 0 : 1;
+			o1 = (v < 0 || v > k.peak) ? 1 : 0;       // the reference's per-element bound
 			o2 = iexp_from_parts(parts, f);
 			break;
 		}
