@@ -272,6 +272,8 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	if (t < 8) {
 		s.x_max[t] = INT32_MIN;
 		s.x_sum[t] = 0ull;
+		s.l_max[t] = INT32_MIN;
+		s.l_sum[t] = 0ull;
 	}
 	if (t == 8) s.x_flags[0] = 0u;
 	if (t == 9) s.x_flags[1] = 0u;
@@ -283,15 +285,18 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	const bool solo = splits == 1 && !whole_row;
 	if (solo && !live) return;
 
-	// ---- stage 1: scores, 8 positions per MMA group, groups dealt round-robin to the warps.
-	// Lanes beyond the slice's end read its last position again (no predicated loads); their
-	// columns are stored as INT32_MIN, which the row maximum ignores.
+	// ---- stage 1: scores, 8 positions per MMA group, groups dealt round-robin to the warps, and the
+	// slice's maximum per head on the way. Lanes beyond the slice's end read its last position again
+	// (no predicated loads); their columns are stored as INT32_MIN, which the maximum ignores.
+	int32_t* const s_max = solo ? s.l_max : s.x_max;
+	unsigned long long* const s_sum = solo ? s.l_sum : s.x_sum;
 	if (live) {
 		constexpr int NW = HD / 16;
 		uint32_t qw[NW];
 		load_row_words<HD>(b.qrot + (size_t)r * d.hidden + (size_t)(kvh * G + min(g, G - 1)) * HD, c, qw);
 		const int nblk = (n + 7) >> 3;
 		constexpr int U = 4;
+		int rmax = INT32_MIN;
 		for (int blk0 = warp * U; blk0 < nblk; blk0 += kAttnWarps * U) {
 			uint32_t kw[U][NW];
 #pragma unroll
@@ -305,10 +310,16 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 #pragma unroll
 				for (int j = 0; j < NW / 2; ++j) mma_s8s8(acc, qw[2 * j], qw[2 * j + 1], kw[u][2 * j], kw[u][2 * j + 1]);
 				const int k = (blk0 + u) * 8 + c * 2;
-				if (g < G && blk0 + u < nblk)
-					*(int2*)&s.sc[(size_t)g * cp + k] = make_int2(k < n ? acc[0] : INT32_MIN, k + 1 < n ? acc[1] : INT32_MIN);
+				if (g < G && blk0 + u < nblk) {
+					const int v0 = k < n ? acc[0] : INT32_MIN, v1 = k + 1 < n ? acc[1] : INT32_MIN;
+					*(int2*)&s.sc[(size_t)g * cp + k] = make_int2(v0, v1);
+					rmax = max(rmax, max(v0, v1));
+				}
 			}
 		}
+		rmax = max(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
+		rmax = max(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
+		if (c == 0 && g < G && rmax != INT32_MIN) atomicMax(&s_max[g], rmax);
 	}
 	__syncthreads();
 
@@ -317,34 +328,7 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		for (int ln = t; ln < npages * (kPageTokens * HD / 128); ln += kAttnThreads)
 			prefetch_l2(vplane + s.pbase[ln / (kPageTokens * HD / 128)] + (ln % (kPageTokens * HD / 128)) * 128);
 
-	// ---- stage 2: softmax, one head after the other (the loop over heads is kept rolled: a small
-	// body that stays in the instruction cache beats eight unrolled copies); a thread takes 4
-	// consecutive positions per trip.
-	const IExpFast fx = iexp_fast_prepare(smc);
-	int* redi = (int*)s.red;
-#pragma unroll 1
-	for (int h = 0; h < G; ++h) {
-		int m = INT32_MIN;
-		if (live) {
-			const int32_t* row = s.sc + (size_t)h * cp;
-			for (int k4 = t * 4; k4 < n; k4 += kAttnThreads * 4) {
-				const int4 v = *(const int4*)&row[k4];
-				m = max(m, max(max(v.x, v.y), max(v.z, v.w)));
-			}
-		}
-		m = __reduce_max_sync(0xffffffffu, m);
-		if (lane == 0) redi[h * kAttnWarps + warp] = m;
-	}
-	__syncthreads();
-	if (t < G) {
-		int m = redi[t * kAttnWarps];
-#pragma unroll
-		for (int w = 1; w < kAttnWarps; ++w) m = max(m, redi[t * kAttnWarps + w]);
-		(solo ? s.l_max : s.x_max)[t] = m;
-	}
-	if (solo) {
-		__syncthreads();
-	} else {
+	if (!solo) {
 		cluster_sync_all();      // ---- exchange 1: every slice's maxima are up
 		// (one thread per head fetches the peers' values; reading them from every thread would put
 		// thousands of remote loads on the cluster's shared-memory network)
@@ -356,44 +340,41 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		__syncthreads();
 	}
 
-	// exponentials and their sum; the score's place then holds the element's (shift, remainder),
-	// which the same thread reads back in the probability pass
+	// ---- stage 2: softmax. The work is dealt to the warps as (head, 128-position chunk) pairs, so
+	// that every warp is busy whatever the width; a lane takes 4 consecutive positions. First the
+	// exponentials and their sum per head; the score's place then holds the element's
+	// (shift, remainder), which the probability pass rebuilds it from.
+	const IExpFast fx = iexp_fast_prepare(smc);
+	const int nchunk = (n64 + 127) >> 7;
+	if (live) {
 #pragma unroll 1
-	for (int h = 0; h < G; ++h) {
-		unsigned long long tot = 0;
-		if (live) {
-			int32_t* row = s.sc + (size_t)h * cp;
-			const uint32_t m = (uint32_t)s.l_max[h];
-			for (int k4 = t * 4; k4 < n; k4 += kAttnThreads * 4) {
+		for (int pr = warp; pr < G * nchunk; pr += kAttnWarps) {
+			const int h = pr / nchunk, k4 = (pr - h * nchunk) * 128 + lane * 4;
+			unsigned long long tot = 0;
+			if (k4 < n) {
+				int32_t* row = s.sc + (size_t)h * cp;
+				const uint32_t m = (uint32_t)s.l_max[h];
 				const int4 v = *(const int4*)&row[k4];
 				uint32_t q0, q1, q2, q3;
 				const int64_t e0 = iexp_fast(m - (uint32_t)v.x, fx, &q0);
 				int64_t e1 = iexp_fast(m - (uint32_t)v.y, fx, &q1);
 				int64_t e2 = iexp_fast(m - (uint32_t)v.z, fx, &q2);
 				int64_t e3 = iexp_fast(m - (uint32_t)v.w, fx, &q3);
-				if (k4 + 3 >= n) {       // the row's last trip: positions beyond its end count for nothing
+				if (k4 + 3 >= n) {       // the row's last group: positions beyond its end count for nothing
 					if (k4 + 1 >= n) { e1 = 0; q1 = kPartsOfZero; }
 					if (k4 + 2 >= n) { e2 = 0; q2 = kPartsOfZero; }
 					e3 = 0; q3 = kPartsOfZero;
 				}
-				tot += (unsigned long long)(e0 + e1) + (unsigned long long)(e2 + e3);
+				tot = (unsigned long long)(e0 + e1) + (unsigned long long)(e2 + e3);
 				*(int4*)&row[k4] = make_int4((int)q0, (int)q1, (int)q2, (int)q3);
 			}
+			// a lane's partial is below 2^50; three 24-bit limbs add up across the warp without
+			// leaving 32 bits, one warp-reduce instruction each
+			const uint32_t l0 = __reduce_add_sync(0xffffffffu, (uint32_t)tot & 0xFFFFFFu);
+			const uint32_t l1 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot >> 24) & 0xFFFFFFu);
+			const uint32_t l2 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot >> 48));
+			if (lane == 0) atomicAdd(&s_sum[h], (unsigned long long)l0 + ((unsigned long long)l1 << 24) + ((unsigned long long)l2 << 48));
 		}
-		// a thread's partial is below 2^62; three 24-bit limbs (the top one 16 bits) add up
-		// across the warp without leaving 32 bits, one warp-reduce instruction each
-		const uint32_t l0 = __reduce_add_sync(0xffffffffu, (uint32_t)tot & 0xFFFFFFu);
-		const uint32_t l1 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot >> 24) & 0xFFFFFFu);
-		const uint32_t l2 = __reduce_add_sync(0xffffffffu, (uint32_t)(tot >> 48));
-		if (lane == 0)
-			s.red[h * kAttnWarps + warp] = (unsigned long long)l0 + ((unsigned long long)l1 << 24) + ((unsigned long long)l2 << 48);
-	}
-	__syncthreads();
-	if (t < G) {
-		unsigned long long x = 0;
-#pragma unroll
-		for (int w = 0; w < kAttnWarps; ++w) x += s.red[t * kAttnWarps + w];
-		(solo ? s.l_sum : s.x_sum)[t] = x;
 	}
 	if (solo) {
 		__syncthreads();
@@ -412,25 +393,22 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 	if (work) {
 		const int n4 = (n + 3) & ~3;
 #pragma unroll 1
-		for (int h = 0; h < G; ++h) {
-			const unsigned long long x = s.l_sum[h];
-			const unsigned long long tot = x > 1ull ? x : 1ull;
-			const float inv = 32768.0f / (float)tot;
-			const int32_t* row = s.sc + (size_t)h * cp;
-			uint8_t* pl = s.pl + (size_t)h * cp;
-			uint8_t* ph = s.ph + (size_t)h * cp;
-			for (int k4 = t * 4; k4 < n4; k4 += kAttnThreads * 4) {
-				const int4 v = *(const int4*)&row[k4];
+		for (int pr = warp; pr < G * nchunk; pr += kAttnWarps) {
+			const int h = pr / nchunk, k4 = (pr - h * nchunk) * 128 + lane * 4;
+			if (k4 < n4) {
+				const unsigned long long x = s.l_sum[h];
+				const unsigned long long tot = x > 1ull ? x : 1ull;
+				const float inv = 32768.0f / (float)tot;
+				const int4 v = *(const int4*)&s.sc[(size_t)h * cp + k4];
 				const uint32_t p0 = prob_q15(iexp_from_parts((uint32_t)v.x, fx), tot, inv);
 				const uint32_t p1 = prob_q15(iexp_from_parts((uint32_t)v.y, fx), tot, inv);
 				const uint32_t p2 = prob_q15(iexp_from_parts((uint32_t)v.z, fx), tot, inv);
 				const uint32_t p3 = prob_q15(iexp_from_parts((uint32_t)v.w, fx), tot, inv);
-				*(uint32_t*)&pl[k4] = pack_plane(p0, p1, p2, p3, 0);
-				*(uint32_t*)&ph[k4] = pack_plane(p0, p1, p2, p3, 1);
-			}
-			for (int k4 = n4 + t * 4; k4 < n64; k4 += kAttnThreads * 4) {
-				*(uint32_t*)&pl[k4] = 0u;
-				*(uint32_t*)&ph[k4] = 0u;
+				*(uint32_t*)&s.pl[(size_t)h * cp + k4] = pack_plane(p0, p1, p2, p3, 0);
+				*(uint32_t*)&s.ph[(size_t)h * cp + k4] = pack_plane(p0, p1, p2, p3, 1);
+			} else if (k4 < n64) {
+				*(uint32_t*)&s.pl[(size_t)h * cp + k4] = 0u;
+				*(uint32_t*)&s.ph[(size_t)h * cp + k4] = 0u;
 			}
 		}
 	}
@@ -452,14 +430,11 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 		const uint8_t* pl = s.pl + (size_t)(g < G ? g : 0) * cp + c * kPageTokens;
 		const uint8_t* ph = s.ph + (size_t)(g < G ? g : 0) * cp + c * kPageTokens;
 		const int8_t* vch = vplane + (warp * NDB * 8 + g) * kPageTokens;
-#pragma unroll 2
-		for (int grp = 0; grp < ngrp; ++grp) {
-			const int64_t pb = s.pbase[grp * 4 + c];
+		// UG groups' V words are requested before the first of them is used
+		constexpr int UG = 4;
+		auto group = [&](int grp, const int4 (&vv)[NDB]) {
 			const int4 al = *(const int4*)(pl + grp * 64);
 			const int4 ah = *(const int4*)(ph + grp * 64);
-			int4 vv[NDB];
-#pragma unroll
-			for (int i = 0; i < NDB; ++i) vv[i] = *(const int4*)(vch + pb + i * 8 * kPageTokens);
 #pragma unroll
 			for (int i = 0; i < NDB; ++i) {
 				const int4 v = vv[i];
@@ -468,6 +443,25 @@ k_attention(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDe
 				mma_u8s8(acch[i], (uint32_t)ah.x, (uint32_t)ah.y, (uint32_t)v.x, (uint32_t)v.y);
 				mma_u8s8(acch[i], (uint32_t)ah.z, (uint32_t)ah.w, (uint32_t)v.z, (uint32_t)v.w);
 			}
+		};
+		int grp0 = 0;
+		for (; grp0 + UG <= ngrp; grp0 += UG) {
+			int4 vv[UG][NDB];
+#pragma unroll
+			for (int u = 0; u < UG; ++u) {
+				const int64_t pb = s.pbase[(grp0 + u) * 4 + c];
+#pragma unroll
+				for (int i = 0; i < NDB; ++i) vv[u][i] = *(const int4*)(vch + pb + i * 8 * kPageTokens);
+			}
+#pragma unroll
+			for (int u = 0; u < UG; ++u) group(grp0 + u, vv[u]);
+		}
+		for (; grp0 < ngrp; ++grp0) {
+			int4 vv[NDB];
+			const int64_t pb = s.pbase[grp0 * 4 + c];
+#pragma unroll
+			for (int i = 0; i < NDB; ++i) vv[i] = *(const int4*)(vch + pb + i * 8 * kPageTokens);
+			group(grp0, vv);
 		}
 	}
 	if (solo) {
