@@ -982,7 +982,11 @@ bool launch_attention(const RowBatch& b, const Dims& d, const LayerDev* layer, i
 	// ... once their prefix is long: up to about a thousand positions the per-row kernel, with
 	// thousands of independent blocks, is as fast or faster; beyond that re-reading the prefix per
 	// token costs more than the tiled kernel's lower parallelism (measured on the 0.5B / 1.5B / 3B widths).
-	if (reverse_rows && b.m >= 4 && max_width >= 1536 && !tile_off) {
+	static const int tile_min = [] {
+		const char* e = getenv("SSLM_B200_ATTN_TILE_MIN");      // tuning: the width from which the tiled kernel runs
+		return e ? atoi(e) : 1536;
+	}();
+	if (reverse_rows && b.m >= 4 && max_width >= tile_min && !tile_off) {
 		cudaError_t e;
 		if (d.head_dim == 128) e = launch_attn_tile<128>(b, d, layer, layer_index, pool, st);
 		else if (d.head_dim == 64) e = launch_attn_tile<64>(b, d, layer, layer_index, pool, st);

