@@ -686,7 +686,7 @@ __device__ int32_t block_residual(const int8_t* branch_s, const int32_t* raw, co
 }
 
 // o-projection funnel -> attention residual -> MLP RMSNorm (forward_sites.cpp:1906-1937)
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, 1024 / kRowThreads)
 k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	Red red{(unsigned long long*)smem, 0};
@@ -746,7 +746,7 @@ k_res1(RowBatch b, Dims d, const LayerDev* layer) {
 
 // down-projection funnel -> MLP residual -> (next layer's attention RMSNorm)
 // (forward_sites.cpp:1968-1987, :1694-1698)
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, 1024 / kRowThreads)
 k_res2(RowBatch b, Dims d, const LayerDev* layer, const LayerDev* next_layer) {
 	extern __shared__ __align__(16) unsigned char smem[];
 	Red red{(unsigned long long*)smem, 0};
@@ -970,7 +970,11 @@ static int row_threads(int rows) {
 		const int v = e ? atoi(e) : 128;
 		return (v == 64 || v == 128 || v == 256) ? v : 128;
 	}();
-	return rows >= 512 ? big : kRowThreads;
+	static const int min_rows = [] {
+		const char* e = getenv("SSLM_B200_ROW_THREADS_MIN_ROWS");      // tuning: batch size from which `big` applies
+		return e ? atoi(e) : 512;
+	}();
+	return rows >= min_rows ? big : kRowThreads;
 }
 static size_t smem_wide(const Dims& d) { return kRedBytes + kLutBytes + (size_t)d.hidden * 8; }
 // reductions, the int64 staging row, four code rows and the staged int32 projection row
