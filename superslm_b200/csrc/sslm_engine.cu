@@ -393,6 +393,8 @@ size_t carve(const Dims& d, int rows, uint8_t* basep, RowBatch* b, size_t* wide_
 	b->status = (int32_t*)take(R * 4);
 	b->done = (int32_t*)take(R * 4);
 	b->sat = (unsigned long long*)take(R * 8);
+	b->sat_layer = (uint32_t*)take(R * d.layers * 4);
+	b->sat_ld = (int)d.layers;
 	b->lora_u = (int8_t*)take(R * 3 * kMaxLoraRank);
 	b->best = (unsigned long long*)take(R * 8);
 	*d_logits = (int32_t*)take((size_t)d.vocab * 4 * std::min<size_t>(R, 64));

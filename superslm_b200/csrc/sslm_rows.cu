@@ -267,6 +267,7 @@ k_begin(RowBatch b, Dims d, const int8_t* embed, Scale c_embed, const RowSource*
 		b.sat[r] = 0ull;
 		b.done[r] = 0;
 	}
+	for (int i = threadIdx.x; i < b.sat_ld; i += blockDim.x) b.sat_layer[(size_t)r * b.sat_ld + i] = 0u;
 	int32_t st = kOk;
 	int site = kSiteEmbed;
 	const RowSource s = src[r];
@@ -509,7 +510,10 @@ k_qkv_post(RowBatch b, Dims d, const LayerDev* layer, int layer_index, KvPoolDev
 			return;
 		}
 	}
-	if (threadIdx.x == 0) b.sat[r] += (unsigned long long)sat;
+	if (threadIdx.x == 0) {
+		b.sat[r] += (unsigned long long)sat;
+		if (layer_index < b.sat_ld) b.sat_layer[(size_t)r * b.sat_ld + layer_index] = (uint32_t)sat;
+	}
 
 	// RoPE: interleaved pairs (2i, 2i+1), table row = position
 	int8_t* qrot = b.qrot + (size_t)r * H;

@@ -118,6 +118,8 @@ struct RowBatch {
 	int32_t* done;               // [m] layers this call completed for the row
 	int layer;                   // index of the layer the current launch works on
 	unsigned long long* sat;     // [m] K/V landing saturation events of this call
+	uint32_t* sat_layer;         // [m][sat_ld] the same events per layer (a refused prefill chunk counts those the
+	int sat_ld;                  //             reference's walk had reached); sat_ld = layers
 	int8_t* lora_u;              // [m][3][kMaxLoraRank] clamped u = fold(A x) per projection slot of the current GEMM
 	unsigned long long* best;    // [m] packed (logit, index) argmax key
 	int32_t* logits;             // optional [m, vocab] dump, or nullptr

@@ -33,11 +33,19 @@ ARTIFACTS = {
     "q_site_exponent": ({"layer0.q_proj": ((1 << 31) - 1, 7)}, "q projection site at the constants' upper edge"),
     # fails only in the second layer: the first layer's K/V row was written and must not count
     "second_layer": ({"layer1.mlp_norm": (CANON, 7)}, "SiluScaleOutOfDomain in layer 1"),
+    # the same with q/k/v biases large enough to saturate the K/V landing: the reference has counted the
+    # landings its walk reached into kv_saturation_count when it refuses, and keeps them
+    "second_layer_saturating": ({"layer1.mlp_norm": (CANON, 7)}, "refused after saturating landings of two layers"),
+    # ... and a refusal inside the per-token stage of the first layer (only token 0's landing counts)
+    "khead_low_saturating": ({"layer0.softmax_khead0": (CANON, -80)}, "refused in the per-token stage after one landing"),
 }
+# artifacts built with a BIA1 section of this many bits (0: none)
+BIAS_BITS = {"second_layer_saturating": 33, "khead_low_saturating": 33}
 
 
 def build(name, shape="tiny", cap=48):
-    return A.build_synthetic_model(shape, SEED ^ (hash_name(name) & 0xFFFF), cap, const_overrides=ARTIFACTS[name][0])
+    return A.build_synthetic_model(shape, SEED ^ (hash_name(name) & 0xFFFF), cap, bias_bits=BIAS_BITS.get(name, 0),
+                                   const_overrides=ARTIFACTS[name][0])
 
 
 def hash_name(name):

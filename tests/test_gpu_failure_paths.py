@@ -36,8 +36,13 @@ def as_json(rec):
 def test_hostile_artifact_is_refused_like_the_reference(gpu_lib, golden, name):
     got = as_json(F.run_artifact_case(gpu_lib, name))
     assert got == golden[name]
-    # the refusal left nothing behind: every digest equals the fresh sequence's
-    assert len({r[-1] for r in got}) == 1
+    if name in F.BIAS_BITS:
+        # the landings the reference's walk had reached stay counted in kv_saturation_count (the only
+        # field a refused prefill moves): both refused calls changed the digest
+        assert len({r[-1] for r in got[:3]}) == 3
+    else:
+        # the refusal left nothing behind: every digest equals the fresh sequence's
+        assert len({r[-1] for r in got}) == 1
 
 
 def test_batch_in_which_one_sequence_is_refused(gpu_lib, golden):
