@@ -251,6 +251,14 @@ SSLM_API sslm_status sslm_b200_tc_variant_counts(uint64_t* counts, int32_t n);
  * Results do not depend on it. For tuning and for tests that walk every cut. */
 SSLM_API sslm_status sslm_b200_set_attention_splits(int32_t splits);
 
+/* Tests only: every wait of the kernels on an mbarrier is bounded, and this makes one run out on
+ * purpose. The next `launches` (0..16) launches of the tensor-core linear kernel arm the barrier of
+ * their first weight tile in block 0 without requesting the tile; the wait on it gives up after its
+ * poll limit (about a second), the rows of that tile end with an internal status, and the verb
+ * that launched the kernel returns SSLM_ALLOCATION_FAILED like any other refusal (a prefill chunk
+ * consumes nothing). Nothing faults and nothing spins without a limit; the next call works normally. */
+SSLM_API sslm_status sslm_b200_debug_withhold_tc_load(int32_t launches);
+
 /* Tests only: the device integer library's primitives evaluated ON THE DEVICE over n operand
  * tuples (host arrays a, b, c, e; three host result arrays), so that their device-only halves
  * (reciprocal / root estimates, 32-bit short forms) are held to the CPU oracle as well. `which`:

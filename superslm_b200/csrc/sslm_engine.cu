@@ -537,6 +537,12 @@ extern "C" sslm_status sslm_b200_tc_variant_counts(uint64_t* counts, int32_t n) 
 	return SSLM_OK;
 }
 
+extern "C" sslm_status sslm_b200_debug_withhold_tc_load(int32_t launches) {
+	if (launches < 0 || launches > 16) return SSLM_INVALID_ARGUMENT;
+	tc_debug_withhold(launches);
+	return SSLM_OK;
+}
+
 extern "C" sslm_status sslm_b200_set_attention_splits(int32_t splits) {
 	if (splits < 0 || splits > 16) return SSLM_INVALID_ARGUMENT;
 	attn_force_splits(splits);

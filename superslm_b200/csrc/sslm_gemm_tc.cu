@@ -287,7 +287,9 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 					const uint32_t sa = base + s * Cfg::kStageBytes;
 #pragma unroll
 					for (int mt = 0; mt < MT; ++mt) tma_load_2d(sa + mt * BM * BK, &map_a, full_bar(s), kb * BK, m0 + mt * BM);
-					tma_load_2d(sa + MT * BM * BK, &map_b, full_bar(s), kb * BK, n0);
+					// (tests of the bounded waits leave this one request out, once)
+					if (!(a.debug_withhold != 0 && blockIdx.x == 0 && it == 0))
+						tma_load_2d(sa + MT * BM * BK, &map_b, full_bar(s), kb * BK, n0);
 				}
 			}
 		}
@@ -303,7 +305,12 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 				for (int kb = kb0; kb < kb1; ++kb, ++it) {
 					const int s = (int)(it % S);
 					const uint32_t phase = (it / S) & 1u;
-					if (!mbar_wait(full_bar(s), phase)) { s_timeout = 1; break; }
+					if (!mbar_wait(full_bar(s), phase)) {
+						// the flag must be up before the commit below lets the epilogue look at this tile
+						s_timeout = 1;
+						__threadfence_block();
+						break;
+					}
 					asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 					const uint32_t sa = base + s * Cfg::kStageBytes;
 					const uint64_t db = umma_desc_sw128(sa + MT * BM * BK);
@@ -373,7 +380,9 @@ k_linear_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 				}
 				break;
 			}
-			const bool acc_ok = mbar_wait(accf_bar(as), (tc >> 1) & 1u);
+			// (the MMA thread commits a tile it gave up on as well, so that nobody waits out a second
+			// limit: the flag, raised before that commit, says the accumulators are not the tile's)
+			const bool acc_ok = mbar_wait(accf_bar(as), (tc >> 1) & 1u) && s_timeout == 0;
 			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 			if (!acc_ok) {
 				s_timeout = 1;
@@ -618,6 +627,8 @@ int pick_splits(const LinearArgs& a, int tiles) {
 	return s < 2 ? 1 : s;
 }
 
+std::atomic<int> g_debug_withhold{0};
+
 template <int MT, int BN>
 bool launch_cfg(const LinearArgs& a_in, cudaStream_t st) {
 	using Cfg = TcCfg<MT, BN>;
@@ -636,6 +647,12 @@ bool launch_cfg(const LinearArgs& a_in, cudaStream_t st) {
 	}
 	const int tiles = ((a.N + BN - 1) / BN) * ((a.M + MT * BM - 1) / (MT * BM));
 	a.splits = pick_splits<MT, BN>(a, tiles);
+	{
+		int left = g_debug_withhold.load();
+		a.debug_withhold = 0;
+		while (left > 0 && !g_debug_withhold.compare_exchange_weak(left, left - 1)) {}
+		if (left > 0) a.debug_withhold = 1;
+	}
 	const int items = tiles * a.splits;
 	const int grid = items < sm_count() ? items : sm_count();
 	if (launch_pdl(k_linear_tc<MT, BN>, dim3(grid), dim3(kTcThreads), Cfg::kSmemBytes, st, ma, mb, a) != cudaSuccess) {
@@ -660,6 +677,8 @@ static bool tc_refuse(int reason) {
 	g_tc_last_reason.store(reason);
 	return false;
 }
+
+void tc_debug_withhold(int launches) { g_debug_withhold.store(launches < 0 ? 0 : launches); }
 
 bool launch_linear_tc(const LinearArgs& a, cudaStream_t st) {
 	if (a.K % 16 != 0 || ((uintptr_t)a.x & 15) || ((uintptr_t)a.w & 15)) return tc_refuse(1);

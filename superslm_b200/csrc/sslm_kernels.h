@@ -134,12 +134,17 @@ struct LinearArgs {
 	unsigned int* tile_counters;
 	int n_tile_counters;
 	int splits;           // filled in by launch_linear_tc
+	int debug_withhold;   // tests only (tc_debug_withhold): block 0 never requests its first weight tile
 };
 // HBM-bound small-M path: bulk-copy weight streaming through a shared-memory ring, dp4a.
 cudaError_t launch_linear_gemv(const LinearArgs& a, cudaStream_t st);
 // tensor-core path for M > 8 rows (tcgen05 kind::i8, TMA-fed). Returns false when the
 // shape is not supported by that kernel (caller then uses the GEMV path).
 bool launch_linear_tc(const LinearArgs& a, cudaStream_t st);
+// Tests of the bounded waits: the next `launches` tensor-core launches arm their first weight-tile
+// barrier in block 0 without requesting the tile, so that the wait on it runs out (no fault, no
+// endless loop: the rows of that tile end with the internal wait-timeout status).
+void tc_debug_withhold(int launches);
 // process-wide counters of the tensor-core path: launches, refusals, reason of the last refusal
 void tc_stats(unsigned long long* launches, unsigned long long* refusals, int* last_reason);
 // launches per kernel variant (tile shape) of the tensor-core path
