@@ -605,6 +605,10 @@ def run_ours(args):
     barrier()
     wall_max, dev_max = rmax(wall), rmax(dev_s)
     produced_all = rsum(produced)
+    # host<->device bytes of one step inside sslm_decode_step, summed over the ranks: RowDesc + RowSource +
+    # RowSink per row and phase up, status + finished layers + saturation + argmax key per row and phase down
+    h2d_all = int(rsum(2 * n * (24 + 16 + 16)))
+    d2h_all = int(rsum(2 * n * 24))
 
     # ---- the same sequences in total dealt over the GPUs (strong scaling): every rank keeps 1/world of its own
     strong = None
@@ -683,7 +687,6 @@ def run_ours(args):
                "prefill_tok_s": round(r["prefill_tok_s"], 2)}
     if rank != 0:
         return
-    h2d = n * (24 + 16 + 16)     # RowDesc + RowSource + RowSink per row and phase
     cfg = workload_config(args, sh, n, world)
     out = {
         "metric": METRIC, "impl": "ours",
@@ -693,8 +696,8 @@ def run_ours(args):
         "config": cfg,
         "details": {"context_cap": cap, "prefill_chunk": args.chunk, "model_device_bytes": int(model_bytes)},
         "clocks": clocks,
-        "e2e": {"value": round(produced_all / wall_max, 1), "unit": "tok/s", "h2d_bytes_per_step": 2 * h2d,
-                "d2h_bytes_per_step": 2 * n * 24, "ms_per_step": round(wall_max * 1e3 / steps, 4)},
+        "e2e": {"value": round(produced_all / wall_max, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d_all,
+                "d2h_bytes_per_step": d2h_all, "ms_per_step": round(wall_max * 1e3 / steps, 4)},
         "gpu_launches": int(launches2 - launches1),
         "prefill": {"value": round(ptoks_all / prefill_dev, 1), "e2e": round(ptoks_all / prefill_wall, 1),
                     "unit": "tok/s", "tokens": int(ptoks_all), "gpu_launches": int(launches1 - launches0)},
