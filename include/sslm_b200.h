@@ -251,6 +251,16 @@ SSLM_API sslm_status sslm_b200_tc_variant_counts(uint64_t* counts, int32_t n);
  * Results do not depend on it. For tuning and for tests that walk every cut. */
 SSLM_API sslm_status sslm_b200_set_attention_splits(int32_t splits);
 
+/* Bisection aid (the counterpart of the reference's per-site trace hook,
+ * src/forward/checked_chain_funnel.cpp:338-361). With a buffer set, every later sslm_prefill /
+ * sslm_decode_step on this workspace appends one record per traced site, layer and row:
+ *   { int64 position; int32 layer; int32 site; int64 scale_m; int64 scale_e; int32 n; int32 row }
+ * followed by the site's n int8 codes, padded to a multiple of 8 bytes. Sites: 0 attn_norm,
+ * 2 rotated q (no scale), 3 attn_ctx, 5 attn_residual, 6 mlp_norm, 9 mlp_act, 11 mlp_residual.
+ * Records that do not fit are dropped. buf = NULL ends the trace; *used (optional) receives the
+ * bytes the trace held when this call was made. Slow (a copy per record); results are unchanged. */
+SSLM_API sslm_status sslm_b200_trace(sslm_workspace ws, void* buf, size_t capacity, size_t* used);
+
 /* Tests only: every wait of the kernels on an mbarrier is bounded, and this makes one run out on
  * purpose. The next `launches` (0..16) launches of the tensor-core linear kernel arm the barrier of
  * their first weight tile in block 0 without requesting the tile; the wait on it gives up after its

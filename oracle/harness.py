@@ -101,6 +101,7 @@ def port():
             "osc_fold": (i64, [i64, i32, i32, i32]), "osc_amp_fold": (i64, [i64, i32, i32, i32]),
             "osc_fold_matrix": (None, [p, C.c_size_t, C.c_size_t, p, p]),
             "osc_sweep": (None, [C.c_int, p, p, p, p, i64, p, p, p]),
+            "osc_trace_begin": (None, [p, C.c_size_t]), "osc_trace_end": (C.c_size_t, []),
             "osc_combine": (Scale, [Scale, Scale]),
             "osc_landing_rescale": (i64, [i64, i64, i64, i64, i64, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]),
             "osc_silu_sigmoid_q15": (i32, [p, C.c_int8, i64, C.c_int]),
@@ -321,3 +322,18 @@ class PortSeq:
             if tok >= 0:
                 out.append(tok)
         return out
+
+
+def parse_trace(buf) -> dict:
+    """Per-site trace records (osc_trace_begin / sslm_b200_trace write the same layout) as
+    {(position, layer, site): (m, e, codes bytes)}."""
+    import struct
+    raw = bytes(buf)
+    out, off = {}, 0
+    while off + 40 <= len(raw):
+        position, layer, site, m, e, n, row = struct.unpack_from("<qiiqqii", raw, off)
+        if n <= 0:
+            break
+        out[(position, layer, site)] = (m, e, raw[off + 40:off + 40 + n])
+        off += 40 + ((n + 7) & ~7)
+    return out

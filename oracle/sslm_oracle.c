@@ -531,6 +531,41 @@ static void rope_row(const osc_model* m, const int8_t* row, int64_t pos, int8_t*
 	}
 }
 
+/* Per-site trace for bisection (the counterpart of the reference's trace hook,
+ * src/forward/checked_chain_funnel.cpp:338-361): while a buffer is set, one_layer appends a
+ * record per site: { int64 position; int32 layer; int32 site; int64 m; int64 e; int32 n;
+ * int32 row (= -1 here) } followed by n codes, padded to a multiple of 8 bytes. Site numbers:
+ * 0 attn_norm, 2 rotated q (no scale), 3 attn_ctx, 5 attn_residual, 6 mlp_norm, 9 mlp_act,
+ * 11 mlp_residual -- the sites whose codes the CUDA path keeps in global memory. */
+static uint8_t* g_trace_buf = NULL;
+static size_t g_trace_cap = 0, g_trace_used = 0;
+void osc_trace_begin(uint8_t* buf, size_t capacity) {
+	g_trace_buf = buf;
+	g_trace_cap = capacity;
+	g_trace_used = 0;
+}
+size_t osc_trace_end(void) {
+	g_trace_buf = NULL;
+	return g_trace_used;
+}
+static void trace_emit(int64_t position, uint32_t layer, int site, const int8_t* codes, size_t n, osc_scale sc) {
+	if (g_trace_buf == NULL) return;
+	const size_t bytes = 40 + ((n + 7) & ~(size_t)7);
+	if (g_trace_used + bytes > g_trace_cap) return;
+	uint8_t* p = g_trace_buf + g_trace_used;
+	int32_t l32 = (int32_t)layer, s32 = site, n32 = (int32_t)n, row = -1;
+	memset(p, 0, bytes);
+	memcpy(p, &position, 8);
+	memcpy(p + 8, &l32, 4);
+	memcpy(p + 12, &s32, 4);
+	memcpy(p + 16, &sc.m, 8);
+	memcpy(p + 24, &sc.e, 8);
+	memcpy(p + 32, &n32, 4);
+	memcpy(p + 36, &row, 4);
+	memcpy(p + 40, codes, n);
+	g_trace_used += bytes;
+}
+
 /* One layer for one token at `position`: steps 1-13 of RunLayerLoopImpl's body
  * (forward_sites.cpp:1685-1987). hidden/hidden_scale are the layer input; the new
  * stream is written to out_hidden/out_scale. K/V of this position are landed in kv. */
@@ -552,6 +587,7 @@ static int one_layer(const osc_model* m, const osc_lora_layer* lora, uint32_t l,
 	osc_scale s_n, s_q, s_ctx, s_o, s_a, s_n2, s_g, s_u, s_act, s_d;
 
 	if ((st = osc_rmsnorm_site(hidden, lw->attn_gain, H, lw->c_attn_norm, normed, &s_n))) goto done;
+	trace_emit(position, l, 0, normed, H, s_n);
 	if ((st = project_funnel_bias(normed, s_n, lw->q_w, H, H, lw->q_fold, lw->c_q, lora ? &lora->q : NULL,
 	                              rank, lw->q_bias, q, &s_q))) goto done;
 	/* K/V projection + landing (LandTokenKVRow, forward_sites.cpp:1281-1418, legacy branch) */
@@ -585,6 +621,10 @@ static int one_layer(const osc_model* m, const osc_lora_layer* lora, uint32_t l,
 		rope_row(m, krow, position, tmp);
 		memcpy(krow, tmp, hd);
 	}
+	{
+		const osc_scale none = {0, 0};
+		trace_emit(position, l, 2, q_rot, H, none);
+	}
 	/* attention (forward_sites.cpp:1791-1905) */
 	for (size_t h = 0; h < heads; ++h) {
 		size_t kvhd = h / group;
@@ -614,18 +654,23 @@ static int one_layer(const osc_model* m, const osc_lora_layer* lora, uint32_t l,
 		}
 	}
 	if ((st = osc_funnel(ctx_wide, H, NULL, 0, lw->c_ctx, ctx, &s_ctx))) goto done;
+	trace_emit(position, l, 3, ctx, H, s_ctx);
 	if ((st = project_funnel(ctx, s_ctx, lw->o_w, H, H, lw->o_fold, lw->c_o, lora ? &lora->o : NULL,
 	                         rank, o, &s_o))) goto done;
 	if ((st = osc_residual_site(o, s_o, hidden, hidden_scale, H, lw->c_attn_res, attn_stream, &s_a))) goto done;
+	trace_emit(position, l, 5, attn_stream, H, s_a);
 	if ((st = osc_rmsnorm_site(attn_stream, lw->mlp_gain, H, lw->c_mlp_norm, normed, &s_n2))) goto done;
+	trace_emit(position, l, 6, normed, H, s_n2);
 	if ((st = project_funnel(normed, s_n2, lw->gate_w, H, I, lw->gate_fold, lw->c_gate,
 	                         lora ? &lora->gate : NULL, rank, gate, &s_g))) goto done;
 	if ((st = project_funnel(normed, s_n2, lw->up_w, H, I, lw->up_fold, lw->c_up,
 	                         lora ? &lora->up : NULL, rank, up, &s_u))) goto done;
 	if ((st = osc_mlp_act_site(gate, s_g, up, s_u, I, m->silu_table, lw->c_act, act, &s_act))) goto done;
+	trace_emit(position, l, 9, act, I, s_act);
 	if ((st = project_funnel(act, s_act, lw->down_w, I, H, lw->down_fold, lw->c_down,
 	                         lora ? &lora->down : NULL, rank, o, &s_d))) goto done;
 	st = osc_residual_site(o, s_d, attn_stream, s_a, H, lw->c_mlp_res, out_hidden, out_scale);
+	if (!st) trace_emit(position, l, 11, out_hidden, H, *out_scale);
 done:
 	free(buf);
 	free(wide);

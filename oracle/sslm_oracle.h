@@ -147,6 +147,10 @@ int osc_logits_argmax(const osc_model* m, const osc_seq* s, int32_t* out_logits,
 /* embed the token into the sequence's hidden state (src/sslm_abi.cpp:2231-2251) */
 int osc_embed_into_seq(const osc_model* m, osc_seq* s, int32_t token);
 
+/* per-site trace of one_layer into a caller buffer (record layout at the definition) */
+void osc_trace_begin(uint8_t* buf, size_t capacity);
+size_t osc_trace_end(void);
+
 /* the primitives over arrays of operands (see sslm_oracle.c) */
 void osc_sweep(int which, const int64_t* a, const int64_t* b, const int64_t* c, const int64_t* e, int64_t n,
                int64_t* out0, int64_t* out1, int64_t* out2);

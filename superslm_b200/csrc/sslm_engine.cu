@@ -537,6 +537,17 @@ extern "C" sslm_status sslm_b200_tc_variant_counts(uint64_t* counts, int32_t n) 
 	return SSLM_OK;
 }
 
+extern "C" sslm_status sslm_b200_trace(sslm_workspace ws, void* buf, size_t capacity, size_t* used) {
+	if (!ws) return SSLM_INVALID_ARGUMENT;
+	if (used) *used = ws->trace_used;          // what the trace that ends (or continues) here holds
+	if (!cuda_ok(cudaSetDevice(ws->device))) return SSLM_ALLOCATION_FAILED;
+	cudaStreamSynchronize(ws->stream);
+	ws->trace_buf = (uint8_t*)buf;
+	ws->trace_cap = buf ? capacity : 0;
+	ws->trace_used = 0;
+	return SSLM_OK;
+}
+
 extern "C" sslm_status sslm_b200_debug_withhold_tc_load(int32_t launches) {
 	if (launches < 0 || launches > 16) return SSLM_INVALID_ARGUMENT;
 	tc_debug_withhold(launches);

@@ -64,6 +64,10 @@ struct sslm_workspace_s {
 	float last_ms = 0.f;
 	uint64_t launches = 0;
 	bool launch_failed = false;   // a kernel launch of the current call was refused by the runtime
+	// optional per-site trace (sslm_b200_trace): host buffer that receives one record per traced
+	// site, layer and row of the calls that follow
+	uint8_t* trace_buf = nullptr;
+	size_t trace_cap = 0, trace_used = 0;
 	// optional per-kernel-class timing (sslm_b200_profile): an event before every launch
 	bool profile = false;
 	std::vector<cudaEvent_t> prof_events;
