@@ -73,6 +73,9 @@ def parse_args():
     ap.add_argument("--no-single", action="store_true", help="skip the single-sequence measurement")
     ap.add_argument("--only-sweep", action="store_true", help="just the standalone linear-layer grid (no model)")
     ap.add_argument("--sweep-cell", default="", help="K,N,M: restrict the grid to one cell (for profiler captures)")
+    ap.add_argument("--config-table", action="store_true",
+                    help="time the single-sequence configurations (0, 2 and 4 as tests/golden/config_cases.py states them): "
+                         "prefill and decode tok/s through the ABI; with --impl reference the CPU library on one host thread")
     return ap.parse_args()
 
 
@@ -738,6 +741,60 @@ def run_reference(args):
     }))
 
 
+def run_config_table(args):
+    """Prefill and decode tok/s of the single-sequence configurations, one sequence through the sslm_* verbs,
+    wall clock around the prefill calls and around the decode loop (the reference's own methodology,
+    tools/t2147_chunk_batched_pins.cpp:133-154). The cases are the parity cases of tests/golden/config_cases.py:
+    configuration 0 and 2 at their stated shape and lengths, configuration 4 at the 3B widths with 4 of its 36
+    layers and 16 decode tokens. --impl reference runs the compiled reference on ONE host thread."""
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    from config_cases import CASES, build_case_artifacts, case_prompt
+    if args.impl == "reference":
+        from oracle import harness as H      # (the CPU arm: the one place besides cpu_baseline that runs oracle/)
+        lib = H.ref()
+        if lib is None:
+            print(json.dumps({"config_table": None, "unavailable": "oracle/_ref is not built"}))
+            return
+        impl = {"impl": "reference", "cores": 1}
+    else:
+        from superslm_b200 import build as B
+        lib = abi.SslmLib(B.LIB if os.path.exists(B.LIB) else B.build())
+        d = bind_extras(lib)
+        if d.sslm_b200_set_device(int(os.environ.get("LOCAL_RANK", "0"))) != 0:
+            raise SystemExit("no usable CUDA device: the CUDA path is the only path")
+        impl = {"impl": "ours"}
+    rows = {}
+    for name in ("config0", "config2", "config4"):
+        case = CASES[name]
+        sh = A.SHAPES[case["shape"]]
+        art, adapters = build_case_artifacts(case)
+        prompt = case_prompt(case)
+        chunk = case["cpu_chunk"] if args.impl == "reference" else max(c for c, _ in case["gpu_splits"])
+        budget = 1 if name == "config4" else sh.layers
+        eng = abi.Engine(lib, art, blocks=2, max_batch=1, max_chunk=min(chunk, 2048))
+        try:
+            warm = eng.new_seq()                            # one discarded warm-up of both phases
+            warm.prefill(prompt[:48], 48)
+            warm.decode(2, budget)
+            s = eng.new_seq()
+            if adapters:
+                s.set_adapter(eng.map_adapter(adapters[case.get("attach", 0)]))
+            t0 = time.perf_counter()
+            assert s.prefill(prompt, chunk) == len(prompt)
+            t1 = time.perf_counter()
+            s.decode(1, budget)                             # the pending logits: no layer runs
+            n = case["decode"] - 1
+            t2 = time.perf_counter()
+            s.decode(n, budget)
+            t3 = time.perf_counter()
+        finally:
+            eng.close()
+        rows[name] = {"shape": case["shape"], "prompt_tokens": len(prompt), "prefill_chunk": chunk,
+                      "prefill_tok_s": round(len(prompt) / (t1 - t0), 2), "decode_tokens": n, "layer_budget": budget,
+                      "decode_tok_s": round(n / (t3 - t2), 2)}
+    print(json.dumps({"config_table": rows, **impl}))
+
+
 def run_only_sweep(args):
     from superslm_b200 import build as B
     lib = abi.SslmLib(B.LIB if os.path.exists(B.LIB) else B.build())
@@ -749,7 +806,9 @@ def run_only_sweep(args):
 if __name__ == "__main__":
     a = parse_args()
     try:
-        if a.only_sweep:
+        if a.config_table:
+            run_config_table(a)
+        elif a.only_sweep:
             run_only_sweep(a)
         elif a.impl == "reference":
             run_reference(a)
