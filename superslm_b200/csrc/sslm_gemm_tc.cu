@@ -4,7 +4,7 @@
 //
 // A = activations [M,K] and B = weights [N,K] are both K-major, which is exactly the
 // operand form tcgen05.mma wants, so nothing is repacked: TMA (cp.async.bulk.tensor.2d,
-// 128-byte swizzle, no multicast) streams 128-byte-wide tiles of both into a shared-memory
+// 128-byte swizzle, loads of this block only) streams 128-byte-wide tiles of both into a shared-memory
 // ring, one thread issues tcgen05.mma.kind::i8 (s8 x s8 -> s32, M=128, N=BN, K=32 per
 // instruction) into TMEM accumulators, and eight epilogue warps read the accumulators back
 // with tcgen05.ld, apply the per-channel fixed-point fold (ApplyWeightScaleFold,
