@@ -24,6 +24,12 @@ CASES = {
                       logit_rows=2, gpu_splits=[(2288, 2), (256, 1)]),
     "long_3b": dict(shape="mini3b", seed=SEED | 0x103, context_cap=4608, prompt_len=4592, decode=10, cpu_chunk=4592,
                     logit_rows=2, gpu_splits=[(4592, 2), (1000, 1)]),
+    # the widest rows the library admits: context_cap 32768 (16 slices of 2048 positions per kv head) on the
+    # smallest shape, and a row beyond 8192 positions (16 slices, funnel not fused) at the 1.5B widths
+    "max_context_tiny": dict(shape="tiny", seed=SEED | 0x106, context_cap=32768, prompt_len=32768 - 24, decode=10,
+                             cpu_chunk=2048, logit_rows=2, gpu_splits=[(2048, 2), (777, 1)]),
+    "long_1p5b_9k": dict(shape="mini1.5b", seed=SEED | 0x107, context_cap=9216, prompt_len=9216 - 16, decode=8,
+                         cpu_chunk=2048, logit_rows=2, gpu_splits=[(2048, 2), (1500, 1)]),
     # configuration 2 on the full 1.5B model: 2048-token prompt, chunked prefill, sliced decode
     "config2": dict(shape="1.5b", seed=SEED | 0x104, context_cap=2304, prompt_len=2048, decode=24, cpu_chunk=256,
                     logit_rows=2, gpu_splits=[(256, 28), (2048, 7), (64, 1)]),

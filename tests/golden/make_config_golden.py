@@ -13,7 +13,8 @@ small records are committed. The long cases take minutes of CPU each; they run a
 processes.
 
     python tests/golden/make_config_golden.py            # all cases, in parallel
-    python tests/golden/make_config_golden.py --case NAME
+    python tests/golden/make_config_golden.py --case NAME     # one case into _config_parts/
+    python tests/golden/make_config_golden.py --assemble       # write the JSON from the parts at hand
 """
 import argparse
 import ctypes as C
@@ -105,6 +106,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case")
     ap.add_argument("--jobs", type=int, default=4)
+    ap.add_argument("--assemble", action="store_true")
     args = ap.parse_args()
     outdir = os.path.join(HERE, "_config_parts")
     os.makedirs(outdir, exist_ok=True)
@@ -113,7 +115,7 @@ def main():
         json.dump(rec, open(os.path.join(outdir, args.case + ".json"), "w"))
         print(args.case, rec["tokens"][:6], rec["kv_saturation_count"], rec["kv_nonzero"], rec["cpu_seconds"])
         return
-    pending = list(CASES)
+    pending = [] if args.assemble else list(CASES)
     running = []
     while pending or running:
         while pending and len(running) < args.jobs:
