@@ -67,7 +67,7 @@ def parse_args():
     ap.add_argument("--chunk", type=int, default=1024, help="prefill chunk budget")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-threads", type=int, default=0)
-    ap.add_argument("--parity-seqs", type=int, default=4,
+    ap.add_argument("--parity-seqs", type=int, default=16,
                     help="workload sequences compared with the CPU reference's records (up to 16)")
     ap.add_argument("--no-sweep", action="store_true", help="skip the standalone linear-layer grid")
     ap.add_argument("--no-single", action="store_true", help="skip the single-sequence measurement")
